@@ -1,0 +1,90 @@
+"""Builds cuke_b200/libkge_b200.so from cuke_b200/csrc/*.cu with nvcc for sm_100a (in-tree, no JIT cache).
+
+    python -m cuke_b200.build [--force] [--verbose]
+
+Every .cu is compiled to an object under cuke_b200/csrc/build/ (in parallel) and linked into one shared
+library with C linkage entry points only (include/kge_b200.h).  `-Xptxas -v` output (registers, spills,
+shared memory per kernel) is kept in cuke_b200/csrc/build/ptxas.log.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG, "csrc")
+BUILD = os.path.join(CSRC, "build")
+LIB = os.path.join(PKG, "libkge_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v",
+    "--expt-relaxed-constexpr", "-diag-suppress", "177,550",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target: str, deps) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    os.makedirs(BUILD, exist_ok=True)
+    nvcc = _nvcc()
+    sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(PKG, "..", "include", "kge_b200.h"),
+                                                                  os.path.abspath(__file__)]
+    jobs = []
+    for src in sources:
+        obj = os.path.join(BUILD, os.path.basename(src)[:-3] + ".o")
+        if force or _stale(obj, [src] + headers):
+            jobs.append((src, obj))
+
+    def compile_one(job):
+        src, obj = job
+        cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return src, r.returncode, r.stdout + r.stderr
+
+    logs = []
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for src, rc, out in ex.map(compile_one, jobs):
+                logs.append(f"==== {os.path.basename(src)}\n{out}")
+                if rc != 0:
+                    sys.stderr.write(out)
+                    raise RuntimeError(f"nvcc failed on {src}")
+                if verbose:
+                    print(out)
+        with open(os.path.join(BUILD, "ptxas.log"), "a") as f:
+            f.write("\n".join(logs))
+    objs = [os.path.join(BUILD, os.path.basename(s)[:-3] + ".o") for s in sources]
+    if force or jobs or _stale(LIB, objs):
+        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build(a.force, a.verbose))

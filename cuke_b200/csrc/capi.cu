@@ -1,0 +1,324 @@
+// extern "C" entry points of libkge_b200.so: argument validation, workspace carving, launch sequencing.
+// Declarations and their reference counterparts are in include/kge_b200.h.
+#include <stdarg.h>
+#include <string.h>
+#include "common.cuh"
+
+namespace kge {
+
+// ---- error plumbing ------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int cuda_status(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return (int)e;
+}
+
+__device__ int32_t g_error_word = 0;
+int32_t* device_error_word() {
+    int32_t* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_error_word) != cudaSuccess) return nullptr;
+    return p;
+}
+
+// implemented in the other translation units
+int launch_pair_forward(const ScoreArgs& a, int head, cudaStream_t s);
+int launch_pair_backward(const ScoreArgs& a, const float* anchors, float* ga, cudaStream_t s);
+size_t inspect_workspace_bytes(long long n);
+int launch_inspect(const void* ids, int id_bits, long long n, long long id_space, void* ws, size_t ws_bytes,
+                   long long* uniq, int* inverse, int* perm, int* seg, long long* n_unique, cudaStream_t s);
+size_t segment_reduce_workspace_bytes(long long n, int dim);
+int launch_segment_reduce(const float* rows, int dim, long long n, const int* perm, const int* seg,
+                          const long long* n_unique, float* out, long long n_out, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_gather_rows(const void* table, int dtype, int dim, const long long* ids, long long n, const long long* n_dev,
+                       long long first_row, void* out, cudaStream_t s);
+int launch_owner_counts(const long long* uniq, const long long* n_unique, long long n_max, long long rows_per_rank,
+                        int world, long long* counts, cudaStream_t s);
+int launch_legacy_inspect(const long long* rel, long long n, long long rel_num, long long* uniq, long long* buf,
+                          long long* cnt, cudaStream_t s);
+int launch_logistic_loss(const float* pos, long long n_pos, const float* neg, long long n_neg, float neg_w, float* dpos,
+                         float* dneg, float* loss, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anchors, cudaStream_t s);
+int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
+                           cudaStream_t s);
+int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
+
+// ---- validation -------------------------------------------------------------------------------------------
+#define KGE_REQUIRE_PTR(ptr, name)                                                     \
+    do {                                                                               \
+        if ((ptr) == nullptr) { set_error("%s: %s is NULL", fn, name); return KGE_E_NULL; } \
+        if (!aligned16(ptr)) { set_error("%s: %s is not 16-byte aligned", fn, name); return KGE_E_ALIGN; } \
+    } while (0)
+#define KGE_OPTIONAL_PTR(ptr, name)                                                    \
+    do {                                                                               \
+        if ((ptr) != nullptr && !aligned16(ptr)) { set_error("%s: %s is not 16-byte aligned", fn, name); return KGE_E_ALIGN; } \
+    } while (0)
+
+static bool uses_rel(int model) { return model != KGE_RESCAL; }
+static bool uses_rel2(int model) { return model == KGE_TRANSH || model == KGE_TRANSR || model == KGE_RESCAL; }
+static bool matrix_model(int model) { return model == KGE_TRANSR || model == KGE_RESCAL; }
+
+static int check_problem(const char* fn, const kge_problem* p, const kge_tensors* t, bool scored) {
+    if (!p || !t) { set_error("%s: problem/tensors is NULL", fn); return KGE_E_NULL; }
+    if (p->model < KGE_TRANSE || p->model > KGE_COMPLEX) { set_error("%s: unknown model %d", fn, p->model); return KGE_E_UNSUPPORTED; }
+    if (p->dtype != KGE_F32 && p->dtype != KGE_BF16) { set_error("%s: unknown dtype %d", fn, p->dtype); return KGE_E_UNSUPPORTED; }
+    if (p->id_bits != 32 && p->id_bits != 64) { set_error("%s: id_bits must be 32 or 64, got %d", fn, p->id_bits); return KGE_E_UNSUPPORTED; }
+    if (p->dim <= 0 || p->dim > 1024) { set_error("%s: dim %d outside [1, 1024]", fn, p->dim); return KGE_E_UNSUPPORTED; }
+    if (p->model == KGE_COMPLEX && (p->dim & 1)) { set_error("%s: ComplEx needs an even dim (re,im interleaved), got %d", fn, p->dim); return KGE_E_SHAPE; }
+    if (p->dtype == KGE_BF16 && (p->dim & 7)) { set_error("%s: bf16 tables need dim %% 8 == 0 (16-byte rows), got %d", fn, p->dim); return KGE_E_UNSUPPORTED; }
+    if (p->batch < 0) { set_error("%s: negative batch", fn); return KGE_E_SHAPE; }
+    if (p->batch == 0) return 0;
+    KGE_REQUIRE_PTR(t->ent, "ent");
+    if (uses_rel(p->model)) KGE_REQUIRE_PTR(t->rel, "rel");
+    if (uses_rel2(p->model)) KGE_REQUIRE_PTR(t->rel2, "rel2");
+    KGE_REQUIRE_PTR(t->h, "h"); KGE_REQUIRE_PTR(t->r, "r"); KGE_REQUIRE_PTR(t->t, "t");
+    if (!scored) {
+        if (p->neg_mode != KGE_NEG_NONE) { set_error("%s: neg_mode must be KGE_NEG_NONE (flatten negatives into the batch)", fn); return KGE_E_UNSUPPORTED; }
+        return 0;
+    }
+    if (p->neg_mode < KGE_NEG_NONE || p->neg_mode > KGE_NEG_CHUNK_SHARED) { set_error("%s: unknown neg_mode %d", fn, p->neg_mode); return KGE_E_UNSUPPORTED; }
+    if (p->neg_mode != KGE_NEG_NONE) {
+        if (p->n_neg <= 0) { set_error("%s: n_neg must be > 0 with negatives", fn); return KGE_E_SHAPE; }
+        if (p->n_neg_head < 0 || p->n_neg_head > p->n_neg) { set_error("%s: n_neg_head %d outside [0, n_neg]", fn, p->n_neg_head); return KGE_E_SHAPE; }
+        KGE_REQUIRE_PTR(t->neg, "neg");
+    }
+    if (p->neg_mode == KGE_NEG_CHUNK_SHARED) {
+        if (p->chunk <= 0 || p->batch % p->chunk != 0) { set_error("%s: batch %lld is not a multiple of chunk %d", fn, (long long)p->batch, p->chunk); return KGE_E_SHAPE; }
+        if (p->n_neg_head != 0 && p->n_neg_head != p->n_neg) { set_error("%s: chunk-shared negatives replace one side only (n_neg_head must be 0 or n_neg)", fn); return KGE_E_UNSUPPORTED; }
+        if (p->model == KGE_TRANSH || p->model == KGE_TRANSF || p->model == KGE_TRANSR) {
+            set_error("%s: model %d supports per-triple negatives only", fn, p->model); return KGE_E_UNSUPPORTED;
+        }
+    }
+    if (p->model == KGE_RESCAL && p->neg_mode != KGE_NEG_NONE && p->n_neg_head != 0) {
+        set_error("%s: RESCAL negatives replace the tail only", fn); return KGE_E_UNSUPPORTED;
+    }
+    if (matrix_model(p->model)) {
+        KGE_REQUIRE_PTR(t->rel_perm, "rel_perm"); KGE_REQUIRE_PTR(t->rel_seg, "rel_seg");
+        KGE_REQUIRE_PTR(t->rel_uniq, "rel_uniq"); KGE_REQUIRE_PTR(t->n_rel_groups, "n_rel_groups");
+        if (p->n_rel <= 0) { set_error("%s: n_rel must be given for relation-matrix models", fn); return KGE_E_SHAPE; }
+    }
+    return 0;
+}
+
+static ScoreArgs score_args(const kge_problem* p, const kge_tensors* t) {
+    ScoreArgs a;
+    memset(&a, 0, sizeof(a));
+    a.ent = t->ent; a.rel = t->rel; a.rel2 = t->rel2; a.h = t->h; a.r = t->r; a.t = t->t; a.neg = t->neg;
+    a.batch = p->batch; a.dim = p->dim; a.chunk = p->chunk;
+    a.n_neg = p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg;
+    a.n_neg_head = p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg_head;
+    a.model = p->model; a.dtype = p->dtype; a.id_bits = p->id_bits;
+    return a;
+}
+
+static inline size_t rows_bytes(const kge_problem* p) { return ((size_t)p->batch * p->dim * 4 + 255) / 256 * 256; }
+
+}  // namespace kge
+
+using namespace kge;
+
+extern "C" {
+
+int kge_version(void) { return KGE_ABI_VERSION; }
+const char* kge_last_error(void) { return g_err; }
+
+int kge_check(kge_stream_t stream, int32_t* flags_out) {
+    const char* fn = "kge_check";
+    if (!flags_out) { set_error("%s: flags_out is NULL", fn); return KGE_E_NULL; }
+    int32_t* w = device_error_word();
+    if (!w) { set_error("%s: no device error word (no usable device?)", fn); return KGE_E_DEVICE; }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(flags_out, w, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(w, 0, sizeof(int32_t), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return cuda_status(e, fn);
+}
+
+int kge_ref_forward(const kge_problem* p, const kge_tensors* t, float* out, kge_stream_t stream) {
+    const char* fn = "kge_ref_forward";
+    int rc = check_problem(fn, p, t, false);
+    if (rc) return rc;
+    if (p->batch == 0) return 0;
+    KGE_REQUIRE_PTR(out, "out");
+    return launch_ref_forward(p, t, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t kge_inspect_workspace_bytes(int64_t n) { return inspect_workspace_bytes(n); }
+
+int kge_inspect(const void* ids, int32_t id_bits, int64_t n, int64_t id_space, void* workspace, size_t workspace_bytes,
+                int64_t* uniq, int32_t* inverse, int32_t* perm, int32_t* seg, int64_t* n_unique, kge_stream_t stream) {
+    const char* fn = "kge_inspect";
+    if (n < 0 || n > 2147483647LL) { set_error("%s: n %lld outside [0, 2^31-1]", fn, (long long)n); return KGE_E_RANGE; }
+    if (id_space < 1 || id_space > (1LL << 31)) { set_error("%s: id_space %lld outside [1, 2^31]", fn, (long long)id_space); return KGE_E_RANGE; }
+    if (id_bits != 32 && id_bits != 64) { set_error("%s: id_bits must be 32 or 64", fn); return KGE_E_UNSUPPORTED; }
+    KGE_REQUIRE_PTR(seg, "seg"); KGE_REQUIRE_PTR(n_unique, "n_unique");
+    if (n > 0) {
+        KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(workspace, "workspace"); KGE_REQUIRE_PTR(uniq, "uniq");
+        KGE_REQUIRE_PTR(inverse, "inverse"); KGE_REQUIRE_PTR(perm, "perm");
+    }
+    return launch_inspect(ids, id_bits, n, id_space, workspace, workspace_bytes, (long long*)uniq, inverse, perm, seg,
+                          (long long*)n_unique, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_legacy_inspect(const int64_t* rel, int64_t n, int64_t rel_num, int64_t* uniq, int64_t* buf, int64_t* cnt,
+                       kge_stream_t stream) {
+    const char* fn = "kge_legacy_inspect";
+    if (n < 0 || n % 16 != 0) { set_error("%s: n %lld is not a non-negative multiple of 16", fn, (long long)n); return KGE_E_SHAPE; }
+    if (n == 0) return 0;
+    KGE_REQUIRE_PTR(rel, "rel"); KGE_REQUIRE_PTR(uniq, "uniq"); KGE_REQUIRE_PTR(buf, "buf"); KGE_REQUIRE_PTR(cnt, "cnt");
+    return launch_legacy_inspect((const long long*)rel, n, rel_num, (long long*)uniq, (long long*)buf, (long long*)cnt,
+                                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_gather_rows(const void* table, int32_t dtype, int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev,
+                    int64_t first_row, void* out, kge_stream_t stream) {
+    const char* fn = "kge_gather_rows";
+    if (n <= 0) return 0;
+    if (dim <= 0) { set_error("%s: dim must be positive", fn); return KGE_E_SHAPE; }
+    if (dtype != KGE_F32 && dtype != KGE_BF16) { set_error("%s: unknown dtype %d", fn, dtype); return KGE_E_UNSUPPORTED; }
+    KGE_REQUIRE_PTR(table, "table"); KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
+    return launch_gather_rows(table, dtype, dim, (const long long*)ids, n, (const long long*)n_dev, first_row, out,
+                              reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t kge_segment_reduce_workspace_bytes(int64_t n, int32_t dim) { return segment_reduce_workspace_bytes(n < 1 ? 1 : n, dim); }
+
+int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t* perm, const int32_t* seg,
+                       const int64_t* n_unique, float* out, int64_t n_out, void* workspace, size_t workspace_bytes,
+                       kge_stream_t stream) {
+    const char* fn = "kge_segment_reduce";
+    if (n < 0 || n > 2147483647LL || n_out < 0) { set_error("%s: bad sizes", fn); return KGE_E_RANGE; }
+    if (dim <= 0 || dim > 1024) { set_error("%s: dim %d outside [1, 1024]", fn, dim); return KGE_E_UNSUPPORTED; }
+    if (n_out > 0) KGE_REQUIRE_PTR(out, "out");
+    if (n > 0) {
+        KGE_REQUIRE_PTR(rows, "rows"); KGE_REQUIRE_PTR(perm, "perm"); KGE_REQUIRE_PTR(seg, "seg");
+        KGE_REQUIRE_PTR(n_unique, "n_unique"); KGE_REQUIRE_PTR(workspace, "workspace");
+    }
+    return launch_segment_reduce(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, workspace,
+                                 workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
+    if (!p || p->batch <= 0) return 256;
+    const size_t rb = rows_bytes(p);
+    if (backward) return 3 * rb + 256;
+    return (p->model == KGE_RESCAL ? rb : 0) + 256;
+}
+
+int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_score, float* neg_score, void* workspace,
+                      size_t workspace_bytes, kge_stream_t stream) {
+    const char* fn = "kge_score_forward";
+    int rc = check_problem(fn, p, t, true);
+    if (rc) return rc;
+    if (p->batch == 0) return 0;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    KGE_REQUIRE_PTR(pos_score, "pos_score");
+    if (p->neg_mode != KGE_NEG_NONE) KGE_REQUIRE_PTR(neg_score, "neg_score");
+    const size_t need = kge_score_workspace_bytes(p, 0);
+    if (need > 256) {
+        KGE_REQUIRE_PTR(workspace, "workspace");
+        if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    }
+    ScoreArgs a = score_args(p, t);
+    a.pos = pos_score; a.negs = neg_score;
+    if (p->model == KGE_TRANSR) return launch_transr_forward(p, t, pos_score, neg_score, s);
+    if (p->model == KGE_RESCAL) {
+        float* anchors = static_cast<float*>(workspace);
+        rc = launch_rescal_anchors(p, t, anchors, s);
+        if (rc) return rc;
+        a.anchors = anchors;
+    }
+    if (p->neg_mode != KGE_NEG_CHUNK_SHARED) return launch_triple_forward(a, s);
+    ScoreArgs apos = a;
+    apos.n_neg = 0; apos.n_neg_head = 0;
+    rc = launch_triple_forward(apos, s);
+    if (rc) return rc;
+    return launch_pair_forward(a, p->n_neg_head > 0 ? 1 : 0, s);
+}
+
+int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* pos_score, const float* neg_score,
+                       const float* dpos, const float* dneg, const kge_grads* g, void* workspace, size_t workspace_bytes,
+                       kge_stream_t stream) {
+    const char* fn = "kge_score_backward";
+    int rc = check_problem(fn, p, t, true);
+    if (rc) return rc;
+    if (p->batch == 0) return 0;
+    if (p->model == KGE_TRANSR) { set_error("%s: TransR backward is not available", fn); return KGE_E_UNSUPPORTED; }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }
+    KGE_REQUIRE_PTR(dpos, "dpos");
+    KGE_REQUIRE_PTR(g->g_head, "g_head"); KGE_REQUIRE_PTR(g->g_tail, "g_tail");
+    if (p->model != KGE_RESCAL) KGE_REQUIRE_PTR(g->g_rel, "g_rel");
+    if (p->model == KGE_TRANSH || p->model == KGE_RESCAL) KGE_REQUIRE_PTR(g->g_rel2, "g_rel2");
+    if (p->neg_mode != KGE_NEG_NONE) {
+        KGE_REQUIRE_PTR(dneg, "dneg"); KGE_REQUIRE_PTR(g->g_neg, "g_neg");
+        if (p->neg_mode == KGE_NEG_CHUNK_SHARED && p->model == KGE_TRANSE) KGE_REQUIRE_PTR(neg_score, "neg_score");
+    }
+    (void)pos_score;
+    const size_t need = kge_score_workspace_bytes(p, 1);
+    KGE_REQUIRE_PTR(workspace, "workspace");
+    if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    const size_t rb = rows_bytes(p);
+    float* ws0 = static_cast<float*>(workspace);                                          // anchors
+    float* ws1 = reinterpret_cast<float*>(static_cast<char*>(workspace) + rb);            // chunk-shared anchor gradients
+    float* ws2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * rb);        // RESCAL total anchor gradient
+
+    ScoreArgs a = score_args(p, t);
+    a.negs = const_cast<float*>(neg_score);
+    a.dpos = dpos; a.dneg = dneg;
+    a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel; a.g_rel2 = g->g_rel2;
+    if (p->model == KGE_RESCAL) {
+        rc = launch_rescal_anchors(p, t, ws0, s);
+        if (rc) return rc;
+        a.anchors = ws0; a.g_rel = ws2; a.g_rel2 = nullptr;
+    }
+    if (p->neg_mode == KGE_NEG_CHUNK_SHARED) {
+        const bool head = p->n_neg_head > 0;
+        if (p->model != KGE_RESCAL) {
+            rc = launch_anchor(a, head ? nullptr : ws0, head ? ws0 : nullptr, s);
+            if (rc) return rc;
+        }
+        rc = launch_pair_backward(a, ws0, ws1, s);
+        if (rc) return rc;
+        ScoreArgs b = a;
+        b.n_neg = 0; b.n_neg_head = 0;
+        if (head) b.ga_head_init = ws1; else b.ga_tail_init = ws1;
+        rc = launch_triple_backward(b, s);
+    } else {
+        rc = launch_triple_backward(a, s);
+    }
+    if (rc) return rc;
+    if (p->model == KGE_RESCAL) rc = launch_rescal_backward(p, t, ws2, g->g_head, g->g_rel2, s);
+    return rc;
+}
+
+int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg, int64_t n_neg_total, float neg_weight,
+                      float* dpos, float* dneg, float* loss_out, void* workspace, size_t workspace_bytes,
+                      kge_stream_t stream) {
+    const char* fn = "kge_logistic_loss";
+    if (n_pos < 0 || n_neg_total < 0) { set_error("%s: negative size", fn); return KGE_E_SHAPE; }
+    KGE_REQUIRE_PTR(loss_out, "loss_out"); KGE_REQUIRE_PTR(workspace, "workspace");
+    if (n_pos > 0) { KGE_REQUIRE_PTR(pos, "pos"); KGE_REQUIRE_PTR(dpos, "dpos"); }
+    if (n_neg_total > 0) { KGE_REQUIRE_PTR(neg, "neg"); KGE_REQUIRE_PTR(dneg, "dneg"); }
+    return launch_logistic_loss(pos, n_pos, neg, n_neg_total, neg_weight, dpos, dneg, loss_out, workspace, workspace_bytes,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank, int32_t world,
+                     int64_t* counts, kge_stream_t stream) {
+    const char* fn = "kge_owner_counts";
+    if (world <= 0 || rows_per_rank <= 0) { set_error("%s: world and rows_per_rank must be positive", fn); return KGE_E_SHAPE; }
+    KGE_REQUIRE_PTR(n_unique, "n_unique"); KGE_REQUIRE_PTR(counts, "counts");
+    if (n_max > 0) KGE_REQUIRE_PTR(uniq, "uniq");
+    return launch_owner_counts((const long long*)uniq, (const long long*)n_unique, n_max, rows_per_rank, world,
+                               (long long*)counts, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

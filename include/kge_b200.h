@@ -1,0 +1,220 @@
+/*
+ * kge_b200.h — C ABI of libkge_b200.so: knowledge-graph-embedding scoring on NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary that replaces cuke's "emit CUDA text, JIT-compile it, call module.run(*args)"
+ * step (reference: pycuke1/run/gpu.py:4-19 and the generated host wrapper
+ * pycuke1/codegen/gpu_template.cu:8-17) and its hand-written inspector module
+ * (reference: apps/kge/kge.py:249-271, apps/kge/inspection/inspector.cu:139-146).
+ *
+ * Conventions
+ *   - C linkage, POD structs, raw DEVICE pointers (e.g. torch `tensor.data_ptr()`), row-major contiguous
+ *     tensors, every base pointer 16-byte aligned.  Pointers are never retained after a call returns.
+ *   - The library never allocates or frees device memory that the caller can see: outputs and scratch
+ *     ("workspace") are caller-provided; `*_workspace_bytes` says how much is needed.
+ *   - Every launch goes to the `cudaStream_t` passed in; calls are asynchronous with respect to the host
+ *     unless stated otherwise.  Re-entrant per (device, stream).
+ *   - Return value: 0 = success; negative = argument error (KGE_E_*), nothing was launched;
+ *     positive = a cudaError_t reported by the runtime for this call's launches.  `kge_last_error()`
+ *     returns a thread-local, human-readable description of the last non-zero return.
+ *   - Entity / relation ids are int64 (the reference's GPU convention, pycuke1/codegen/gpu.py:200-201)
+ *     or int32 (`id_bits`).  Ids are trusted to lie inside the tables, exactly as in the reference
+ *     (its generated kernels do no bounds checks either).
+ *   - Relation matrices use the orientation of the reference's CPU path: for `'i,ij->j'`
+ *     (apps/kge/kge.py:21-23) out[j] = sum_i x[i] * Proj[r][i][j].
+ */
+#ifndef KGE_B200_H
+#define KGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque stand-in so that this header needs no CUDA include; pass a cudaStream_t. */
+typedef struct CUstream_st* kge_stream_t;
+
+#define KGE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define KGE_API __attribute__((visibility("default")))
+#else
+#define KGE_API
+#endif
+
+enum kge_status {
+    KGE_OK = 0,
+    KGE_E_NULL = -1,         /* a required pointer is NULL */
+    KGE_E_ALIGN = -2,        /* a pointer is not 16-byte aligned */
+    KGE_E_UNSUPPORTED = -3,  /* model / dtype / mode / dim combination not supported */
+    KGE_E_SHAPE = -4,        /* inconsistent sizes (e.g. batch not a multiple of chunk) */
+    KGE_E_WORKSPACE = -5,    /* workspace too small */
+    KGE_E_RANGE = -6,        /* size beyond a stated maximum */
+    KGE_E_DEVICE = -7        /* no usable sm_100 device / kernel image missing */
+};
+
+/* Score functions.  TransE/TransH/TransR/TransF/RESCAL follow apps/kge/kge.py:273-390; DistMult and
+ * ComplEx are absent from the reference and written with the same operators (bvv over elementwise
+ * products). */
+enum kge_model {
+    KGE_TRANSE = 0,   /* v = E[h] - E[t] + R[r]                         score = -||v||_2 */
+    KGE_TRANSH = 1,   /* u = E[h]-E[t]; v = u + R[r] - (W[r].u) W[r]    score = -||v||_2 */
+    KGE_TRANSR = 2,   /* v = (E[h]-E[t]) . P[r] + R[r]                  score = -||v||_2 */
+    KGE_TRANSF = 3,   /* score = (E[h]+R[r]).E[t] + (E[t]-R[r]).E[h]                     */
+    KGE_DISTMULT = 4, /* score = sum_k E[h][k] R[r][k] E[t][k]                           */
+    KGE_RESCAL = 5,   /* score = sum_j (sum_i E[h][i] P[r][i][j]) E[t][j]                */
+    KGE_COMPLEX = 6   /* rows interleaved re,im; score = Re(sum_k h_k r_k conj(t_k))     */
+};
+
+enum kge_dtype { KGE_F32 = 0, KGE_BF16 = 1 };   /* storage type of the tables; accumulation is fp32 */
+
+enum kge_neg_mode {
+    KGE_NEG_NONE = 0,         /* positives only */
+    KGE_NEG_PER_TRIPLE = 1,   /* neg is (batch, n_neg): triple i is scored against its own n_neg rows */
+    KGE_NEG_CHUNK_SHARED = 2  /* neg is (batch/chunk, n_neg): all triples of a chunk share n_neg rows
+                                 (the layout of apps/examples/examples.py:1434-1441) */
+};
+
+typedef struct kge_problem {
+    int32_t model;       /* enum kge_model */
+    int32_t dtype;       /* enum kge_dtype */
+    int32_t neg_mode;    /* enum kge_neg_mode */
+    int32_t id_bits;     /* 32 or 64: width of h, r, t, neg */
+    int32_t dim;         /* floats per entity row (ComplEx: 2 x complex dimension) */
+    int32_t n_neg;       /* negatives per triple (per-triple) or per chunk (chunk-shared); 0 if none */
+    int32_t n_neg_head;  /* the first n_neg_head negatives replace the head, the others the tail */
+    int32_t chunk;       /* triples per chunk (chunk-shared), else 0 */
+    int64_t batch;       /* number of positive triples */
+    int64_t n_ent;       /* rows of `ent` */
+    int64_t n_rel;       /* rows of `rel` / `rel2` */
+} kge_problem;
+
+typedef struct kge_tensors {
+    const void* ent;   /* (n_ent, dim) entity table, or a compact staging buffer addressed by slot ids */
+    const void* rel;   /* (n_rel, dim) relation vectors; NULL for RESCAL */
+    const void* rel2;  /* TransH: hyperplane normals (n_rel, dim); TransR/RESCAL: (n_rel, dim, dim); else NULL */
+    const void* h;     /* (batch,) head ids */
+    const void* r;     /* (batch,) relation ids */
+    const void* t;     /* (batch,) tail ids */
+    const void* neg;   /* negative entity ids, shape per neg_mode; NULL if none */
+    /* Relation grouping produced by kge_inspect over `r`; required by TransR/RESCAL scoring, else NULL. */
+    const int32_t* rel_perm;    /* (batch,) triples ordered by relation id (stable) */
+    const int32_t* rel_seg;     /* (>= n_rel_groups+1,) start of each group in rel_perm */
+    const int64_t* rel_uniq;    /* (n_rel_groups,) relation id of each group */
+    const int64_t* n_rel_groups;/* device scalar */
+} kge_tensors;
+
+/* Per-slot gradient rows written by kge_score_backward ("slot" = one id occurrence).  g_head, g_tail and
+ * g_neg are normally three consecutive regions of one buffer laid out like the id list [h | t | neg] given
+ * to kge_inspect, so that a single kge_segment_reduce turns them into one gradient row per distinct entity. */
+typedef struct kge_grads {
+    float* g_head;   /* (batch, dim) */
+    float* g_tail;   /* (batch, dim) */
+    float* g_neg;    /* (number of negative ids, dim); NULL if no negatives */
+    float* g_rel;    /* (batch, dim) gradient of R[r] per triple; NULL for RESCAL */
+    float* g_rel2;   /* TransH: (batch, dim) gradient of W[r] per triple.
+                        TransR/RESCAL: (n_rel_groups, dim, dim) gradient of P[rel_uniq[g]], already summed
+                        over the triples of group g.  Else NULL. */
+} kge_grads;
+
+/* ---- library ------------------------------------------------------------------------------------ */
+
+KGE_API int kge_version(void);                 /* KGE_ABI_VERSION of the loaded library */
+KGE_API const char* kge_last_error(void);      /* thread-local message for the last non-zero return */
+
+/* Reads (and clears) the device error word of the current device: 0 = clean.  Synchronises `stream`.
+ * Bit 2: a bounded wait inside a kernel ran out and the kernel gave up (its outputs are then invalid). */
+KGE_API int kge_check(kge_stream_t stream, int32_t* flags_out);
+
+/* ---- reference-compatible forward ---------------------------------------------------------------
+ * Replaces `module.run(*args)` of the code the reference generates for apps/kge/kge.py:273-390
+ * (launch site pycuke1/codegen/gpu_template.cu:11).  Output exactly as the reference returns it:
+ * TransE/TransH/TransR -> the per-triple VECTOR v, (batch, dim) fp32, no norm;
+ * TransF/RESCAL/DistMult/ComplEx -> the scalar score, (batch,) fp32.
+ * neg_mode must be KGE_NEG_NONE (the reference flattens negatives into a longer batch,
+ * apps/kge/data/data_init.py:55-61).  TransR/RESCAL do not need the rel_* grouping here. */
+KGE_API int kge_ref_forward(const kge_problem* p, const kge_tensors* t, float* out, kge_stream_t stream);
+
+/* ---- inspector ----------------------------------------------------------------------------------
+ * GPU inspector: LSD radix sort + unique over n ids in [0, id_space).  Supersedes the per-16-id
+ * `build_index` kernel (apps/kge/inspection/inspector.cu:68-136) and the host-side
+ * `torch.argsort(rel_ids)` (apps/kge/test_cuke.py:93-96).  All outputs are bit-exact with
+ *   uniq, inverse = numpy.unique(ids, return_inverse=True);  perm = numpy.argsort(ids, kind="stable");
+ *   seg[u] = first sorted position of uniq[u];  seg[U..n] = n.
+ *   uniq     (n,)   int64  sorted distinct ids in [0, U); entries >= U are left untouched
+ *   inverse  (n,)   int32  ids[i] == uniq[inverse[i]]
+ *   perm     (n,)   int32  sorted position -> original position
+ *   seg      (n+1,) int32
+ *   n_unique (1,)   int64  U, on the device
+ * id_space must be <= 2^31.  n <= 2^31 - 1. */
+KGE_API size_t kge_inspect_workspace_bytes(int64_t n);
+KGE_API int kge_inspect(const void* ids, int32_t id_bits, int64_t n, int64_t id_space,
+                void* workspace, size_t workspace_bytes,
+                int64_t* uniq, int32_t* inverse, int32_t* perm, int32_t* seg, int64_t* n_unique,
+                kge_stream_t stream);
+
+/* Legacy inspector with the reference's exact outputs (apps/kge/kge.py:249-271,
+ * apps/kge/inspection/inspector.cu:68-143): for every chunk of 16 consecutive relation ids the two most
+ * frequent ids (count >= 2) go to uniq[b][0..1] (other entries = rel_num), buf[b][i] is the cache slot
+ * (0/1) or id+16, cnt[b] the number of cached ids.  rel (n,) int64, n a multiple of 16;
+ * uniq, buf (n/16, 16) int64 and cnt (n/16,) int64 must be zero-initialised by the caller as the
+ * reference does.  Chunks whose 16 ids are all distinct are handled without the reference's
+ * out-of-bounds shared-memory write (inspector.cu:90) and give the result that write-free code gives. */
+KGE_API int kge_legacy_inspect(const int64_t* rel, int64_t n, int64_t rel_num,
+                       int64_t* uniq, int64_t* buf, int64_t* cnt, kge_stream_t stream);
+
+/* Copies the rows ids[0..n) of `table` (n_rows x dim, dtype) into out (n x dim, same dtype): the
+ * dedup staging step (each distinct row leaves HBM once per batch).  If n_dev is not NULL the row
+ * count is min(n, *n_dev) read on the device.  `first_row` is subtracted from every id (row-partitioned
+ * tables: the local shard starts at global row first_row). */
+KGE_API int kge_gather_rows(const void* table, int32_t dtype, int32_t dim, const int64_t* ids, int64_t n,
+                    const int64_t* n_dev, int64_t first_row, void* out, kge_stream_t stream);
+
+/* Segmented sum: out[u][:] = sum over sorted positions p in [seg[u], seg[u+1]) of rows[perm[p]][:],
+ * added in ascending p (deterministic, no atomics).  rows (n, dim) fp32; out (n_out, dim) fp32 where
+ * n_out >= U; rows u in [U, n_out) are zero-filled.  The backward "scatter-add" of per-slot gradient rows
+ * into one row per distinct id (replaces the un-aggregated outputs of apps/kge/kge.py:393-515). */
+KGE_API size_t kge_segment_reduce_workspace_bytes(int64_t n, int32_t dim);
+KGE_API int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t* perm, const int32_t* seg,
+                       const int64_t* n_unique, float* out, int64_t n_out,
+                       void* workspace, size_t workspace_bytes, kge_stream_t stream);
+
+/* ---- scoring ------------------------------------------------------------------------------------
+ * Fused gather + score.  pos_score (batch,) ; neg_score (batch, n_neg) per-triple or
+ * (batch/chunk, chunk, n_neg) chunk-shared.  Scores as in enum kge_model.  Ids index `ent` directly; to
+ * score against a compact staging buffer pass that buffer as `ent` and slot numbers (the inspector's
+ * `inverse`, id_bits = 32) as h, t, neg.  Replaces the generated kernels of apps/kge/kge.py:273-390 plus
+ * the norm the reference leaves to the caller. */
+KGE_API size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward);
+KGE_API int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_score, float* neg_score,
+                      void* workspace, size_t workspace_bytes, kge_stream_t stream);
+
+/* Backward of kge_score_forward: given d(loss)/d(score) for every score, writes the per-slot gradient rows
+ * of struct kge_grads.  pos_score / neg_score are the forward's outputs (the distance models reuse them).
+ * True gradients of the forward above (the reference's backward_* demos, apps/kge/kge.py:393-515, are
+ * per-triple pieces of these). */
+KGE_API int kge_score_backward(const kge_problem* p, const kge_tensors* t,
+                       const float* pos_score, const float* neg_score,
+                       const float* dpos, const float* dneg, const kge_grads* g,
+                       void* workspace, size_t workspace_bytes, kge_stream_t stream);
+
+/* Logistic ranking loss over the scores and its derivative, for driving fwd+bwd without a host round trip:
+ * loss = sum softplus(-pos) + (1/n_neg_per_pos) sum softplus(neg);  dpos = -sigmoid(-pos),
+ * dneg = sigmoid(neg)/n_neg_per_pos.  loss_out (1,) fp32 device, reduced in a fixed order.
+ * workspace >= 4096 bytes. */
+KGE_API int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg, int64_t n_neg_total,
+                      float neg_weight, float* dpos, float* dneg, float* loss_out,
+                      void* workspace, size_t workspace_bytes, kge_stream_t stream);
+
+/* ---- row-partitioned tables (multi-GPU) ----------------------------------------------------------
+ * counts[g] = number of ids in uniq[0..U) owned by rank g under the contiguous partition
+ * owner(id) = id / rows_per_rank; uniq is sorted, so each rank's ids are one contiguous range.
+ * counts (world,) int64 device. */
+KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank,
+                     int32_t world, int64_t* counts, kge_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KGE_B200_H */
