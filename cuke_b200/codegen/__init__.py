@@ -1,0 +1,1 @@
+from . import gpu, cpu  # noqa: F401

@@ -1,0 +1,281 @@
+"""GPU parity: every entry of the C ABI against the CPU oracle on identical seeded inputs (bit-exact for the
+inspector's integer outputs, relative 1e-4 for fp32 scores/gradients, 2e-2 for bf16 tables)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.kge_testlib import (BF16_TOL, FP32_TOL, MODELS, bf16_round, gpu_grads_dense, gpu_ids, gpu_scorer,
+                               make_problem, rel_err, to_dev)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+CHUNK_MODELS = ["TransE", "DistMult", "ComplEx", "RESCAL"]
+BWD_MODELS = ["TransE", "TransH", "TransF", "DistMult", "RESCAL", "ComplEx"]
+
+
+# ---- reference-compatible forward against the reference's own golden outputs ------------------------------
+@pytest.mark.parametrize("model", MODELS)
+def test_ref_forward_golden(model):
+    from cuke_b200.scoring import Scorer
+    z = np.load(os.path.join(GOLDEN, f"ref_{model}.npz"))
+    g = {k: z[k] for k in z.files}
+    sc = Scorer(model, to_dev(g["E"]), to_dev(g.get("R")), to_dev(g.get("P2")))
+    out = sc.ref_forward(to_dev(g["h"]), to_dev(g["r"]), to_dev(g["t"])).cpu().numpy()
+    assert out.shape == g["ref_pos"].shape
+    assert rel_err(out, g["ref_pos"]) < FP32_TOL
+    fh, fr, ft = oracle.flatten(g["h"], g["r"], g["t"], g["neg"], "per_triple", int(g["n_neg_head"]))
+    outn = sc.ref_forward(to_dev(fh), to_dev(fr), to_dev(ft)).cpu().numpy()
+    assert rel_err(outn, g["ref_neg"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("model", MODELS)
+@pytest.mark.parametrize("d,B", [(4, 1), (37, 20), (128, 33), (200, 64), (520, 16)])
+@pytest.mark.parametrize("idt", [torch.int64, torch.int32])
+def test_ref_forward_shapes(model, d, B, idt):
+    if model == "ComplEx" and d % 2:
+        d += 1
+    if model in ("TransR", "RESCAL") and d > 256:
+        d = 264
+    p = make_problem(model, seed=d, d=d, B=B, neg_mode="none")
+    sc = gpu_scorer(p)
+    h, r, t, _ = gpu_ids(p, idt)
+    out = sc.ref_forward(h, r, t).cpu().numpy()
+    ref = oracle.ref_forward(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"])
+    assert rel_err(out, ref) < FP32_TOL
+
+
+# ---- scores ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("model", MODELS)
+@pytest.mark.parametrize("d,B,nn,nnh", [(40, 64, 8, 0), (40, 64, 8, 8), (37, 20, 5, 2), (200, 48, 70, 35), (512, 8, 33, 1)])
+def test_score_forward_per_triple(model, d, B, nn, nnh):
+    if model == "ComplEx" and d % 2:
+        d += 1
+    if model == "RESCAL":
+        nnh = 0
+    if model in ("TransR", "RESCAL") and d > 256:
+        d = 264
+    p = make_problem(model, seed=d + nn, d=d, B=B, nn=nn)
+    sc = gpu_scorer(p, nnh)
+    h, r, t, neg = gpu_ids(p)
+    pos, negs, _ = sc.forward(h, r, t, neg)
+    rpos, rneg = oracle.scores(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], p["neg"], "per_triple", nnh)
+    assert rel_err(pos.cpu().numpy(), rpos) < FP32_TOL
+    assert rel_err(negs.cpu().numpy(), rneg) < FP32_TOL
+    pos2, negs2, _ = sc.forward(h, r, t, neg)      # same launch twice: bit-identical (no races)
+    assert torch.equal(pos, pos2) and torch.equal(negs, negs2)
+
+
+@pytest.mark.parametrize("model", CHUNK_MODELS)
+@pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(40, 16, 3, 24, 0), (128, 128, 2, 128, 0), (200, 130, 2, 150, 1),
+                                                     (38, 7, 3, 9, 0), (400, 256, 1, 300, 0)])
+def test_score_forward_chunk_shared(model, d, chunk, nchunks, nn, head):
+    if model == "RESCAL":
+        head = 0
+        d = min(d, 200)
+    p = make_problem(model, seed=d + chunk, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    nnh = nn if head else 0
+    sc = gpu_scorer(p, nnh)
+    h, r, t, neg = gpu_ids(p, torch.int32 if d == 40 else torch.int64)
+    pos, negs, _ = sc.forward(h, r, t, neg)
+    rpos, rneg = oracle.scores(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], p["neg"], "chunk_shared", nnh, chunk)
+    assert rel_err(pos.cpu().numpy(), rpos) < FP32_TOL
+    assert rel_err(negs.reshape(len(rpos), -1).cpu().numpy(), rneg) < FP32_TOL
+
+
+@pytest.mark.parametrize("model", ["TransE", "TransH", "DistMult", "ComplEx", "RESCAL", "TransR"])
+def test_score_forward_bf16(model):
+    d = 200 if model != "ComplEx" else 256
+    p = make_problem(model, seed=77, d=d, B=64, nn=16)
+    nnh = 0 if model == "RESCAL" else 8
+    sc = gpu_scorer(p, nnh, bf16=True)
+    h, r, t, neg = gpu_ids(p)
+    pos, negs, _ = sc.forward(h, r, t, neg)
+    # oracle on the bf16-rounded tables: isolates kernel error from storage rounding
+    rpos, rneg = oracle.scores(model, bf16_round(p["E"]), bf16_round(p["R"]), bf16_round(p["P2"]), p["h"], p["r"], p["t"],
+                               p["neg"], "per_triple", nnh)
+    assert rel_err(pos.cpu().numpy(), rpos) < BF16_TOL
+    assert rel_err(negs.cpu().numpy(), rneg) < BF16_TOL
+
+
+# ---- gradients -------------------------------------------------------------------------------------------------
+def _check_grads(p, nnh, chunk, bf16=False, tol=FP32_TOL):
+    model = p["model"]
+    sc = gpu_scorer(p, nnh, bf16=bf16)
+    h, r, t, neg = gpu_ids(p)
+    g = p["g"]
+    B = len(p["h"])
+    dpos_np = g.standard_normal(B).astype(np.float32)
+    nshape = (B, p["neg"].shape[1])
+    dneg_np = g.standard_normal(nshape).astype(np.float32)
+    dneg = to_dev(dneg_np if p["neg_mode"] == "per_triple" else dneg_np.reshape(B // chunk, chunk, -1))
+    pos, negs, gE, gR, gP = gpu_grads_dense(p, sc, h, r, t, neg, to_dev(dpos_np), dneg)
+    E, R, P2 = (bf16_round(p[k]) for k in ("E", "R", "P2")) if bf16 else (p["E"], p["R"], p["P2"])
+    oE, oR, oP = oracle.grads(model, E, R, P2, p["h"], p["r"], p["t"], dpos_np, p["neg"], dneg_np, p["neg_mode"], nnh, chunk)
+    assert rel_err(gE, oE) < tol, "entity gradient"
+    if oR is not None:
+        assert rel_err(gR, oR) < tol, "relation gradient"
+    if oP is not None:
+        assert rel_err(gP, oP) < tol, "relation-2 gradient"
+
+
+@pytest.mark.parametrize("model", BWD_MODELS)
+@pytest.mark.parametrize("d,B,nn,nnh", [(40, 64, 8, 0), (40, 64, 8, 8), (36, 20, 5, 2), (200, 48, 40, 20), (264, 8, 9, 1)])
+def test_backward_per_triple(model, d, B, nn, nnh):
+    if model == "RESCAL":
+        nnh = 0
+    p = make_problem(model, seed=3 * d + nn, ne=90, d=d, B=B, nn=nn, zipf=True)
+    _check_grads(p, nnh, 0)
+
+
+@pytest.mark.parametrize("model", CHUNK_MODELS)
+@pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(40, 16, 3, 24, 0), (128, 128, 2, 128, 0), (200, 130, 2, 150, 1),
+                                                     (36, 7, 4, 9, 0), (400, 64, 1, 300, 0)])
+def test_backward_chunk_shared(model, d, chunk, nchunks, nn, head):
+    if model == "RESCAL":
+        head = 0
+        d = min(d, 200)
+    p = make_problem(model, seed=5 * d + chunk, ne=150, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    _check_grads(p, nn if head else 0, chunk)
+
+
+@pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx"])
+def test_backward_bf16_tables(model):
+    p = make_problem(model, seed=9, ne=90, d=64, B=32, nn=8, zipf=True)
+    _check_grads(p, 4, 0, bf16=True, tol=BF16_TOL)
+
+
+# ---- inspector ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,space", [(1, 1), (1, 7), (16, 3), (255, 256), (2048, 5), (2049, 70000), (5000, 300),
+                                     (100000, 4000000), (300000, 1 << 25), (70001, 1 << 31)])
+@pytest.mark.parametrize("idt", [torch.int64, torch.int32])
+def test_inspect_bit_exact(n, space, idt):
+    from cuke_b200 import scoring
+    if idt == torch.int32 and space > (1 << 31) - 1:
+        space = (1 << 31) - 1
+    g = np.random.Generator(np.random.PCG64(n + space % 1000))
+    ids = g.integers(0, space, n)
+    if n > 1000:   # make heavy duplicates as Zipf ids do
+        ids[: n // 3] = ids[0]
+    insp = scoring.inspect(to_dev(ids, idt), space)
+    uniq, inv, perm, seg = oracle.inspect(ids)
+    U = insp.count()
+    assert U == len(uniq)
+    assert np.array_equal(insp.uniq[:U].cpu().numpy(), uniq)
+    assert np.array_equal(insp.inverse[:n].cpu().numpy(), inv)
+    assert np.array_equal(insp.perm[:n].cpu().numpy(), perm)
+    assert np.array_equal(insp.seg.cpu().numpy(), seg)
+
+
+def test_inspect_empty():
+    from cuke_b200 import scoring
+    insp = scoring.inspect(torch.empty(0, dtype=torch.int64, device="cuda"), 10)
+    assert insp.count() == 0 and insp.seg.cpu().tolist() == [0]
+
+
+@pytest.mark.parametrize("n,space,d", [(1, 1, 4), (40, 3, 8), (1000, 7, 40), (5000, 900, 200), (3000, 3000, 37), (4096, 2, 400)])
+def test_segment_reduce(n, space, d):
+    from cuke_b200 import scoring
+    g = np.random.Generator(np.random.PCG64(n + d))
+    w = np.arange(1, space + 1, dtype=np.float64) ** -1.1
+    ids = g.choice(space, size=n, p=w / w.sum())
+    rows = g.standard_normal((n, d)).astype(np.float32)
+    insp = scoring.inspect(to_dev(ids), space)
+    out = scoring.segment_reduce(to_dev(rows), insp).cpu().numpy()
+    uniq, inv, _, _ = oracle.inspect(ids)
+    ref = np.zeros((n, d), dtype=np.float64)
+    np.add.at(ref, inv, rows.astype(np.float64))
+    assert rel_err(out, ref) < 1e-5
+    assert np.all(out[len(uniq):] == 0)
+    out2 = scoring.segment_reduce(to_dev(rows), insp).cpu().numpy()
+    assert np.array_equal(out, out2)          # fixed summation order
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.float32, 200), (torch.bfloat16, 200), (torch.float32, 37), (torch.bfloat16, 3)])
+def test_gather_rows(dtype, d):
+    from cuke_b200 import scoring
+    g = np.random.Generator(np.random.PCG64(d))
+    table = torch.from_numpy(g.standard_normal((500, d)).astype(np.float32)).cuda().to(dtype).contiguous()
+    ids = torch.from_numpy(g.integers(100, 400, 77)).cuda()
+    out = scoring.gather_rows(table[100:].clone(), ids, first_row=100)
+    assert torch.equal(out, table[ids])
+    n_dev = torch.tensor([10], dtype=torch.int64, device="cuda")
+    out = torch.zeros((77, d), dtype=dtype, device="cuda")
+    scoring.gather_rows(table, ids, n_dev=n_dev, out=out)
+    assert torch.equal(out[:10], table[ids[:10]]) and torch.all(out[10:] == 0)
+
+
+def test_owner_counts():
+    from cuke_b200 import scoring
+    g = np.random.Generator(np.random.PCG64(8))
+    ids = g.integers(0, 1000, 600)
+    insp = scoring.inspect(to_dev(ids), 1000)
+    for world in (1, 2, 4, 8):
+        rpr = (1000 + world - 1) // world
+        counts = scoring.owner_counts(insp, rpr, world).cpu().numpy()
+        ref = np.bincount(np.minimum(np.unique(ids) // rpr, world - 1), minlength=world)
+        assert np.array_equal(counts, ref)
+
+
+def test_legacy_inspector_matches_reference_semantics():
+    from cuke_b200 import scoring
+    g = np.random.Generator(np.random.PCG64(21))
+    for rel_num in (3, 9, 40, 1350):
+        rel = np.sort(g.integers(0, rel_num, 16 * 300))
+        rel[:16] = np.arange(16) % rel_num if rel_num >= 16 else rel[:16]
+        if rel_num >= 16:
+            rel[:16] = np.arange(16)          # a chunk of 16 distinct ids
+        uniq, buf, cnt = scoring.legacy_inspector(to_dev(rel), rel_num)
+        ou, ob, oc = oracle.legacy_inspect(rel, rel_num)
+        assert np.array_equal(uniq.cpu().numpy(), ou)
+        assert np.array_equal(buf.cpu().numpy(), ob)
+        assert np.array_equal(cnt.cpu().numpy(), oc)
+
+
+def test_logistic_loss():
+    from cuke_b200 import scoring
+    g = np.random.Generator(np.random.PCG64(4))
+    pos = torch.from_numpy(g.standard_normal(1000).astype(np.float32) * 3).cuda()
+    neg = torch.from_numpy(g.standard_normal((1000, 7)).astype(np.float32) * 3).cuda()
+    loss, dpos, dneg = scoring.logistic_loss(pos, neg)
+    p64, n64 = pos.double().requires_grad_(True), neg.double().requires_grad_(True)
+    ref = torch.nn.functional.softplus(-p64).sum() + torch.nn.functional.softplus(n64).sum() / 7
+    ref.backward()
+    assert abs(loss.item() - ref.item()) / abs(ref.item()) < 1e-5
+    assert rel_err(dpos.cpu().numpy(), p64.grad.cpu().numpy()) < 1e-5
+    assert rel_err(dneg.cpu().numpy(), n64.grad.cpu().numpy()) < 1e-5
+
+
+# ---- staged scoring: scoring a compact buffer through the inverse map equals scoring the table ------------------
+@pytest.mark.parametrize("model", ["TransE", "DistMult"])
+def test_staged_equals_direct(model):
+    from cuke_b200 import scoring
+    p = make_problem(model, seed=31, ne=5000, d=400, B=256, nn=128, neg_mode="chunk_shared", chunk=128, zipf=True)
+    sc = gpu_scorer(p, 0)
+    h, r, t, neg = gpu_ids(p)
+    pos, negs, _ = sc.forward(h, r, t, neg)
+    ids = scoring.entity_id_list(h, t, neg)
+    insp = scoring.inspect(ids, 5000)
+    staged = scoring.gather_rows(sc.ent, insp.uniq, n_dev=insp.n_unique)
+    B = h.numel()
+    sh, st, sneg = insp.inverse[:B], insp.inverse[B:2 * B], insp.inverse[2 * B:].reshape(neg.shape)
+    pos2, negs2, _ = sc.with_entities(staged).forward(sh.contiguous(), r.to(torch.int32), st.contiguous(), sneg.contiguous())
+    assert torch.equal(pos, pos2) and torch.equal(negs, negs2)
+
+
+# ---- error behaviour ------------------------------------------------------------------------------------------------
+def test_argument_errors():
+    from cuke_b200._lib import KgeError
+    p = make_problem("TransH", d=40, B=32, nn=8, neg_mode="chunk_shared", chunk=16)
+    sc = gpu_scorer(p, 0)
+    h, r, t, neg = gpu_ids(p)
+    with pytest.raises(KgeError) as e:
+        sc.forward(h, r, t, neg)
+    assert e.value.code == -3 and "per-triple" in str(e.value)
+    p = make_problem("TransE", d=40, B=30, nn=8, neg_mode="chunk_shared", chunk=16)
+    p["neg"] = p["neg"][:1]
+    sc = gpu_scorer(p, 0)
+    with pytest.raises((KgeError, ValueError)):
+        sc.forward(*gpu_ids(p))
