@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the KGE scoring hot path: scored triples/sec, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Workload (default c5): TransE and DistMult scored on the same batch, fp32, entity table 4,000,000 x 400 rows
+row-partitioned over the N GPUs, relations 1000 x 400 replicated, 65,536 triples per GPU per step, 1,024 shared
+negatives per 1,024-triple chunk, Zipf(1.1) entity ids.  A step = inspector, staging of distinct rows (NCCL
+all-to-all when N > 1), forward, logistic loss, backward, segmented gradient reduction (and the exchange back to
+the owners) for BOTH scorers.  Scored triples per step per GPU = 2 scorers x (65,536 + 64 x 1,024 x 1,024).
+
+One JSON line is printed by rank 0.  `value` is measured with the step's ids already on the device; `e2e` includes
+the pinned-host -> device copy of the ids and the device -> host read of the losses every step.  `--impl reference`
+times the reference's own CPU path (cuke's generated OpenMP C++, oracle/_ref) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "scored_triples_per_sec_fwd_bwd"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="c5")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); pw.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# reference (CPU) arm and cpu_baseline
+# ---------------------------------------------------------------------------------------------------------
+def cpu_reference_rate(cfg, models, seconds: float, steps: int = 1, warmup: int = 0):
+    """Scored triples/s of cuke's generated OpenMP C++ (forward: the reference's only complete path) on a bounded
+    sample of the workload: the first m triples of chunk 0 against that chunk's shared negatives, flattened the
+    way the reference flattens negatives, over a compact copy of exactly the rows the sample touches."""
+    import torch
+    from cuke_b200 import synth
+    from oracle import oracle
+    kind = "reference" if all(oracle.have_ref(m, omp=True) for m in models) else "port"
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    h, r, t, neg = synth.make_batch(cfg, 0, 0)
+    n_neg = neg.shape[1]
+    d = cfg.dim
+    g = np.random.Generator(np.random.PCG64(synth.BASE_SEED + 5))
+
+    def sample(m):
+        hh, rr, tt = h[:m], r[:m], t[:m]
+        fh, fr, ft = oracle.flatten(hh, rr, tt, neg[:1], "chunk_shared", 0, m)
+        fh, fr, ft = np.concatenate([hh, fh]), np.concatenate([rr, fr]), np.concatenate([tt, ft])
+        ue, inv = np.unique(np.concatenate([fh, ft]), return_inverse=True)
+        E = (g.standard_normal((len(ue), d)) / np.sqrt(d)).astype(np.float32)
+        R = (g.standard_normal((cfg.n_rel, d)) / np.sqrt(d)).astype(np.float32)
+        return E, R, inv[: len(fh)].astype(np.int32), fr.astype(np.int32), inv[len(fh):].astype(np.int32)
+
+    def run(model, E, R, fh, fr, ft):
+        if kind == "reference":
+            tt = torch.from_numpy
+            out = oracle.ref_run(model, tt(E), tt(R), None, tt(fh), tt(fr), tt(ft), omp=True)
+            if model in oracle.VECTOR_MODELS:
+                out = -torch.linalg.vector_norm(out, dim=1)      # the norm the reference leaves to its caller
+            return out
+        return oracle.flat_scores(model, E, R, None, fh, fr, ft)
+
+    # size the sample: probe with 8 triples x n_neg, then scale to the time budget
+    E, R, fh, fr, ft = sample(8)
+    t0 = time.perf_counter(); run(models[0], E, R, fh, fr, ft); probe = time.perf_counter() - t0
+    t0 = time.perf_counter(); run(models[0], E, R, fh, fr, ft); probe = min(probe, time.perf_counter() - t0)
+    per_triple = probe / len(fh)
+    m = int(max(8, min(cfg.chunk, seconds / max(steps + warmup, 1) / max(per_triple, 1e-9) / (n_neg + 1))))
+    E, R, fh, fr, ft = sample(m)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for model in models:
+            run(model, E, R, fh, fr, ft)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    scored = len(fh) * len(models)
+    best = min(times)
+    return {"value": scored / best, "unit": "triples/s", "cores": cores if kind == "reference" else 1, "kind": kind,
+            "sample": f"forward only (the reference has no aggregated backward): {m} triples of chunk 0 x {n_neg} shared "
+                      f"negatives + positives, flattened ({len(fh)} triples) x {len(models)} scorers, compact row table, "
+                      f"best of {len(times)}", "ms_per_step": statistics.mean(times) * 1e3, "scored_per_step": scored}
+
+
+def reference_arm(args, cfg, models):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    res = cpu_reference_rate(cfg, models, seconds=max(20.0, 4.0 * (args.steps + args.warmup)), steps=args.steps, warmup=args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": res["scored_per_step"] / (res["ms_per_step"] * 1e-3),
+            "unit": "triples/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, models, args.gpus),
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}}
+    line["cpu_baseline"]["value"] = line["value"]
+    line["e2e"] = {"value": line["value"], "unit": "triples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, models, n_gpus):
+    return {"workload": f"{cfg.name}: {'+'.join(models)} fwd+bwd fp32, entities {cfg.n_ent}x{cfg.dim} row-partitioned over "
+                        f"{n_gpus} GPU(s), relations {cfg.n_rel}x{cfg.dim}, {cfg.batch} triples/GPU, {cfg.n_neg} shared negatives "
+                        f"per {cfg.chunk}-triple chunk, Zipf(1.1) entity ids",
+            "scorers": models, "triples_per_gpu": cfg.batch, "neg_mode": cfg.neg_mode, "n_neg": cfg.n_neg, "chunk": cfg.chunk,
+            "dim": cfg.dim, "n_ent": cfg.n_ent, "n_rel": cfg.n_rel, "parallelism": f"dp{n_gpus}+row-sharded-entities",
+            "l2": "inputs larger than L2 (6.4 GB table, 76 MB staged rows, 269 MB scores per scorer); no flush"}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------------
+def main():
+    args = parse()
+    from cuke_b200 import synth
+    if args.config not in ("c4", "c5"):
+        raise SystemExit("bench.py times the chunk-shared configurations (c5 default, c4 ComplEx); the others are parity cases")
+    cfg = synth.CONFIGS[args.config]
+    models = ["TransE", "DistMult"] if cfg.name == "c5" else ["ComplEx"]
+    if args.impl == "reference":
+        reference_arm(args, cfg, models)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from cuke_b200 import _lib, scoring
+    from cuke_b200.pipeline import KgeStep
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    _lib.lib()          # fail loudly if the CUDA library is missing
+
+    d = synth.row_floats(cfg, models[0])
+    rows_per_rank = (cfg.n_ent + world - 1) // world
+    my_rows = max(0, min(cfg.n_ent, (rank + 1) * rows_per_rank) - rank * rows_per_rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(synth.BASE_SEED + 1000 * cfg.cid + 1 + 100000 * rank)
+    ent_local = torch.randn((my_rows, d), generator=gen, device=dev, dtype=torch.float32) * (1.0 / np.sqrt(d))
+    rel = {}
+    for mi, m in enumerate(models):
+        g = np.random.Generator(np.random.PCG64(synth.BASE_SEED + 1000 * cfg.cid + 2 + mi))
+        rel[m] = torch.from_numpy((g.standard_normal((cfg.n_rel, d)) / np.sqrt(d)).astype(np.float32)).to(dev)
+    stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group)
+
+    nb = 4
+    host = []
+    for s in range(nb):
+        h, r, t, neg = synth.make_batch(cfg, s, rank)
+        host.append(tuple(torch.from_numpy(x).pin_memory() for x in (h, r, t, neg)))
+    devb = [tuple(x.to(dev) for x in b) for b in host]
+    h2d_bytes = sum(x.numel() * x.element_size() for x in host[0])
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=group)
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        tns = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tns, op=dist.ReduceOp.MAX, group=group)
+        return float(tns.item())
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        sync_all()
+        return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    scored_per_gpu = synth.scored_triples(cfg) * len(models)
+
+    # ---- value: ids resident on the device ------------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.lib().kge_launch_count()
+    ms_step = timed(lambda i: stepper.step(*devb[i % nb]), args.steps, max(args.warmup, 3))
+    launches = (_lib.lib().kge_launch_count() - launches0) // (args.steps + max(args.warmup, 3))
+    clocks = sampler.stop() if rank == 0 else None
+    value = scored_per_gpu * world / (ms_step * 1e-3)
+
+    ms_fwd = timed(lambda i: stepper.step(*devb[i % nb], backward=False), max(3, args.steps // 2), 2)
+
+    # ---- e2e: host ids in, losses out, every step --------------------------------------------------------------
+    sink = []
+
+    def e2e_step(i):
+        b = tuple(x.to(dev, non_blocking=True) for x in host[i % nb])
+        out = stepper.step(*b)
+        res = torch.cat([out.loss[m] for m in models]).cpu()       # device -> host read of the step's result
+        sink.append(float(res.sum()))
+
+    ms_e2e = timed(e2e_step, args.steps, 2)
+    e2e = {"value": scored_per_gpu * world / (ms_e2e * 1e-3), "unit": "triples/s", "h2d_bytes_per_step": h2d_bytes,
+           "d2h_bytes_per_step": 4 * len(models), "ms_per_step": ms_e2e}
+
+    # ---- roofline of the dominant kernel, timed live ------------------------------------------------------------
+    hbm_gbs, _, peak_kind = peaks()
+    roof = None
+    if rank == 0:
+        out = stepper.step(*devb[0])
+        U = int(out.n_staged.item())
+        h, r, t, neg = devb[0]
+        insp = scoring.inspect(scoring.entity_id_list(h, t, neg), cfg.n_ent)
+        if world == 1:
+            staged = scoring.gather_rows(ent_local, insp.uniq, n_dev=insp.n_unique)
+        else:
+            staged = torch.randn((insp.n, d), device=dev) * (1.0 / np.sqrt(d))
+        B = h.numel()
+        sc = scoring.Scorer(models[0], staged, rel[models[0]], None, cfg.neg_mode, cfg.n_neg_head, cfg.chunk)
+        sh, st, sneg = insp.inverse[:B], insp.inverse[B:2 * B], insp.inverse[2 * B:].view(neg.shape)
+        r32 = r.to(torch.int32)
+        for _ in range(3):
+            sc.forward(sh, r32, st, sneg)
+        torch.cuda.synchronize()
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            sc.forward(sh, r32, st, sneg)
+        e1.record()
+        torch.cuda.synchronize()
+        t_k = e0.elapsed_time(e1) * 1e-3 / reps
+        pairs = (B // cfg.chunk) * cfg.chunk * cfg.n_neg
+        flop_per = 3 if models[0] == "TransE" else 2
+        flops = flop_per * d * (pairs + B)
+        fma_peak = scoring.fma_peak_tflops(dev)
+        U_r = int(torch.unique(r).numel())
+        bytes_alg = U * d * 4 + U_r * d * 4 + 4 * (3 * B + neg.numel()) + 4 * (pairs + B)
+        roof = {"kernel": f"pair_fwd_kernel<{models[0]}> (+ positives kernel, <2% of the time)", "bound": "fp32_fma",
+                "achieved": flops / t_k / 1e12, "peak": fma_peak, "unit": "TFLOP/s", "frac": flops / t_k / 1e12 / fma_peak,
+                "peak_source": "kge_probe_fma microbenchmark on this GPU (2 flop per FMA)",
+                "pipe_slot_frac": (2 * d * (pairs + B) if models[0] == "TransE" else d * (pairs + B)) / t_k / (fma_peak * 1e12 / 2),
+                "traffic": None, "ms": t_k * 1e3,
+                "hbm": {"bound": "hbm", "achieved": bytes_alg / t_k / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                        "frac": bytes_alg / t_k / 1e9 / hbm_gbs, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
+                        "bytes_alg": bytes_alg}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            res = cpu_reference_rate(cfg, models, seconds=args.cpu_seconds, steps=2, warmup=1)
+            cpu = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as e:          # the baseline is reported, never required
+            cpu = {"value": None, "unit": "triples/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, models, world),
+                "value_fwd_only": scored_per_gpu * world / (ms_fwd * 1e-3), "ms_per_step_fwd_only": ms_fwd,
+                "e2e": e2e, "gpu_launches": int(launches) * args.steps, "gpu_launches_per_step": int(launches),
+                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier(group=group)
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,12 +52,15 @@ _PP, _PT, _PG = C.POINTER(KgeProblem), C.POINTER(KgeTensors), C.POINTER(KgeGrads
 SIGNATURES = {
     "kge_version": (C.c_int, []),
     "kge_last_error": (C.c_char_p, []),
+    "kge_launch_count": (C.c_longlong, []),
     "kge_check": (C.c_int, [_vp, C.POINTER(C.c_int32)]),
     "kge_ref_forward": (C.c_int, [_PP, _PT, _vp, _vp]),
     "kge_inspect_workspace_bytes": (_sz, [_i64]),
     "kge_inspect": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
     "kge_legacy_inspect": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "kge_gather_rows": (C.c_int, [_vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "kge_scatter_rows": (C.c_int, [_vp, _i32, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "kge_probe_fma": (C.c_int, [_vp, _i32, _i32, C.POINTER(C.c_double), _vp]),
     "kge_segment_reduce_workspace_bytes": (_sz, [_i64, _i32]),
     "kge_segment_reduce": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _vp]),
     "kge_score_workspace_bytes": (_sz, [_PP, _i32]),

@@ -2,6 +2,7 @@
 // Declarations and their reference counterparts are in include/kge_b200.h.
 #include <stdarg.h>
 #include <string.h>
+#include <atomic>
 #include "common.cuh"
 
 namespace kge {
@@ -21,6 +22,9 @@ int cuda_status(cudaError_t e, const char* what) {
     return (int)e;
 }
 
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 __device__ int32_t g_error_word = 0;
 int32_t* device_error_word() {
     int32_t* p = nullptr;
@@ -39,6 +43,9 @@ int launch_segment_reduce(const float* rows, int dim, long long n, const int* pe
                           const long long* n_unique, float* out, long long n_out, void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_gather_rows(const void* table, int dtype, int dim, const long long* ids, long long n, const long long* n_dev,
                        long long first_row, void* out, cudaStream_t s);
+int launch_scatter_rows(const float* rows, int dim, const long long* ids, long long n, const long long* n_dev,
+                        long long first_row, float* out, cudaStream_t s);
+int launch_fma_probe(float* out, int blocks, int iters, cudaStream_t s);
 int launch_owner_counts(const long long* uniq, const long long* n_unique, long long n_max, long long rows_per_rank,
                         int world, long long* counts, cudaStream_t s);
 int launch_legacy_inspect(const long long* rel, long long n, long long rel_num, long long* uniq, long long* buf,
@@ -55,6 +62,12 @@ int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos
     do {                                                                               \
         if ((ptr) == nullptr) { set_error("%s: %s is NULL", fn, name); return KGE_E_NULL; } \
         if (!aligned16(ptr)) { set_error("%s: %s is not 16-byte aligned", fn, name); return KGE_E_ALIGN; } \
+    } while (0)
+// id arrays are read element-wise: natural alignment is enough (slices of an inverse map start anywhere)
+#define KGE_REQUIRE_IDS(ptr, name, bits)                                               \
+    do {                                                                               \
+        if ((ptr) == nullptr) { set_error("%s: %s is NULL", fn, name); return KGE_E_NULL; } \
+        if (reinterpret_cast<uintptr_t>(ptr) & ((bits) / 8 - 1)) { set_error("%s: %s is not aligned to its element size", fn, name); return KGE_E_ALIGN; } \
     } while (0)
 #define KGE_OPTIONAL_PTR(ptr, name)                                                    \
     do {                                                                               \
@@ -78,7 +91,7 @@ static int check_problem(const char* fn, const kge_problem* p, const kge_tensors
     KGE_REQUIRE_PTR(t->ent, "ent");
     if (uses_rel(p->model)) KGE_REQUIRE_PTR(t->rel, "rel");
     if (uses_rel2(p->model)) KGE_REQUIRE_PTR(t->rel2, "rel2");
-    KGE_REQUIRE_PTR(t->h, "h"); KGE_REQUIRE_PTR(t->r, "r"); KGE_REQUIRE_PTR(t->t, "t");
+    KGE_REQUIRE_IDS(t->h, "h", p->id_bits); KGE_REQUIRE_IDS(t->r, "r", p->id_bits); KGE_REQUIRE_IDS(t->t, "t", p->id_bits);
     if (!scored) {
         if (p->neg_mode != KGE_NEG_NONE) { set_error("%s: neg_mode must be KGE_NEG_NONE (flatten negatives into the batch)", fn); return KGE_E_UNSUPPORTED; }
         return 0;
@@ -87,7 +100,7 @@ static int check_problem(const char* fn, const kge_problem* p, const kge_tensors
     if (p->neg_mode != KGE_NEG_NONE) {
         if (p->n_neg <= 0) { set_error("%s: n_neg must be > 0 with negatives", fn); return KGE_E_SHAPE; }
         if (p->n_neg_head < 0 || p->n_neg_head > p->n_neg) { set_error("%s: n_neg_head %d outside [0, n_neg]", fn, p->n_neg_head); return KGE_E_SHAPE; }
-        KGE_REQUIRE_PTR(t->neg, "neg");
+        KGE_REQUIRE_IDS(t->neg, "neg", p->id_bits);
     }
     if (p->neg_mode == KGE_NEG_CHUNK_SHARED) {
         if (p->chunk <= 0 || p->batch % p->chunk != 0) { set_error("%s: batch %lld is not a multiple of chunk %d", fn, (long long)p->batch, p->chunk); return KGE_E_SHAPE; }
@@ -128,6 +141,7 @@ extern "C" {
 
 int kge_version(void) { return KGE_ABI_VERSION; }
 const char* kge_last_error(void) { return g_err; }
+long long kge_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int kge_check(kge_stream_t stream, int32_t* flags_out) {
     const char* fn = "kge_check";
@@ -186,6 +200,24 @@ int kge_gather_rows(const void* table, int32_t dtype, int32_t dim, const int64_t
     KGE_REQUIRE_PTR(table, "table"); KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
     return launch_gather_rows(table, dtype, dim, (const long long*)ids, n, (const long long*)n_dev, first_row, out,
                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_scatter_rows(const float* rows, int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev,
+                     int64_t first_row, float* out, kge_stream_t stream) {
+    const char* fn = "kge_scatter_rows";
+    if (n <= 0) return 0;
+    if (dim <= 0) { set_error("%s: dim must be positive", fn); return KGE_E_SHAPE; }
+    KGE_REQUIRE_PTR(rows, "rows"); KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
+    return launch_scatter_rows(rows, dim, (const long long*)ids, n, (const long long*)n_dev, first_row, out,
+                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_probe_fma(float* out, int32_t blocks, int32_t iters, double* flops_out, kge_stream_t stream) {
+    const char* fn = "kge_probe_fma";
+    KGE_REQUIRE_PTR(out, "out");
+    if (blocks <= 0 || iters <= 0) { set_error("%s: blocks and iters must be positive", fn); return KGE_E_SHAPE; }
+    if (flops_out) *flops_out = 2.0 * 8 * 16 * (double)iters * 256.0 * (double)blocks;
+    return launch_fma_probe(out, blocks, iters, reinterpret_cast<cudaStream_t>(stream));
 }
 
 size_t kge_segment_reduce_workspace_bytes(int64_t n, int32_t dim) { return segment_reduce_workspace_bytes(n < 1 ? 1 : n, dim); }

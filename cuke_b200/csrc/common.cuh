@@ -14,12 +14,14 @@ constexpr unsigned kFull = 0xffffffffu;
 // ---- host-side error plumbing -------------------------------------------------------------------
 void set_error(const char* fmt, ...);          // thread-local message (capi.cu)
 int cuda_status(cudaError_t e, const char* what);  // 0 or positive cudaError_t, records message
-int32_t* device_error_word();                  // per-device error word (lazily created, capi.cu)
+int32_t* device_error_word();                  // per-device error word (capi.cu)
+void note_launch();                            // counts kernel launches issued by this library (capi.cu)
 
 #define KGE_LAUNCH_CHECK(what)                                   \
     do {                                                         \
         cudaError_t e__ = cudaGetLastError();                    \
         if (e__ != cudaSuccess) return kge::cuda_status(e__, what); \
+        kge::note_launch();                                      \
     } while (0)
 
 // ---- element access --------------------------------------------------------------------------------

@@ -262,6 +262,36 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const V* table, long l
     for (long long k = lane; k < row_units; k += 32) dst[k] = __ldg(src + k);
 }
 
+// out[ids[i] - first_row][:] = rows[i][:] for i < min(n, *n_dev): places compact rows into a dense table.
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const float* rows, int dim, const long long* ids, long long n,
+                                                           const long long* n_dev, long long first_row, float* out) {
+    const int lane = threadIdx.x & 31;
+    const long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long cnt = n_dev ? min(n, *n_dev) : n;
+    if (i >= cnt) return;
+    const float* src = rows + i * dim;
+    float* dst = out + (ids[i] - first_row) * dim;
+    for (int k = lane; k < dim; k += 32) dst[k] = src[k];
+}
+
+// Measurement aid: dependent-free FMA chains, 8 accumulators per thread; reports nothing but keeps the result live.
+__global__ void __launch_bounds__(256) fma_probe_kernel(float* out, int iters) {
+    float a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = threadIdx.x * 1e-3f + i;
+    const float x = 1.0000001f, y = 1e-7f;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = fmaf(a[i], x, y);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += a[i];
+    if (s == 12345.678f) out[0] = s;
+}
+
 __global__ void owner_counts_kernel(const long long* uniq, const long long* n_unique, long long n_max,
                                     long long rows_per_rank, int world, long long* counts) {
     const int g = blockIdx.x * blockDim.x + threadIdx.x;
@@ -479,6 +509,21 @@ int launch_gather_rows(const void* table, int dtype, int dim, const long long* i
     else
         gather_rows_kernel<unsigned short><<<blocks, wpb * 32, 0, s>>>(static_cast<const unsigned short*>(table), (long long)(row_bytes / 2), ids, n, n_dev, first_row, static_cast<unsigned short*>(out));
     KGE_LAUNCH_CHECK("gather_rows_kernel");
+    return 0;
+}
+
+int launch_scatter_rows(const float* rows, int dim, const long long* ids, long long n, const long long* n_dev,
+                        long long first_row, float* out, cudaStream_t s) {
+    if (n <= 0) return 0;
+    const int wpb = 8;
+    scatter_rows_kernel<<<(unsigned)((n + wpb - 1) / wpb), wpb * 32, 0, s>>>(rows, dim, ids, n, n_dev, first_row, out);
+    KGE_LAUNCH_CHECK("scatter_rows_kernel");
+    return 0;
+}
+
+int launch_fma_probe(float* out, int blocks, int iters, cudaStream_t s) {
+    fma_probe_kernel<<<blocks, 256, 0, s>>>(out, iters);
+    KGE_LAUNCH_CHECK("fma_probe_kernel");
     return 0;
 }
 

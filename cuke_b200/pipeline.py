@@ -1,0 +1,142 @@
+"""One forward+backward step of the KGE scorers over a (possibly row-partitioned) entity table.
+
+Inspector-executor per step and rank:
+  1. inspector over the batch's entity ids [h | t | neg]  -> sorted distinct ids, inverse map, segments
+  2. stage every distinct row once into a compact buffer:
+        1 GPU : gather from the local table
+        N GPUs: the table is row-partitioned (owner = id // rows_per_rank); distinct ids are already sorted, so
+                each owner's ids are one contiguous range -> all-to-all of ids, owners gather the requested
+                rows, all-to-all of rows (NCCL over NVLink); everything lands in local HBM before it is read
+  3. score forward, loss, score backward against the compact buffer through the inverse map
+  4. segmented reduction: per-slot gradient rows -> one row per distinct id (fixed order, no atomics)
+  5. N GPUs: gradient rows travel back to their owners (all-to-all), who sum the contributions of all ranks
+     with the same inspector + segmented reduction (the "reduce-scatter"); relation gradients are all-reduced.
+
+The reference has no counterpart of steps 2 and 5 (single GPU, `cuda:0`, apps/kge/data/data_init.py:6-15) and
+only the relation half of step 1 (apps/kge/kge.py:249-271).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from . import scoring
+from .scoring import Inspection, Scorer
+
+
+class RowExchange:
+    """The row-partition protocol of steps 2 and 5, independent of where the kernels run.
+
+    `ops` supplies inspect / owner_counts / gather_rows / segment_reduce with the signatures of
+    cuke_b200.scoring (the CUDA kernels); tests drive the same protocol on CPU ranks over gloo with a
+    numpy stand-in, which is how the multi-rank bookkeeping is checked without GPUs."""
+
+    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None, ops=scoring):
+        self.ent_local, self.n_ent, self.rank, self.world, self.group, self.ops = ent_local, int(n_ent), rank, world, group, ops
+        self.rows_per_rank = (self.n_ent + world - 1) // world
+        self.dim = ent_local.shape[1]
+        self.need = self.serve = None
+        self.req_ids = None
+
+    def stage(self, insp: Inspection) -> torch.Tensor:
+        """Compact buffer holding row uniq[u] of the global table at position u (u < U)."""
+        import torch.distributed as dist
+        dev = self.ent_local.device
+        counts = self.ops.owner_counts(insp, self.rows_per_rank, self.world)       # ids I need from each owner
+        wanted = torch.empty_like(counts)                                           # ids each rank needs from me
+        dist.all_to_all_single(wanted, counts, group=self.group)
+        both = torch.stack((counts, wanted)).cpu()                                  # the one host read: split sizes
+        self.need, self.serve = both[0].tolist(), both[1].tolist()
+        U, S = sum(self.need), sum(self.serve)
+        self.req_ids = torch.empty(max(S, 1), dtype=torch.int64, device=dev)
+        dist.all_to_all_single(self.req_ids[:S], insp.uniq[:U], output_split_sizes=self.serve,
+                               input_split_sizes=self.need, group=self.group)
+        if S:
+            send_rows = self.ops.gather_rows(self.ent_local, self.req_ids[:S], first_row=self.rank * self.rows_per_rank)
+        else:
+            send_rows = torch.empty((0, self.dim), dtype=self.ent_local.dtype, device=dev)
+        staged = torch.empty((max(U, 1), self.dim), dtype=self.ent_local.dtype, device=dev)
+        dist.all_to_all_single(staged[:U], send_rows, output_split_sizes=self.need, input_split_sizes=self.serve,
+                               group=self.group)
+        return staged
+
+    def return_grads(self, grad_rows: torch.Tensor):
+        """grad_rows[u] belongs to uniq[u] of the last stage().  Returns (ids, n_rows, rows): one summed gradient
+        row per distinct OWNED id that any rank touched; ids int64 sorted, first n_rows entries valid."""
+        import torch.distributed as dist
+        U, S = sum(self.need), sum(self.serve)
+        recv = torch.empty((max(S, 1), self.dim), dtype=torch.float32, device=grad_rows.device)
+        dist.all_to_all_single(recv[:S], grad_rows[:U].contiguous(), output_split_sizes=self.serve,
+                               input_split_sizes=self.need, group=self.group)
+        if S == 0:
+            return self.req_ids[:0], torch.zeros(1, dtype=torch.int64, device=grad_rows.device), recv[:0]
+        oinsp = self.ops.inspect(self.req_ids[:S], self.n_ent)
+        return oinsp.uniq, oinsp.n_unique, self.ops.segment_reduce(recv[:S], oinsp)
+
+
+@dataclass
+class StepOutput:
+    loss: Dict[str, torch.Tensor] = field(default_factory=dict)        # model -> (1,) fp32
+    pos: Dict[str, torch.Tensor] = field(default_factory=dict)         # model -> (B,) fp32
+    ent_ids: Optional[torch.Tensor] = None       # (n,) int64: ids of the entity gradient rows (first n_ent_rows valid)
+    n_ent_rows: Optional[torch.Tensor] = None    # (1,) int64 device
+    ent_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n, dim) fp32 rows aligned with ent_ids
+    rel_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n_rel, dim) dense fp32
+    n_staged: Optional[torch.Tensor] = None      # (1,) distinct entity rows this rank touched
+
+
+class KgeStep:
+    """models: scorers sharing one entity table; rel: model -> relation table (n_rel, dim).
+
+    ent_local holds rows [rank * rows_per_rank, ...) of the global (n_ent, dim) table (the whole table when
+    world == 1).  `group` is a torch.distributed process group (NCCL) when world > 1."""
+
+    def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
+                 neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None):
+        self.models, self.ent_local, self.rel = list(models), ent_local, rel
+        self.n_ent, self.rank, self.world, self.group = int(n_ent), int(rank), int(world), group
+        self.neg_mode, self.n_neg_head, self.chunk = neg_mode, n_neg_head, chunk
+        self.dim = ent_local.shape[1]
+        self.n_rel = {m: rel[m].shape[0] for m in self.models}
+        for m in self.models:
+            if m in ("TransH", "TransR", "RESCAL"):
+                raise NotImplementedError("KgeStep covers the vector-relation scorers (TransE, DistMult, ComplEx, TransF)")
+        self.exchange = RowExchange(ent_local, n_ent, rank, world, group) if world > 1 else None
+
+    def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True) -> StepOutput:
+        import torch.distributed as dist
+        out = StepOutput()
+        B = h.numel()
+        insp = scoring.inspect(scoring.entity_id_list(h, t, neg), self.n_ent)
+        out.n_staged = insp.n_unique
+        if self.exchange is None:
+            staged = scoring.gather_rows(self.ent_local, insp.uniq, n_dev=insp.n_unique)
+        else:
+            staged = self.exchange.stage(insp)
+        sh, st = insp.inverse[:B], insp.inverse[B:2 * B]
+        sneg = insp.inverse[2 * B:].view(neg.shape)
+        r32 = r.to(torch.int32)
+        rinsp = None
+        for m in self.models:
+            sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk)
+            pos, negs, _ = sc.forward(sh, r32, st, sneg)
+            loss, dpos, dneg = scoring.logistic_loss(pos, negs)
+            out.loss[m], out.pos[m] = loss, pos
+            if not backward:
+                continue
+            sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
+            grad_rows = scoring.segment_reduce(sg.ent_slots, insp)            # aligned with insp.uniq
+            if rinsp is None:
+                rinsp = scoring.inspect(r32, self.n_rel[m])
+            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp)
+            dense_rel = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
+            scoring.scatter_rows(rel_rows, rinsp.uniq, dense_rel, n_dev=rinsp.n_unique)
+            if self.exchange is None:
+                out.ent_ids, out.n_ent_rows, out.ent_grad[m] = insp.uniq, insp.n_unique, grad_rows
+            else:
+                out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
+                dist.all_reduce(dense_rel, group=self.group)
+            out.rel_grad[m] = dense_rel
+        return out

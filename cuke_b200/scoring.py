@@ -119,6 +119,35 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor, n_dev: Optional[torch.Te
     return out
 
 
+def scatter_rows(rows: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, n_dev: Optional[torch.Tensor] = None,
+                 first_row: int = 0) -> torch.Tensor:
+    """out[ids[i] - first_row] = rows[i] for i < min(len(ids), *n_dev); ids distinct."""
+    _need_cuda(rows, ids, out, n_dev)
+    check(_lib.lib().kge_scatter_rows(_ptr(rows), rows.shape[1], _ptr(ids), min(ids.numel(), rows.shape[0]), _ptr(n_dev),
+                                      int(first_row), _ptr(out), _stream()))
+    return out
+
+
+def fma_peak_tflops(device=None, iters: int = 4096) -> float:
+    """Attainable fp32 FMA rate of the current GPU in TFLOP/s (2 flops per FMA), from the library's probe kernel."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    out = torch.zeros(4, dtype=torch.float32, device=dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    flops = C.c_double(0.0)
+    L = _lib.lib()
+    check(L.kge_probe_fma(_ptr(out), sms * 8, 64, C.byref(flops), _stream()))
+    torch.cuda.synchronize()
+    best = 0.0
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(L.kge_probe_fma(_ptr(out), sms * 8, iters, C.byref(flops), _stream()))
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
 def segment_reduce(rows: torch.Tensor, insp: Inspection, out: Optional[torch.Tensor] = None,
                    n_out: Optional[int] = None) -> torch.Tensor:
     """One fp32 row per distinct id: out[u] = sum of rows[slot] over the slots holding uniq[u] (fixed order)."""

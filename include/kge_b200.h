@@ -8,7 +8,8 @@
  *
  * Conventions
  *   - C linkage, POD structs, raw DEVICE pointers (e.g. torch `tensor.data_ptr()`), row-major contiguous
- *     tensors, every base pointer 16-byte aligned.  Pointers are never retained after a call returns.
+ *     tensors, every base pointer 16-byte aligned (id arrays: aligned to their element size).  Pointers are
+ *     never retained after a call returns.
  *   - The library never allocates or frees device memory that the caller can see: outputs and scratch
  *     ("workspace") are caller-provided; `*_workspace_bytes` says how much is needed.
  *   - Every launch goes to the `cudaStream_t` passed in; calls are asynchronous with respect to the host
@@ -122,6 +123,7 @@ typedef struct kge_grads {
 
 KGE_API int kge_version(void);                 /* KGE_ABI_VERSION of the loaded library */
 KGE_API const char* kge_last_error(void);      /* thread-local message for the last non-zero return */
+KGE_API long long kge_launch_count(void);      /* kernels launched by this library in this process so far */
 
 /* Reads (and clears) the device error word of the current device: 0 = clean.  Synchronises `stream`.
  * Bit 2: a bounded wait inside a kernel ran out and the kernel gave up (its outputs are then invalid). */
@@ -171,6 +173,12 @@ KGE_API int kge_legacy_inspect(const int64_t* rel, int64_t n, int64_t rel_num,
 KGE_API int kge_gather_rows(const void* table, int32_t dtype, int32_t dim, const int64_t* ids, int64_t n,
                     const int64_t* n_dev, int64_t first_row, void* out, kge_stream_t stream);
 
+/* Inverse of kge_gather_rows for fp32 rows: out[ids[i] - first_row][:] = rows[i][:] for i < min(n, *n_dev).
+ * ids must be distinct (the inspector's `uniq`); used to place compact gradient rows into a dense table.
+ * No counterpart in the reference, which never aggregates gradients (apps/kge/kge.py:393-515). */
+KGE_API int kge_scatter_rows(const float* rows, int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev,
+                             int64_t first_row, float* out, kge_stream_t stream);
+
 /* Segmented sum: out[u][:] = sum over sorted positions p in [seg[u], seg[u+1]) of rows[perm[p]][:],
  * added in ascending p (deterministic, no atomics).  rows (n, dim) fp32; out (n_out, dim) fp32 where
  * n_out >= U; rows u in [U, n_out) are zero-filled.  The backward "scatter-add" of per-slot gradient rows
@@ -213,6 +221,12 @@ KGE_API int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg,
  * counts (world,) int64 device. */
 KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank,
                      int32_t world, int64_t* counts, kge_stream_t stream);
+
+/* ---- measurement aid -----------------------------------------------------------------------------------
+ * Launches `blocks` x 256 threads of independent fp32 FMA chains (iters x 128 FMAs per thread) and returns the
+ * flop count (2 per FMA) in *flops_out; time it with CUDA events to get this GPU's attainable fp32 FMA rate,
+ * the roofline denominator of the CUDA-core contraction kernels.  No counterpart in the reference. */
+KGE_API int kge_probe_fma(float* out, int32_t blocks, int32_t iters, double* flops_out, kge_stream_t stream);
 
 #ifdef __cplusplus
 }
