@@ -43,6 +43,10 @@ def parse():
     ap.add_argument("--config", default="c5")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="profiling aid: run forward+backward of the scorers 3 times on a reduced case (--chunks chunks, "
+                         "entity table scaled down to fit a few GB) and exit; meant to be run under ncu -k <kernel>")
+    ap.add_argument("--chunks", type=int, default=32)
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
     return ap.parse_args()
 
@@ -218,6 +222,8 @@ def main():
         group = dist.group.WORLD
     _lib.lib()          # fail loudly if the CUDA library is missing
 
+    if args.kernel_only:
+        cfg = cfg.scaled(ent=0.1, batch=args.chunks * cfg.chunk / cfg.batch)
     d = synth.row_floats(cfg, models[0])
     rows_per_rank = (cfg.n_ent + world - 1) // world
     my_rows = max(0, min(cfg.n_ent, (rank + 1) * rows_per_rank) - rank * rows_per_rank)
@@ -264,6 +270,12 @@ def main():
         return max_over_ranks(e0.elapsed_time(e1)) / steps
 
     scored_per_gpu = synth.scored_triples(cfg) * len(models)
+    if args.kernel_only:
+        for i in range(3):
+            stepper.step(*devb[i % nb])
+        torch.cuda.synchronize()
+        print(json.dumps({"kernel_only": True, "chunks": args.chunks, "n_ent": cfg.n_ent, "batch": cfg.batch}))
+        return
 
     # ---- value: ids resident on the device ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)

@@ -103,7 +103,7 @@ struct DenseRowsDirect {
 
 // ---- forward -----------------------------------------------------------------------------------------
 template <int MODEL, typename T, typename I, bool VEC, bool VECOUT>
-__global__ void __launch_bounds__(256) pair_fwd_kernel(ScoreArgs a, int head) {
+__global__ void __launch_bounds__(256, 2) pair_fwd_kernel(ScoreArgs a, int head) {
     __shared__ __align__(16) TileSmem sm;
     constexpr int OP = PairOp<MODEL>::value;
     const int tid = threadIdx.x;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(256) pair_fwd_kernel(ScoreArgs a, int head) {
 
 // ---- backward: anchor gradients  GA[i][:] = sum_j W_ij x_j  (DIST: rowsum_i a_i - that) -------------------
 template <bool DIST, typename T, typename I, bool VEC, bool VECW>
-__global__ void __launch_bounds__(256) pair_bwd_anchor_kernel(ScoreArgs a, const float* anchors, float* ga) {
+__global__ void __launch_bounds__(256, 2) pair_bwd_anchor_kernel(ScoreArgs a, const float* anchors, float* ga) {
     __shared__ __align__(16) TileSmem sm;
     __shared__ float rowsum[TG_BM];
     const int tid = threadIdx.x;
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(256) pair_bwd_anchor_kernel(ScoreArgs a, const
 
 // ---- backward: negative-row gradients  GX[j][:] = sum_i W_ij a_i  (DIST: colsum_j x_j - that) ----------------
 template <bool DIST, typename T, typename I, bool VEC, bool VECW>
-__global__ void __launch_bounds__(256) pair_bwd_neg_kernel(ScoreArgs a, const float* anchors) {
+__global__ void __launch_bounds__(256, 2) pair_bwd_neg_kernel(ScoreArgs a, const float* anchors) {
     __shared__ __align__(16) TileSmem sm;
     __shared__ float colpart[8][TG_BM];
     const int tid = threadIdx.x;
