@@ -63,6 +63,7 @@ SIGNATURES = {
     "kge_probe_fma": (C.c_int, [_vp, _i32, _i32, C.POINTER(C.c_double), _vp]),
     "kge_segment_reduce_workspace_bytes": (_sz, [_i64, _i32]),
     "kge_segment_reduce": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "kge_segment_reduce_static": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),
     "kge_score_workspace_bytes": (_sz, [_PP, _i32]),
     "kge_score_forward": (C.c_int, [_PP, _PT, _vp, _vp, _vp, _sz, _vp]),
     "kge_score_backward": (C.c_int, [_PP, _PT, _vp, _vp, _vp, _vp, _PG, _vp, _sz, _vp]),

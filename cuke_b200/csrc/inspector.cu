@@ -555,4 +555,75 @@ int launch_logistic_loss(const float* pos, long long n_pos, const float* neg, lo
     return 0;
 }
 
+
+// ---- segmented reduction with library-owned scratch -----------------------------------------------------------
+// Scratch of kge_segment_reduce_static: two halves (lead / trail partial rows), resident on every GPU that loads
+// the library for the life of the process.
+constexpr long long kStaticHalfFloats = 1LL << 20;            // 4 MiB per half, 8 MiB in total
+static __device__ __align__(256) float g_segred_static[2 * kStaticHalfFloats];
+
+// In host code `g_segred_static` is only a handle for the runtime, not a device address: the address the
+// kernels need is looked up once per device (with that device current) and remembered.
+static float* g_static_base[128] = {nullptr};
+
+static int static_scratch(float** base) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "kge_segment_reduce_static: cudaGetDevice");
+    if (dev < 0 || dev >= 128) { set_error("kge_segment_reduce_static: device ordinal %d outside [0, 128)", dev); return KGE_E_DEVICE; }
+    if (g_static_base[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_segred_static);
+        if (e != cudaSuccess) return cuda_status(e, "kge_segment_reduce_static: cudaGetSymbolAddress");
+        g_static_base[dev] = p;
+    }
+    *base = g_static_base[dev];
+    return 0;
+}
+
 }  // namespace kge
+
+extern "C" int kge_segment_reduce_static(const float* rows, int32_t dim, int64_t n, const int32_t* perm, const int32_t* seg,
+                                         const int64_t* n_unique, float* out, int64_t n_out, kge_stream_t stream) {
+    using namespace kge;
+    const char* fn = "kge_segment_reduce_static";
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (n < 0 || n > 2147483647LL || n_out < 0) { set_error("%s: bad sizes", fn); return KGE_E_RANGE; }
+    if (dim <= 0 || dim > 1024) { set_error("%s: dim %d outside [1, 1024]", fn, dim); return KGE_E_UNSUPPORTED; }
+    const long long nwin = (n + 31) / 32;
+    if (nwin * dim > kStaticHalfFloats) {
+        set_error("%s: ceil(n/32) * dim = %lld exceeds the built-in scratch of %lld floats per half "
+                  "(n = %lld, dim = %d); use kge_segment_reduce with a caller-provided workspace",
+                  fn, nwin * dim, kStaticHalfFloats, (long long)n, dim);
+        return KGE_E_RANGE;
+    }
+    const void* ptrs[] = {n_out > 0 ? out : (float*)16, n > 0 ? (const void*)rows : (const void*)16,
+                          n > 0 ? (const void*)perm : (const void*)16, n > 0 ? (const void*)seg : (const void*)16,
+                          n > 0 ? (const void*)n_unique : (const void*)16};
+    const char* names[] = {"out", "rows", "perm", "seg", "n_unique"};
+    for (int i = 0; i < 5; ++i) {
+        if (ptrs[i] == nullptr) { set_error("%s: %s is NULL", fn, names[i]); return KGE_E_NULL; }
+        if (!aligned16(ptrs[i])) { set_error("%s: %s is not 16-byte aligned", fn, names[i]); return KGE_E_ALIGN; }
+    }
+    float* base = nullptr;
+    int rc = static_scratch(&base);
+    if (rc) return rc;
+    if (n == 0) {
+        if (n_out > 0) return cuda_status(cudaMemsetAsync(out, 0, (size_t)n_out * dim * 4, s), fn);
+        return 0;
+    }
+    float* lead = base;
+    float* trail = base + kStaticHalfFloats;
+    const bool vec = dim % 4 == 0;
+    switch (quads_per_lane(dim)) {
+        case 1: return vec ? segred_go<1, true>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s)
+                           : segred_go<1, false>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s);
+        case 2: return vec ? segred_go<2, true>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s)
+                           : segred_go<2, false>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s);
+        case 4: return vec ? segred_go<4, true>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s)
+                           : segred_go<4, false>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s);
+        case 8: return vec ? segred_go<8, true>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s)
+                           : segred_go<8, false>(rows, dim, n, perm, seg, (const long long*)n_unique, out, n_out, lead, trail, s);
+    }
+    return KGE_E_UNSUPPORTED;
+}

@@ -165,6 +165,18 @@ def segment_reduce(rows: torch.Tensor, insp: Inspection, out: Optional[torch.Ten
     return out
 
 
+def segment_reduce_static(rows: torch.Tensor, insp: Inspection, out: torch.Tensor) -> torch.Tensor:
+    """segment_reduce through the entry point that owns its scratch: nothing is allocated, so `out` must be given.
+    Limited to ceil(n/32) * dim <= 1,048,576; calls on one device must not overlap (they share the scratch)."""
+    _need_cuda(rows, out)
+    n, dim = rows.shape
+    if n != insp.n:
+        raise ValueError(f"rows has {n} slots, the inspection {insp.n}")
+    check(_lib.lib().kge_segment_reduce_static(_ptr(rows), dim, n, _ptr(insp.perm), _ptr(insp.seg), _ptr(insp.n_unique),
+                                               _ptr(out), out.shape[0], _stream()))
+    return out
+
+
 def owner_counts(insp: Inspection, rows_per_rank: int, world: int) -> torch.Tensor:
     counts = torch.empty(world, dtype=torch.int64, device=insp.uniq.device)
     check(_lib.lib().kge_owner_counts(_ptr(insp.uniq), _ptr(insp.n_unique), insp.n, int(rows_per_rank), int(world),

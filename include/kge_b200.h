@@ -188,6 +188,24 @@ KGE_API int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const 
                        const int64_t* n_unique, float* out, int64_t n_out,
                        void* workspace, size_t workspace_bytes, kge_stream_t stream);
 
+/* Same result as kge_segment_reduce, for hosts that may not allocate device memory: the partial-row scratch
+ * lives in a fixed array inside the library (8 MiB of device memory per GPU, held from library load to process
+ * exit) instead of a caller-provided workspace, and this call performs no allocation of any kind.
+ * It has no counterpart in the reference.  Typical callers: a serving or training loop that was handed its
+ * buffers up front and runs under a "no allocation after start-up" rule (allocator calls synchronise the device
+ * and can fail late), or an FFI host that can pass its own input/output buffers but has no device allocator to
+ * size a workspace with.  Inputs and outputs are still the caller's.
+ * Limit: ceil(n / 32) * dim <= 1,048,576 (e.g. n = 131,072 slots at dim = 256); larger problems are rejected
+ * with KGE_E_RANGE and a message, nothing is launched.
+ * The first call on each device looks up the scratch address (a host-side, non-stream operation); make that
+ * first call before any stream capture begins on that device.
+ * All calls on a device share the one scratch array: two calls that overlap on the GPU (different streams, or
+ * different host threads without ordering) race on it and corrupt each other's sums.  The array keeps the
+ * previous call's contents; nothing in it needs to start at zero, because every partial row is written before
+ * it is read within a call. */
+KGE_API int kge_segment_reduce_static(const float* rows, int32_t dim, int64_t n, const int32_t* perm, const int32_t* seg,
+                                      const int64_t* n_unique, float* out, int64_t n_out, kge_stream_t stream);
+
 /* ---- scoring ------------------------------------------------------------------------------------
  * Fused gather + score.  pos_score (batch,) ; neg_score (batch, n_neg) per-triple or
  * (batch/chunk, chunk, n_neg) chunk-shared.  Scores as in enum kge_model.  Ids index `ent` directly; to
