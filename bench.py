@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the KGE scoring hot path: scored triples/sec, forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --config c1|c2|c3|c4          (side measurements of the parity configurations, 1 GPU)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
 
@@ -47,6 +48,8 @@ def parse():
                     help="profiling aid: run forward+backward of the scorers 3 times on a reduced case (--chunks chunks, "
                          "entity table scaled down to fit a few GB) and exit; meant to be run under ncu -k <kernel>")
     ap.add_argument("--chunks", type=int, default=32)
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "tensor"],
+                    help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
     return ap.parse_args()
 
@@ -190,15 +193,86 @@ def workload_config(cfg, models, n_gpus):
 
 
 # ---------------------------------------------------------------------------------------------------------
+# side measurements: the parity configurations c1-c4, one scorer at a time, single GPU
+# ---------------------------------------------------------------------------------------------------------
+def side_config(args):
+    """Times forward (and backward + gradient reduction where the scorer has one) of configs c1-c4 on one GPU and
+    prints one JSON line per scorer with the HBM view of the roofline.  Not the headline metric: the tables of
+    c1-c3 fit in L2, so a >256 MB buffer is written between timed iterations (cold-L2 figure) and the warm-L2
+    figure is reported beside it."""
+    import torch
+    from cuke_b200 import scoring, synth
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = synth.CONFIGS[args.config]
+    hbm_gbs, _, peak_kind = peaks()
+    flush = torch.empty(384 << 20, dtype=torch.uint8, device=dev)
+    for model in (cfg.model,) + tuple(cfg.extra_models):
+        ent, rel, rel2 = synth.make_tables(cfg, model)
+        to = lambda a: None if a is None else torch.from_numpy(a).to(dev).to(torch.bfloat16 if cfg.dtype == "bf16" else torch.float32).contiguous()
+        sc = scoring.Scorer(model, to(ent), to(rel), to(rel2), cfg.neg_mode, cfg.n_neg_head if model != "RESCAL" else 0, cfg.chunk)
+        h, r, t, neg = (torch.from_numpy(x).to(dev) for x in synth.make_batch(cfg, 0, 0))
+        backward = cfg.backward and model != "TransR"
+        d = synth.row_floats(cfg, model)
+        ids = scoring.entity_id_list(h, t, neg)
+
+        def step():
+            pos, negs, rinsp = sc.forward(h, r, t, neg)
+            if backward:
+                loss, dpos, dneg = scoring.logistic_loss(pos, negs)
+                sg = sc.backward(h, r, t, neg, pos, negs, dpos, dneg, rinsp)
+                insp = scoring.inspect(ids, cfg.n_ent)
+                scoring.segment_reduce(sg.ent_slots, insp)
+            return pos
+
+        def timed(cold):
+            for _ in range(max(args.warmup, 3)):
+                step()
+            torch.cuda.synchronize()
+            tot = 0.0
+            for _ in range(args.steps):
+                if cold:
+                    flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); step(); e1.record()
+                torch.cuda.synchronize()
+                tot += e0.elapsed_time(e1)
+            return tot / args.steps
+
+        ms_cold, ms_warm = timed(True), timed(False)
+        S = synth.scored_triples(cfg)
+        U_e = int(torch.unique(ids).numel()); U_r = int(torch.unique(r).numel())
+        es = 2 if cfg.dtype == "bf16" else 4
+        relrow = {"TransH": 2 * d * es, "TransR": (d + d * d) * es, "RESCAL": d * d * es}.get(model, d * es)
+        bytes_fwd = U_e * d * es + U_r * relrow + 8 * (3 * cfg.batch + neg.numel()) + 4 * S
+        bytes_bwd = (4 * S + U_e * d * 4 + U_r * relrow * 4 // es + U_e * d * es + U_r * relrow) if backward else 0
+        bytes_alg = bytes_fwd + bytes_bwd
+        print(json.dumps({"metric": METRIC if backward else "scored_triples_per_sec_fwd", "side_measurement": True,
+                          "value": S / (ms_cold * 1e-3), "value_warm_l2": S / (ms_warm * 1e-3), "unit": "triples/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm,
+                          "dtype": cfg.dtype, "data": "synthetic",
+                          "config": {"workload": f"{cfg.name}: {model} {'fwd+bwd' if backward else 'fwd'}, entities {cfg.n_ent}x{d}, "
+                                                 f"batch {cfg.batch}, {cfg.n_neg} negatives ({cfg.neg_mode})",
+                                     "l2": "384 MB written between timed iterations (cold L2); warm figure beside it"},
+                          "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms_cold * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                                       "frac": bytes_alg / (ms_cold * 1e-3) / 1e9 / hbm_gbs, "bytes_alg": bytes_alg,
+                                       "gathered_bytes": S * 2 * d * es, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
+                                       "traffic": None}}), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     from cuke_b200 import synth
-    if args.config not in ("c4", "c5"):
-        raise SystemExit("bench.py times the chunk-shared configurations (c5 default, c4 ComplEx); the others are parity cases")
+    if args.config != "c5":
+        if args.impl == "reference" or args.gpus != 1:
+            raise SystemExit("only c5 has a reference arm and a multi-GPU run; c1-c4 are single-GPU side measurements")
+        side_config(args)
+        return
     cfg = synth.CONFIGS[args.config]
-    models = ["TransE", "DistMult"] if cfg.name == "c5" else ["ComplEx"]
+    models = ["TransE", "DistMult"]
     if args.impl == "reference":
         reference_arm(args, cfg, models)
         return
@@ -234,7 +308,8 @@ def main():
     for mi, m in enumerate(models):
         g = np.random.Generator(np.random.PCG64(synth.BASE_SEED + 1000 * cfg.cid + 2 + mi))
         rel[m] = torch.from_numpy((g.standard_normal((cfg.n_rel, d)) / np.sqrt(d)).astype(np.float32)).to(dev)
-    stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group)
+    stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group,
+                      precision=args.precision)
 
     nb = 4
     host = []

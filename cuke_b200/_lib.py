@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libkge_b200.so")
 MODELS = {"TransE": 0, "TransH": 1, "TransR": 2, "TransF": 3, "DistMult": 4, "RESCAL": 5, "ComplEx": 6}
 DTYPES = {"f32": 0, "bf16": 1}
 NEG_MODES = {"none": 0, "per_triple": 1, "chunk_shared": 2}
+PRECISIONS = {"fp32": 0, "tensor": 1}
 VECTOR_MODELS = ("TransE", "TransH", "TransR")
 MATRIX_MODELS = ("TransR", "RESCAL")
 
@@ -28,7 +29,8 @@ class KgeError(RuntimeError):
 class KgeProblem(C.Structure):
     _fields_ = [("model", C.c_int32), ("dtype", C.c_int32), ("neg_mode", C.c_int32), ("id_bits", C.c_int32),
                 ("dim", C.c_int32), ("n_neg", C.c_int32), ("n_neg_head", C.c_int32), ("chunk", C.c_int32),
-                ("batch", C.c_int64), ("n_ent", C.c_int64), ("n_rel", C.c_int64)]
+                ("batch", C.c_int64), ("n_ent", C.c_int64), ("n_rel", C.c_int64),
+                ("precision", C.c_int32), ("reserved", C.c_int32)]
 
 
 class KgeTensors(C.Structure):

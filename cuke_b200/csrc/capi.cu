@@ -56,6 +56,8 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s);
 int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
+size_t tc_pair_workspace_bytes(long long n_a, long long n_x, int dim);
+int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -87,6 +89,7 @@ static int check_problem(const char* fn, const kge_problem* p, const kge_tensors
     if (p->model == KGE_COMPLEX && (p->dim & 1)) { set_error("%s: ComplEx needs an even dim (re,im interleaved), got %d", fn, p->dim); return KGE_E_SHAPE; }
     if (p->dtype == KGE_BF16 && (p->dim & 7)) { set_error("%s: bf16 tables need dim %% 8 == 0 (16-byte rows), got %d", fn, p->dim); return KGE_E_UNSUPPORTED; }
     if (p->batch < 0) { set_error("%s: negative batch", fn); return KGE_E_SHAPE; }
+    if (p->precision != KGE_PREC_FP32 && p->precision != KGE_PREC_TENSOR) { set_error("%s: unknown precision %d", fn, p->precision); return KGE_E_UNSUPPORTED; }
     if (p->batch == 0) return 0;
     KGE_REQUIRE_PTR(t->ent, "ent");
     if (uses_rel(p->model)) KGE_REQUIRE_PTR(t->rel, "rel");
@@ -132,6 +135,15 @@ static ScoreArgs score_args(const kge_problem* p, const kge_tensors* t) {
 }
 
 static inline size_t rows_bytes(const kge_problem* p) { return ((size_t)p->batch * p->dim * 4 + 255) / 256 * 256; }
+
+// Tensor-core forward is available for the dot-product scorers with chunk-shared negatives.
+static bool tc_forward(const kge_problem* p) {
+    return p->precision == KGE_PREC_TENSOR && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 && p->dtype == KGE_F32 &&
+           (p->model == KGE_DISTMULT || p->model == KGE_COMPLEX || p->model == KGE_RESCAL);
+}
+static size_t tc_bytes(const kge_problem* p) {
+    return tc_forward(p) ? tc_pair_workspace_bytes(p->batch, (p->batch / p->chunk) * (long long)p->n_neg, p->dim) : 0;
+}
 
 }  // namespace kge
 
@@ -241,7 +253,7 @@ size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
     if (!p || p->batch <= 0) return 256;
     const size_t rb = rows_bytes(p);
     if (backward) return 3 * rb + 256;
-    return (p->model == KGE_RESCAL ? rb : 0) + 256;
+    return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p) + 256;
 }
 
 int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_score, float* neg_score, void* workspace,
@@ -272,6 +284,10 @@ int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_sco
     apos.n_neg = 0; apos.n_neg_head = 0;
     rc = launch_triple_forward(apos, s);
     if (rc) return rc;
+    if (tc_forward(p)) {
+        char* tcw = static_cast<char*>(workspace) + (p->model == KGE_RESCAL ? rows_bytes(p) : 0);
+        return launch_pair_forward_tc(a, p->n_neg_head > 0 ? 1 : 0, tcw, tc_bytes(p), s);
+    }
     return launch_pair_forward(a, p->n_neg_head > 0 ? 1 : 0, s);
 }
 

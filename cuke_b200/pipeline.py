@@ -94,10 +94,11 @@ class KgeStep:
     world == 1).  `group` is a torch.distributed process group (NCCL) when world > 1."""
 
     def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
-                 neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None):
+                 neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None,
+                 precision: str = "fp32"):
         self.models, self.ent_local, self.rel = list(models), ent_local, rel
         self.n_ent, self.rank, self.world, self.group = int(n_ent), int(rank), int(world), group
-        self.neg_mode, self.n_neg_head, self.chunk = neg_mode, n_neg_head, chunk
+        self.neg_mode, self.n_neg_head, self.chunk, self.precision = neg_mode, n_neg_head, chunk, precision
         self.dim = ent_local.shape[1]
         self.n_rel = {m: rel[m].shape[0] for m in self.models}
         for m in self.models:
@@ -120,7 +121,7 @@ class KgeStep:
         r32 = r.to(torch.int32)
         rinsp = None
         for m in self.models:
-            sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk)
+            sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk, self.precision)
             pos, negs, _ = sc.forward(sh, r32, st, sneg)
             loss, dpos, dneg = scoring.logistic_loss(pos, negs)
             out.loss[m], out.pos[m] = loss, pos

@@ -12,7 +12,8 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import DTYPES, MATRIX_MODELS, MODELS, NEG_MODES, VECTOR_MODELS, KgeGrads, KgeProblem, KgeTensors, check
+from ._lib import (DTYPES, MATRIX_MODELS, MODELS, NEG_MODES, PRECISIONS, VECTOR_MODELS, KgeGrads, KgeProblem, KgeTensors,
+                   check)
 
 
 def _stream() -> int:
@@ -184,6 +185,14 @@ def owner_counts(insp: Inspection, rows_per_rank: int, world: int) -> torch.Tens
     return counts
 
 
+def device_flags() -> int:
+    """Reads and clears the device error word (synchronises the current stream); 0 = clean, bit 2 = a bounded wait
+    inside a tensor-core kernel ran out and its outputs are invalid."""
+    flags = C.c_int32(0)
+    check(_lib.lib().kge_check(_stream(), C.byref(flags)))
+    return int(flags.value)
+
+
 def logistic_loss(pos: torch.Tensor, neg: Optional[torch.Tensor]):
     """(loss (1,), dpos, dneg): sum softplus(-pos) + mean-over-negatives-per-positive softplus(neg), and derivatives."""
     _need_cuda(pos, neg)
@@ -221,9 +230,11 @@ class Scorer:
     """
 
     def __init__(self, model: str, ent: torch.Tensor, rel: Optional[torch.Tensor] = None,
-                 rel2: Optional[torch.Tensor] = None, neg_mode: str = "none", n_neg_head: int = 0, chunk: int = 0):
+                 rel2: Optional[torch.Tensor] = None, neg_mode: str = "none", n_neg_head: int = 0, chunk: int = 0,
+                 precision: str = "fp32"):
         if model not in MODELS:
             raise KeyError(model)
+        self.precision = PRECISIONS[precision]
         _need_cuda(ent, rel, rel2)
         self.model, self.ent, self.rel, self.rel2 = model, ent, rel, rel2
         self.neg_mode, self.n_neg_head, self.chunk = neg_mode, int(n_neg_head), int(chunk)
@@ -232,14 +243,17 @@ class Scorer:
 
     def with_entities(self, ent: torch.Tensor) -> "Scorer":
         """Same scorer over another entity buffer (e.g. the compact staging buffer of distinct rows)."""
-        return Scorer(self.model, ent, self.rel, self.rel2, self.neg_mode, self.n_neg_head, self.chunk)
+        sc = Scorer(self.model, ent, self.rel, self.rel2, self.neg_mode, self.n_neg_head, self.chunk)
+        sc.precision = self.precision
+        return sc
 
     # -- struct plumbing
     def _problem(self, h, neg) -> KgeProblem:
         n_neg = 0 if (neg is None or self.neg_mode == "none") else int(neg.shape[-1])
         return KgeProblem(MODELS[self.model], DTYPES[_dtype_of(self.ent)], NEG_MODES[self.neg_mode if n_neg else "none"],
                           _id_bits(h), self.dim, n_neg, self.n_neg_head if n_neg else 0,
-                          self.chunk if self.neg_mode == "chunk_shared" else 0, h.numel(), self.ent.shape[0], self.n_rel)
+                          self.chunk if self.neg_mode == "chunk_shared" else 0, h.numel(), self.ent.shape[0], self.n_rel,
+                          self.precision, 0)
 
     def _tensors(self, h, r, t, neg, rel_insp: Optional[Inspection]) -> KgeTensors:
         kt = KgeTensors(_ptr(self.ent), _ptr(self.rel), _ptr(self.rel2), _ptr(h), _ptr(r), _ptr(t), _ptr(neg),

@@ -70,6 +70,13 @@ enum kge_model {
 
 enum kge_dtype { KGE_F32 = 0, KGE_BF16 = 1 };   /* storage type of the tables; accumulation is fp32 */
 
+enum kge_precision {
+    KGE_PREC_FP32 = 0,    /* fp32 CUDA-core arithmetic throughout (default) */
+    KGE_PREC_TENSOR = 1   /* contractions on the tensor cores where a kernel exists: fp32 tables as 3-term split tf32
+                             ("3xTF32", product error ~2^-20, same 1e-4 tolerance), bf16 tables as bf16 MMA with fp32
+                             accumulation; everything else as KGE_PREC_FP32 */
+};
+
 enum kge_neg_mode {
     KGE_NEG_NONE = 0,         /* positives only */
     KGE_NEG_PER_TRIPLE = 1,   /* neg is (batch, n_neg): triple i is scored against its own n_neg rows */
@@ -89,6 +96,8 @@ typedef struct kge_problem {
     int64_t batch;       /* number of positive triples */
     int64_t n_ent;       /* rows of `ent` */
     int64_t n_rel;       /* rows of `rel` / `rel2` */
+    int32_t precision;   /* enum kge_precision */
+    int32_t reserved;    /* must be 0 */
 } kge_problem;
 
 typedef struct kge_tensors {

@@ -58,10 +58,10 @@ def bf16_round(a):
     return None if a is None else torch.from_numpy(a).to(torch.bfloat16).float().numpy()
 
 
-def gpu_scorer(p, n_neg_head=0, bf16=False):
+def gpu_scorer(p, n_neg_head=0, bf16=False, precision="fp32"):
     from cuke_b200.scoring import Scorer
     return Scorer(p["model"], to_dev(p["E"], bf16=bf16), to_dev(p["R"], bf16=bf16), to_dev(p["P2"], bf16=bf16),
-                  p["neg_mode"], n_neg_head, p["chunk"])
+                  p["neg_mode"], n_neg_head, p["chunk"], precision)
 
 
 def gpu_ids(p, id_dtype=torch.int64):

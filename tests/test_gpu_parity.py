@@ -85,6 +85,29 @@ def test_score_forward_chunk_shared(model, d, chunk, nchunks, nn, head):
     assert rel_err(negs.reshape(len(rpos), -1).cpu().numpy(), rneg) < FP32_TOL
 
 
+@pytest.mark.parametrize("model", ["DistMult", "ComplEx", "RESCAL"])
+@pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (64, 128, 2, 256, 0), (400, 256, 2, 384, 0),
+                                                     (200, 130, 2, 150, 1), (36, 7, 3, 9, 0), (512, 1024, 1, 1024, 0)])
+def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
+    """3xTF32 tcgen05 path of the chunk-shared dot-product scorers: same 1e-4 tolerance as the fp32 CUDA-core path."""
+    from cuke_b200 import scoring
+    if model == "RESCAL":
+        head = 0
+        d = min(d, 200)
+    p = make_problem(model, seed=7 * d + chunk, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    nnh = nn if head else 0
+    sc = gpu_scorer(p, nnh, precision="tensor")
+    h, r, t, neg = gpu_ids(p)
+    pos, negs, _ = sc.forward(h, r, t, neg)
+    assert scoring.device_flags() == 0, "a bounded wait inside the tensor-core kernel ran out"
+    rpos, rneg = oracle.scores(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], p["neg"], "chunk_shared", nnh, chunk)
+    assert rel_err(pos.cpu().numpy(), rpos) < FP32_TOL
+    err = rel_err(negs.reshape(len(rpos), -1).cpu().numpy(), rneg)
+    assert err < FP32_TOL, err
+    pos2, negs2, _ = sc.forward(h, r, t, neg)
+    assert torch.equal(negs, negs2)
+
+
 @pytest.mark.parametrize("model", ["TransE", "TransH", "DistMult", "ComplEx", "RESCAL", "TransR"])
 def test_score_forward_bf16(model):
     d = 200 if model != "ComplEx" else 256
