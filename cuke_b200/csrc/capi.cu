@@ -56,8 +56,9 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s);
 int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
-size_t tc_pair_workspace_bytes(long long n_a, long long n_x, int dim);
+size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int backward);
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, size_t ws_bytes, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -136,13 +137,15 @@ static ScoreArgs score_args(const kge_problem* p, const kge_tensors* t) {
 
 static inline size_t rows_bytes(const kge_problem* p) { return ((size_t)p->batch * p->dim * 4 + 255) / 256 * 256; }
 
-// Tensor-core forward is available for the dot-product scorers with chunk-shared negatives.
+// The tensor-core contractions exist for the scorers that support chunk-shared negatives.
 static bool tc_forward(const kge_problem* p) {
-    return p->precision == KGE_PREC_TENSOR && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 && p->dtype == KGE_F32 &&
-           (p->model == KGE_DISTMULT || p->model == KGE_COMPLEX || p->model == KGE_RESCAL);
+    return p->precision == KGE_PREC_TENSOR && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 &&
+           (p->model == KGE_TRANSE || p->model == KGE_DISTMULT || p->model == KGE_COMPLEX || p->model == KGE_RESCAL);
 }
-static size_t tc_bytes(const kge_problem* p) {
-    return tc_forward(p) ? tc_pair_workspace_bytes(p->batch, (p->batch / p->chunk) * (long long)p->n_neg, p->dim) : 0;
+static bool tc_backward(const kge_problem* p) { return tc_forward(p) && p->n_neg % 4 == 0; }
+static size_t tc_bytes(const kge_problem* p, int backward) {
+    if (backward ? !tc_backward(p) : !tc_forward(p)) return 0;
+    return tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, backward);
 }
 
 }  // namespace kge
@@ -252,8 +255,8 @@ int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t*
 size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
     if (!p || p->batch <= 0) return 256;
     const size_t rb = rows_bytes(p);
-    if (backward) return 3 * rb + 256;
-    return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p) + 256;
+    if (backward) return 3 * rb + tc_bytes(p, 1) + 256;
+    return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + 256;
 }
 
 int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_score, float* neg_score, void* workspace,
@@ -286,7 +289,7 @@ int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_sco
     if (rc) return rc;
     if (tc_forward(p)) {
         char* tcw = static_cast<char*>(workspace) + (p->model == KGE_RESCAL ? rows_bytes(p) : 0);
-        return launch_pair_forward_tc(a, p->n_neg_head > 0 ? 1 : 0, tcw, tc_bytes(p), s);
+        return launch_pair_forward_tc(a, p->n_neg_head > 0 ? 1 : 0, tcw, tc_bytes(p, 0), s);
     }
     return launch_pair_forward(a, p->n_neg_head > 0 ? 1 : 0, s);
 }
@@ -329,11 +332,15 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     }
     if (p->neg_mode == KGE_NEG_CHUNK_SHARED) {
         const bool head = p->n_neg_head > 0;
-        if (p->model != KGE_RESCAL) {
-            rc = launch_anchor(a, head ? nullptr : ws0, head ? ws0 : nullptr, s);
-            if (rc) return rc;
+        if (tc_backward(p)) {
+            rc = launch_pair_backward_tc(a, head ? 1 : 0, ws1, static_cast<char*>(workspace) + 3 * rb, tc_bytes(p, 1), s);
+        } else {
+            if (p->model != KGE_RESCAL) {
+                rc = launch_anchor(a, head ? nullptr : ws0, head ? ws0 : nullptr, s);
+                if (rc) return rc;
+            }
+            rc = launch_pair_backward(a, ws0, ws1, s);
         }
-        rc = launch_pair_backward(a, ws0, ws1, s);
         if (rc) return rc;
         ScoreArgs b = a;
         b.n_neg = 0; b.n_neg_head = 0;

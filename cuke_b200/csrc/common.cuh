@@ -119,6 +119,8 @@ struct ScoreArgs {
     const float* ga_tail_init;               // (batch, dim) anchor gradients accumulated elsewhere (chunk-shared)
     const float* ga_head_init;
     const float* anchors;                    // (batch, dim) precomputed anchors (RESCAL), or NULL
+    const unsigned long long* guard;         // if set, pair_fwd_kernel only runs when *guard > guard_cap (tensor-core overflow path)
+    unsigned long long guard_cap;
     long long batch; int dim; int n_neg; int n_neg_head; int chunk;
     int model; int dtype; int id_bits;
 };

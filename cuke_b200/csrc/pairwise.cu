@@ -106,6 +106,7 @@ template <int MODEL, typename T, typename I, bool VEC, bool VECOUT>
 __global__ void __launch_bounds__(256, 2) pair_fwd_kernel(ScoreArgs a, int head) {
     __shared__ __align__(16) TileSmem sm;
     constexpr int OP = PairOp<MODEL>::value;
+    if (a.guard != nullptr && *a.guard <= a.guard_cap) return;      // exact recomputation not needed
     const int tid = threadIdx.x;
     const int c = blockIdx.z, m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * TG_BN;
     const long long i0 = (long long)c * a.chunk;

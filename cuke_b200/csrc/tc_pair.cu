@@ -1,22 +1,31 @@
-// Tensor-core path of the chunk-shared scorers (fp32 tables, "3xTF32"): per chunk the score matrix is the
-// contraction  S[i][j] = sum_k a_i[k] x_j[k]  (DistMult / ComplEx / RESCAL anchors against the chunk's negative rows),
-// which runs on the 5th-generation tensor cores:
+// Tensor-core path of the chunk-shared scorers (fp32 tables, "3xTF32").  Per chunk c the work is three contractions
 //
-//   pack kernels   a_i (anchor, computed from the gathered h/t and r rows) and x_j (gathered negative rows) are
-//                  written once as dense K-major matrices split into hi = top 19 bits (exactly representable in
-//                  tf32) and lo = tf32(a - hi); also |a_i|^2 and |x_j|^2 for the distance form.
-//   umma kernel    per 128 x 128 output tile: TMA (128-byte swizzle) feeds a 3-stage shared-memory ring, one
-//                  elected thread issues tcgen05.mma kind::tf32 for hi*hi + hi*lo + lo*hi into one fp32
-//                  accumulator in tensor memory, four epilogue warps read it back with tcgen05.ld and store.
-//   The split makes the products exact to ~2^-20 relative, inside the 1e-4 tolerance of the fp32 path
-//   (a single tf32 pass, 2^-11, would not be).
+//   forward   S[i][j]   = sum_k a_i[k] x_j[k]                       (anchors x negative rows, K = dim)
+//   backward  GA[i][:]  = sum_j W_ij x_j          (K = n_neg)       W = dS (dot-product scorers) or dS / S (TransE)
+//             GX[j][:]  = sum_i W_ij a_i          (K = chunk)
+//
+// all run by ONE kernel, umma_gemm_kernel, on the 5th-generation tensor cores:
+//   * operands are dense fp32 matrices split into hi = top 19 bits (exact in tf32) and lo = tf32(v - hi), written
+//     once by pack kernels (anchors are computed there from the gathered h/t and r rows; W from dS and S);
+//   * TMA (3-D tensor maps: batch, rows, cols; 128-byte swizzle; out-of-range reads as zero) feeds a shared-memory
+//     ring; an operand is used K-major (rows of 32 k-values) or MN-major (32 m/n-values per k-row) as it lies in
+//     memory, so W, X and A are never transposed;
+//   * one elected thread issues tcgen05.mma kind::tf32 for lo*hi + hi*lo + hi*hi into an fp32 accumulator in tensor
+//     memory; four epilogue warps read it back with tcgen05.ld and apply the scorer's epilogue.
+//   The split makes products exact to ~2^-20 relative, inside the 1e-4 tolerance of the fp32 path (a single tf32
+//   pass, 2^-11, would not be).  TransE's distance uses |a|^2 + |x|^2 - 2 a.x; entries where that form cancels
+//   (d^2 < 2^-6 (|a|^2 + |x|^2)) are listed by the epilogue and recomputed exactly from the rows by a fix-up kernel;
+//   if the list overflows, the exact CUDA-core kernel recomputes the whole matrix (device-side guard, no host sync).
 //
 // Replaces the scalar-FMA inner loops that cuke generates for bvv over gathered rows
 // (apps/kge/kge.py:13-15, pycuke1/codegen/gpu.py:43-51).
+#include <string.h>
 #include "rows.cuh"
 #include "umma.cuh"
 
 namespace kge {
+
+int launch_pair_forward(const ScoreArgs& a, int head, cudaStream_t s);     // pairwise.cu (exact CUDA-core kernel)
 
 // ---- host: tensor maps -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -34,19 +43,24 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
-                       uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+int make_tensor_map_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t batch, uint64_t rows, uint64_t cols,
+                       uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_rows, uint32_t box_cols, bool atom32) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return KGE_E_DEVICE; }
-    cuuint64_t gdim[2] = {cols, rows};
-    cuuint64_t gstride[1] = {row_stride_bytes};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+    cuuint64_t gdim[3] = {cols, rows, batch};
+    cuuint64_t gstride[2] = {row_stride_bytes, batch_stride_bytes};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                     const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return KGE_E_DEVICE; }
     return 0;
+}
+int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                       uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+    return make_tensor_map_3d(out, base, elem_bytes, 1, rows, cols, row_stride_bytes, rows * row_stride_bytes, box_rows, box_cols);
 }
 
 // ---- pack kernels --------------------------------------------------------------------------------------------
@@ -95,46 +109,86 @@ __global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, lon
     if (lane == 0 && sq) sq[row] = s;
 }
 
-// ---- the tensor-core tile kernel -------------------------------------------------------------------------------
-constexpr int UM_BM = 128, UM_BN = 128, UM_BK = 32;         // 32 fp32 = one 128-byte swizzle row
-constexpr int UM_STAGES = 3;
-constexpr int UM_TILE_BYTES = UM_BM * UM_BK * 4;             // 16 KiB per operand tile
-constexpr int UM_STAGE_BYTES = 4 * UM_TILE_BYTES;            // A_hi, A_lo, B_hi, B_lo
-constexpr int UM_SMEM_BYTES = UM_STAGES * UM_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+// W = dS (DIST == false) or dS / S (DIST: S = -distance; 0 where S == 0), split into hi / lo; row sums for DIST.
+// One warp per row of the (batch, n_neg) matrix.
+template <bool DIST>
+__global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, const float* sc, long long rows, int n_neg,
+                                                        float* hi, float* lo, float* rowsum) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float* d = ds + row * n_neg;
+    const float* s = sc ? sc + row * n_neg : nullptr;
+    float sum = 0.f;
+    for (int j = lane; j < n_neg; j += 32) {
+        float w = d[j];
+        if (DIST) { const float sv = s[j]; w = sv != 0.f ? w / sv : 0.f; sum += w; }
+        const float h = tf32_trunc(w);
+        hi[row * n_neg + j] = h;
+        lo[row * n_neg + j] = tf32_trunc(w - h);
+    }
+    if (DIST) { sum = warp_sum(sum); if (lane == 0) rowsum[row] = sum; }
+}
+// Column sums of W per chunk: colsum[c][j] = sum_i W[c*chunk + i][j], added in ascending i.
+__global__ void __launch_bounds__(256) tc_colsum_kernel(const float* hi, const float* lo, int chunk, int n_neg, long long batch,
+                                                        float* colsum) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = blockIdx.y;
+    if (j >= n_neg) return;
+    const long long i0 = (long long)c * chunk;
+    const int rows = (int)min((long long)chunk, batch - i0);
+    float s = 0.f;
+    for (int i = 0; i < rows; ++i) { const long long o = (i0 + i) * n_neg + j; s += hi[o] + lo[o]; }
+    colsum[(long long)c * n_neg + j] = s;
+}
 
-struct UmmaParams {
-    int rows_a;            // rows of A per batch (chunk)
-    int rows_b;            // rows of B per batch (n_neg)
-    int k;                 // reduction length (dim)
-    float* out;            // (batch, rows_a, rows_b)
-    const float* sq_a;     // squared norms, distance form only
-    const float* sq_b;
-    int dist;              // 0: out = acc;  1: out = -sqrt(max(sq_a + sq_b - 2 acc, 0))
-    int32_t* err;          // device error word
+// ---- the tensor-core tile kernel -------------------------------------------------------------------------------
+constexpr int UM_BM = 128, UM_BK = 32;                       // 32 fp32 = one 128-byte swizzle row
+constexpr int UM_A_BYTES = UM_BM * UM_BK * 4;                // 16 KiB per A tile (either major)
+constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major slab: 32 k-rows x 128 bytes
+constexpr int UM_MAX_SMEM = 2 * (2 * UM_A_BYTES + 2 * 256 * 128) + 1024 + 256;      // 2 stages at BN = 256
+
+enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2 };
+
+struct GemmTc {
+    int m_rows, n_cols, k_len;        // extents per batch
+    int bn;                           // tile width (multiple of 16, <= 256)
+    int a_mn, b_mn;                   // operand majors: 0 K-major, 1 MN-major
+    int stages;
+    int ep;                           // epilogue
+    float* out; long long out_ld; long long out_batch_rows;      // out[(b * out_batch_rows + m) * out_ld + n]
+    // EP_DIST
+    const float* sq_a; const float* sq_b;                        // (batch * m_rows), (batch * n_cols)
+    unsigned long long* fix_count; unsigned long long* fix_list; unsigned long long fix_cap;
+    // EP_RANK1: out = scale[b * m_rows + m] * (y_hi + y_lo)[(b * m_rows + m) * out_ld + n] - acc
+    const float* scale; const float* y_hi; const float* y_lo;
+    int32_t* err;
 };
 
 __global__ void __launch_bounds__(192, 1)
-umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, UmmaParams p) {
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + UM_STAGES * UM_STAGE_BYTES);
-    uint64_t* empty = full + UM_STAGES;
-    uint64_t* acc_ready = empty + UM_STAGES;
+    const int b_slabs = (p.bn + 31) / 32;
+    const int b_bytes = p.b_mn ? b_slabs * UM_SLAB_BYTES : p.bn * 128;       // one B tile (hi or lo)
+    const int stage_bytes = 2 * UM_A_BYTES + 2 * b_bytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
+    uint64_t* empty = full + p.stages;
+    uint64_t* acc_ready = empty + p.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * UM_BN, m0 = blockIdx.y * UM_BM, b = blockIdx.z;
-    const int num_kb = (p.k + UM_BK - 1) / UM_BK;
-    const int row_a0 = b * p.rows_a + m0;        // first row of this tile in the flattened (batch * rows) operand
-    const int row_b0 = b * p.rows_b + n0;
+    const int n0 = blockIdx.x * p.bn, m0 = blockIdx.y * UM_BM, b = blockIdx.z;
+    const int num_kb = (p.k_len + UM_BK - 1) / UM_BK;
+    const uint32_t tmem_cols = p.bn <= 32 ? 32u : p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < UM_STAGES; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
+        for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
         umma::mbar_init(acc_ready, 1);
         umma::fence_barrier_init();
     }
-    if (warp == 1) { umma::tmem_alloc(tmem_slot, UM_BN); umma::tmem_relinquish(); }
+    if (warp == 1) { umma::tmem_alloc(tmem_slot, tmem_cols); umma::tmem_relinquish(); }
     umma::tc_fence_before();
     __syncthreads();
     umma::tc_fence_after();
@@ -146,38 +200,56 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             umma::prefetch_tensormap(&map_a_hi); umma::prefetch_tensormap(&map_a_lo);
             umma::prefetch_tensormap(&map_b_hi); umma::prefetch_tensormap(&map_b_lo);
             for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % UM_STAGES;
-                const uint32_t ph = (kb / UM_STAGES) & 1;
+                const int s = kb % p.stages;
+                const uint32_t ph = (kb / p.stages) & 1;
                 if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); break; }
-                uint8_t* st = smem + s * UM_STAGE_BYTES;
-                umma::mbar_expect_tx(&full[s], UM_STAGE_BYTES);
-                umma::tma_load_2d(st + 0 * UM_TILE_BYTES, &map_a_hi, kb * UM_BK, row_a0, &full[s]);
-                umma::tma_load_2d(st + 1 * UM_TILE_BYTES, &map_a_lo, kb * UM_BK, row_a0, &full[s]);
-                umma::tma_load_2d(st + 2 * UM_TILE_BYTES, &map_b_hi, kb * UM_BK, row_b0, &full[s]);
-                umma::tma_load_2d(st + 3 * UM_TILE_BYTES, &map_b_lo, kb * UM_BK, row_b0, &full[s]);
+                uint8_t* st = smem + s * stage_bytes;
+                uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + 2 * UM_A_BYTES, *b_lo = b_hi + b_bytes;
+                umma::mbar_expect_tx(&full[s], stage_bytes);
+                const int k0 = kb * UM_BK;
+                if (!p.a_mn) {
+                    umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, b, &full[s]);
+                    umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, b, &full[s]);
+                } else {
+                    for (int sl = 0; sl < UM_BM / 32; ++sl) {
+                        umma::tma_load_3d(a_hi + sl * UM_SLAB_BYTES, &map_a_hi, m0 + 32 * sl, k0, b, &full[s]);
+                        umma::tma_load_3d(a_lo + sl * UM_SLAB_BYTES, &map_a_lo, m0 + 32 * sl, k0, b, &full[s]);
+                    }
+                }
+                if (!p.b_mn) {
+                    umma::tma_load_3d(b_hi, &map_b_hi, k0, n0, b, &full[s]);
+                    umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
+                } else {
+                    for (int sl = 0; sl < b_slabs; ++sl) {
+                        umma::tma_load_3d(b_hi + sl * UM_SLAB_BYTES, &map_b_hi, n0 + 32 * sl, k0, b, &full[s]);
+                        umma::tma_load_3d(b_lo + sl * UM_SLAB_BYTES, &map_b_lo, n0 + 32 * sl, k0, b, &full[s]);
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer -----------------------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = umma::instr_desc(2 /* tf32 */, UM_BM, UM_BN);
-            bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % UM_STAGES;
-                const uint32_t ph = (kb / UM_STAGES) & 1;
-                if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
+            const uint32_t idesc = umma::instr_desc(2 /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % p.stages;
+                const uint32_t ph = (kb / p.stages) & 1;
+                if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); break; }
                 umma::tc_fence_after();
-                const uint32_t st = umma::smem_u32(smem + s * UM_STAGE_BYTES);
-                const uint64_t a_hi = umma::smem_desc_k_sw128(st + 0 * UM_TILE_BYTES);
-                const uint64_t a_lo = umma::smem_desc_k_sw128(st + 1 * UM_TILE_BYTES);
-                const uint64_t b_hi = umma::smem_desc_k_sw128(st + 2 * UM_TILE_BYTES);
-                const uint64_t b_lo = umma::smem_desc_k_sw128(st + 3 * UM_TILE_BYTES);
+                const uint32_t st = umma::smem_u32(smem + s * stage_bytes);
+                const uint32_t a_hi = st, a_lo = st + UM_A_BYTES, b_hi = st + 2 * UM_A_BYTES, b_lo = b_hi + b_bytes;
 #pragma unroll
                 for (int k8 = 0; k8 < UM_BK / 8; ++k8) {
-                    const uint64_t adv = static_cast<uint64_t>((k8 * 8 * 4) >> 4);   // 32 bytes per K=8 step, in 16-byte units
-                    umma::mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);   // small terms first
-                    umma::mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-                    umma::mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+                    // K-major: 8 k-values = 32 bytes further along the swizzled row; MN-major: the next 8-row group
+                    const uint32_t ao = p.a_mn ? k8 * 1024 : k8 * 32;
+                    const uint32_t bo = p.b_mn ? k8 * 1024 : k8 * 32;
+                    const uint64_t dah = p.a_mn ? umma::smem_desc_mn_sw128(a_hi + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_hi + ao);
+                    const uint64_t dal = p.a_mn ? umma::smem_desc_mn_sw128(a_lo + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_lo + ao);
+                    const uint64_t dbh = p.b_mn ? umma::smem_desc_mn_sw128(b_hi + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_hi + bo);
+                    const uint64_t dbl = p.b_mn ? umma::smem_desc_mn_sw128(b_lo + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_lo + bo);
+                    umma::mma_tf32(tmem_base, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
+                    umma::mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+                    umma::mma_tf32(tmem_base, dah, dbh, idesc, 1u);
                 }
                 umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
             }
@@ -191,43 +263,121 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         if (!ok && lane == 0) atomicOr(p.err, 2);
         umma::tc_fence_after();
         const int m = m0 + row;
-        const bool row_ok = ok && (m < p.rows_a);
-        float* orow = p.out + (static_cast<long long>(b) * p.rows_a + m) * p.rows_b + n0;
-        const float sa = (p.dist && row_ok) ? p.sq_a[static_cast<long long>(b) * p.rows_a + m] : 0.f;
+        const bool row_ok = ok && (m < p.m_rows);
+        const long long grow = static_cast<long long>(b) * p.m_rows + m;           // row of A-side per-row vectors
+        float* orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld + n0;
+        const float sa = (p.ep == EP_DIST && row_ok) ? p.sq_a[grow] : 0.f;
+        const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
+        const int n_chunks32 = (p.bn + 31) / 32;
 #pragma unroll 1
-        for (int c = 0; c < UM_BN / 32; ++c) {
+        for (int c = 0; c < n_chunks32; ++c) {
             float v[32];
             umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);   // warp-collective
             if (!row_ok) continue;
             const int nbase = n0 + c * 32;
-            if (p.dist) {
-                const float* sb = p.sq_b + static_cast<long long>(b) * p.rows_b + nbase;
+            const int lim = min(32, min(p.bn - c * 32, p.n_cols - nbase));                    // valid columns of this chunk
+            if (lim <= 0) continue;
+            if (p.ep == EP_DIST) {
+                const float* sb = p.sq_b + static_cast<long long>(b) * p.n_cols + nbase;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float nb = (nbase + j < p.rows_b) ? sb[j] : 0.f;
-                    v[j] = -sqrtf(fmaxf(fmaf(-2.f, v[j], sa + nb), 0.f));
+                    if (j < lim) {
+                        const float nn = sa + sb[j];
+                        const float d2 = fmaf(-2.f, v[j], nn);
+                        if (d2 < 0.015625f * nn) {       // cancellation: list for exact recomputation
+                            const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
+                            if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + (nbase + j);
+                        }
+                        v[j] = -sqrtf(fmaxf(d2, 0.f));
+                    }
                 }
+            } else if (p.ep == EP_RANK1) {
+                const float* yh = p.y_hi + grow * p.out_ld + nbase;
+                const float* yl = p.y_lo + grow * p.out_ld + nbase;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < lim) v[j] = fmaf(rs, yh[j] + yl[j], -v[j]);
             }
-            if (nbase + 32 <= p.rows_b && (p.rows_b & 3) == 0) {
+            if (lim == 32 && (p.out_ld & 3) == 0) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4*>(orow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                    if (nbase + j < p.rows_b) orow[c * 32 + j] = v[j];
+                    if (j < lim) orow[c * 32 + j] = v[j];
             }
         }
     }
     umma::tc_fence_before();
     __syncthreads();
-    if (warp == 1) { umma::tc_fence_after(); umma::tmem_dealloc(tmem_base, UM_BN); }
+    if (warp == 1) { umma::tc_fence_after(); umma::tmem_dealloc(tmem_base, tmem_cols); }
 }
 
-// ---- host launcher ---------------------------------------------------------------------------------------------------
-size_t tc_pair_workspace_bytes(long long n_a, long long n_x, int dim) {
-    const size_t rows = static_cast<size_t>(n_a + n_x);
-    return 2 * ((rows * dim * 4 + 255) / 256 * 256) + (rows * 4 + 255) / 256 * 256;
+// Exact recomputation of the listed TransE scores from the table rows (one warp per entry).
+template <typename T, typename I, int NV>
+__global__ void __launch_bounds__(256) tc_fixup_kernel(ScoreArgs a, int head, const unsigned long long* count,
+                                                       const unsigned long long* list, unsigned long long cap) {
+    const int lane = threadIdx.x & 31;
+    const unsigned long long n = min(*count, cap);
+    if (*count > cap) return;                           // overflow: the exact kernel recomputes everything
+    const T* E = reinterpret_cast<const T*>(a.ent);
+    const T* R = reinterpret_cast<const T*>(a.rel);
+    const int dim = a.dim;
+    for (unsigned long long e = (unsigned long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < n;
+         e += (unsigned long long)gridDim.x * (blockDim.x >> 5)) {
+        const unsigned long long pair = list[e];
+        const long long i = (long long)(pair / a.n_neg);           // triple
+        const int j = (int)(pair % a.n_neg);
+        const long long c = i / a.chunk;
+        Row<NV> o, r, x;
+        load_row<T, NV, true>(o, E + load_id<I>(head ? a.t : a.h, i) * dim, dim, lane);
+        load_row<T, NV, true>(r, R + load_id<I>(a.r, i) * dim, dim, lane);
+        load_row<T, NV, true>(x, E + load_id<I>(a.neg, c * a.n_neg + j) * dim, dim, lane);
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < NV; ++q) {
+            const float4 anc = head ? o.v[q] - r.v[q] : o.v[q] + r.v[q];
+            const float4 d = anc - x.v[q];
+            s = dot4(d, d, s);
+        }
+        s = warp_sum(s);
+        if (lane == 0) a.negs[pair] = -sqrtf(s);
+    }
+}
+
+// ---- host launchers ---------------------------------------------------------------------------------------------------
+static inline size_t al256(size_t x) { return (x + 255) / 256 * 256; }
+
+struct TcLayout {        // carving of the tensor-core workspace
+    size_t mat;          // bytes of one (n_a + n_x, dim) matrix
+    size_t w;            // bytes of one (batch, n_neg) matrix (backward only)
+    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, total;
+    unsigned long long fix_cap;
+};
+static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool backward) {
+    TcLayout L;
+    const long long n_chunks = batch / chunk;
+    const size_t rows = static_cast<size_t>(batch + n_chunks * n_neg);
+    const size_t pairs = static_cast<size_t>(batch) * n_neg;
+    L.mat = al256(rows * dim * 4);
+    L.w = backward ? al256(pairs * 4) : 0;
+    L.fix_cap = backward ? 0 : (pairs / 64 > 4096 ? pairs / 64 : 4096);
+    size_t o = 0;
+    L.off_hi = o; o += L.mat;
+    L.off_lo = o; o += L.mat;
+    L.off_sq = o; o += al256(rows * 4);
+    L.off_fixc = o; o += 256;
+    L.off_fixl = o; o += al256(L.fix_cap * 8);
+    L.off_whi = o; o += L.w;
+    L.off_wlo = o; o += L.w;
+    L.off_rowsum = o; o += backward ? al256(static_cast<size_t>(batch) * 4) : 0;
+    L.off_colsum = o; o += backward ? al256(static_cast<size_t>(n_chunks) * n_neg * 4) : 0;
+    L.total = o;
+    return L;
+}
+size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int backward) {
+    return tc_layout(batch, chunk, n_neg, dim, backward != 0).total;
 }
 
 template <int MODEL, typename T, typename I>
@@ -253,47 +403,163 @@ static int tc_pack_types(const ScoreArgs& a, int head, long long n_a, long long 
     return a.id_bits == 64 ? tc_pack_go<MODEL, __nv_bfloat16, int64_t>(a, head, n_a, n_x, hi, lo, sq, s)
                            : tc_pack_go<MODEL, __nv_bfloat16, int32_t>(a, head, n_a, n_x, hi, lo, sq, s);
 }
+static int tc_pack(const ScoreArgs& a, int head, long long n_a, long long n_x, float* hi, float* lo, float* sq, cudaStream_t s) {
+    switch (a.model) {
+        case KGE_TRANSE: return tc_pack_types<KGE_TRANSE>(a, head, n_a, n_x, hi, lo, sq, s);
+        case KGE_DISTMULT: return tc_pack_types<KGE_DISTMULT>(a, head, n_a, n_x, hi, lo, sq, s);
+        case KGE_COMPLEX: return tc_pack_types<KGE_COMPLEX>(a, head, n_a, n_x, hi, lo, sq, s);
+        case KGE_RESCAL: return tc_pack_types<KGE_RESCAL>(a, head, n_a, n_x, hi, lo, sq, s);
+        default: break;
+    }
+    set_error("model %d is not supported with chunk-shared negatives", a.model);
+    return KGE_E_UNSUPPORTED;
+}
 
-// Forward scores of the chunk's negatives on the tensor cores.  ws: tc_pair_workspace_bytes(batch, n_chunks * n_neg, dim).
+template <typename T, typename I>
+static int tc_fixup_go(const ScoreArgs& a, int head, const unsigned long long* cnt, const unsigned long long* list,
+                       unsigned long long cap, cudaStream_t s) {
+    switch (quads_per_lane(a.dim)) {
+        case 1: tc_fixup_kernel<T, I, 1><<<296, 256, 0, s>>>(a, head, cnt, list, cap); break;
+        case 2: tc_fixup_kernel<T, I, 2><<<296, 256, 0, s>>>(a, head, cnt, list, cap); break;
+        case 4: tc_fixup_kernel<T, I, 4><<<296, 256, 0, s>>>(a, head, cnt, list, cap); break;
+        case 8: tc_fixup_kernel<T, I, 8><<<296, 256, 0, s>>>(a, head, cnt, list, cap); break;
+        default: return KGE_E_UNSUPPORTED;
+    }
+    KGE_LAUNCH_CHECK("tc_fixup_kernel");
+    return 0;
+}
+
+// Tile width over `n` columns: one tile if it fits 256, else equal tiles, multiples of 16.
+static int pick_bn(int n) {
+    const int tiles = (n + 255) / 256;
+    int bn = ((n + tiles - 1) / tiles + 15) / 16 * 16;
+    return bn < 16 ? 16 : bn;
+}
+
+static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, GemmTc& p,
+                    long long batch, cudaStream_t s) {
+    p.stages = p.bn <= 128 ? 3 : 2;
+    p.err = device_error_word();
+    if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
+    const int b_bytes = p.b_mn ? ((p.bn + 31) / 32) * UM_SLAB_BYTES : p.bn * 128;
+    const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + 256;
+    const dim3 grid((p.n_cols + p.bn - 1) / p.bn, (p.m_rows + UM_BM - 1) / UM_BM, (unsigned)batch);
+    umma_gemm_kernel<<<grid, 192, smem, s>>>(ah, al, bh, bl, p);
+    KGE_LAUNCH_CHECK("umma_gemm_kernel");
+    return 0;
+}
+
+// Forward scores of the chunk's negatives.  ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 0).
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s) {
     if (a.batch <= 0 || a.n_neg <= 0) return 0;
     if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const size_t need = tc_pair_workspace_bytes(n_a, n_x, a.dim);
-    if (ws_bytes < need) { set_error("tensor-core workspace: need %zu bytes, got %zu", need, ws_bytes); return KGE_E_WORKSPACE; }
-    const size_t mat = (static_cast<size_t>(n_a + n_x) * a.dim * 4 + 255) / 256 * 256;
-    float* hi = static_cast<float*>(ws);
-    float* lo = reinterpret_cast<float*>(static_cast<char*>(ws) + mat);
-    float* sq = reinterpret_cast<float*>(static_cast<char*>(ws) + 2 * mat);
-    int rc;
-    switch (a.model) {
-        case KGE_TRANSE: rc = tc_pack_types<KGE_TRANSE>(a, head, n_a, n_x, hi, lo, sq, s); break;
-        case KGE_DISTMULT: rc = tc_pack_types<KGE_DISTMULT>(a, head, n_a, n_x, hi, lo, sq, s); break;
-        case KGE_COMPLEX: rc = tc_pack_types<KGE_COMPLEX>(a, head, n_a, n_x, hi, lo, sq, s); break;
-        case KGE_RESCAL: rc = tc_pack_types<KGE_RESCAL>(a, head, n_a, n_x, hi, lo, sq, s); break;
-        default: set_error("model %d is not supported with chunk-shared negatives", a.model); return KGE_E_UNSUPPORTED;
-    }
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, false);
+    if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = static_cast<char*>(ws);
+    float* hi = reinterpret_cast<float*>(w + L.off_hi);
+    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    float* sq = reinterpret_cast<float*>(w + L.off_sq);
+    unsigned long long* fixc = reinterpret_cast<unsigned long long*>(w + L.off_fixc);
+    unsigned long long* fixl = reinterpret_cast<unsigned long long*>(w + L.off_fixl);
+    int rc = tc_pack(a, head, n_a, n_x, hi, lo, sq, s);
     if (rc) return rc;
-
-    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    const bool dist = a.model == KGE_TRANSE;
+    if (dist) {
+        cudaError_t e = cudaMemsetAsync(fixc, 0, 8, s);
+        if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(fix counter)");
+    }
+    // n_neg rows need 16-byte row pitch in the output only for vector stores; tensor maps need dim % 4 == 0 (checked)
+    CUtensorMap mah, mal, mbh, mbl;
     const uint64_t ld = static_cast<uint64_t>(a.dim) * 4;
-    if ((rc = make_tensor_map_2d(&ma_hi, hi, 4, n_a, a.dim, ld, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_2d(&ma_lo, lo, 4, n_a, a.dim, ld, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_2d(&mb_hi, hi + n_a * a.dim, 4, n_x, a.dim, ld, UM_BN, UM_BK))) return rc;
-    if ((rc = make_tensor_map_2d(&mb_lo, lo + n_a * a.dim, 4, n_x, a.dim, ld, UM_BN, UM_BK))) return rc;
+    const int bn = a.n_neg >= 128 ? 128 : pick_bn(a.n_neg);
+    if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bn, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bn, UM_BK))) return rc;
+    GemmTc p;
+    memset(&p, 0, sizeof(p));
+    p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0;
+    p.ep = dist ? EP_DIST : EP_STORE;
+    p.out = a.negs; p.out_ld = a.n_neg; p.out_batch_rows = a.chunk;
+    p.sq_a = sq; p.sq_b = sq + n_a; p.fix_count = fixc; p.fix_list = fixl; p.fix_cap = L.fix_cap;
+    if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
+    if (dist) {
+        if (a.dtype == KGE_F32) rc = a.id_bits == 64 ? tc_fixup_go<float, int64_t>(a, head, fixc, fixl, L.fix_cap, s)
+                                                     : tc_fixup_go<float, int32_t>(a, head, fixc, fixl, L.fix_cap, s);
+        else rc = a.id_bits == 64 ? tc_fixup_go<__nv_bfloat16, int64_t>(a, head, fixc, fixl, L.fix_cap, s)
+                                  : tc_fixup_go<__nv_bfloat16, int32_t>(a, head, fixc, fixl, L.fix_cap, s);
+        if (rc) return rc;
+        ScoreArgs g = a;                    // exact kernel behind a device-side guard: runs only if the list overflowed
+        g.guard = fixc; g.guard_cap = L.fix_cap;
+        rc = launch_pair_forward(g, head, s);
+    }
+    return rc;
+}
 
-    cudaError_t e = cudaFuncSetAttribute(umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_SMEM_BYTES);
-    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_pair_kernel)");
-    UmmaParams p;
-    p.rows_a = a.chunk; p.rows_b = a.n_neg; p.k = a.dim; p.out = a.negs;
-    p.sq_a = sq; p.sq_b = sq + n_a; p.dist = (a.model == KGE_TRANSE) ? 1 : 0;
-    p.err = device_error_word();
-    if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
-    const dim3 grid((a.n_neg + UM_BN - 1) / UM_BN, (a.chunk + UM_BM - 1) / UM_BM, (unsigned)n_chunks);
-    umma_pair_kernel<<<grid, 192, UM_SMEM_BYTES, s>>>(ma_hi, ma_lo, mb_hi, mb_lo, p);
-    KGE_LAUNCH_CHECK("umma_pair_kernel");
-    return 0;
+// Backward contractions.  anchors_out: (batch, dim) fp32 anchor-gradient rows GA; g_neg rows are written to a.g_neg.
+// ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 1).
+int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (a.batch <= 0 || a.n_neg <= 0) return 0;
+    if (a.dim % 4 != 0 || a.n_neg % 4 != 0) {
+        set_error("the tensor-core backward needs dim %% 4 == 0 and n_neg %% 4 == 0, got %d and %d", a.dim, a.n_neg);
+        return KGE_E_UNSUPPORTED;
+    }
+    const long long n_chunks = a.batch / a.chunk;
+    const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, true);
+    if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = static_cast<char*>(ws);
+    float* hi = reinterpret_cast<float*>(w + L.off_hi);
+    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    float* whi = reinterpret_cast<float*>(w + L.off_whi);
+    float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
+    float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
+    float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
+    const bool dist = a.model == KGE_TRANSE;
+    int rc = tc_pack(a, head, n_a, n_x, hi, lo, nullptr, s);
+    if (rc) return rc;
+    {
+        const int wpb = 8;
+        const unsigned blocks = (unsigned)((a.batch + wpb - 1) / wpb);
+        if (dist) tc_pack_w_kernel<true><<<blocks, wpb * 32, 0, s>>>(a.dneg, a.negs, a.batch, a.n_neg, whi, wlo, rowsum);
+        else tc_pack_w_kernel<false><<<blocks, wpb * 32, 0, s>>>(a.dneg, nullptr, a.batch, a.n_neg, whi, wlo, rowsum);
+        KGE_LAUNCH_CHECK("tc_pack_w_kernel");
+        if (dist) {
+            const dim3 g((a.n_neg + 255) / 256, (unsigned)n_chunks);
+            tc_colsum_kernel<<<g, 256, 0, s>>>(whi, wlo, a.chunk, a.n_neg, a.batch, colsum);
+            KGE_LAUNCH_CHECK("tc_colsum_kernel");
+        }
+    }
+    const uint64_t ld = static_cast<uint64_t>(a.dim) * 4, lw = static_cast<uint64_t>(a.n_neg) * 4;
+    const int bn = pick_bn(a.dim);
+    CUtensorMap mah, mal, mbh, mbl;
+    // GA = W . X : A = W K-major (rows i, K = j), B = X MN-major (N = dim, K rows = j)
+    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
+    GemmTc p;
+    memset(&p, 0, sizeof(p));
+    p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = bn; p.a_mn = 0; p.b_mn = 1;
+    p.ep = dist ? EP_RANK1 : EP_STORE;
+    p.out = ga; p.out_ld = a.dim; p.out_batch_rows = a.chunk;
+    p.scale = rowsum; p.y_hi = hi; p.y_lo = lo;
+    if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
+    // GX = W^T . A : A-operand = W MN-major (M = j, K rows = i), B = anchors MN-major (N = dim, K rows = i)
+    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BK, 32, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BK, 32, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
+    memset(&p, 0, sizeof(p));
+    p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = bn; p.a_mn = 1; p.b_mn = 1;
+    p.ep = dist ? EP_RANK1 : EP_STORE;
+    p.out = a.g_neg; p.out_ld = a.dim; p.out_batch_rows = a.n_neg;
+    p.scale = colsum; p.y_hi = hi + n_a * a.dim; p.y_lo = lo + n_a * a.dim;
+    return run_gemm(mah, mal, mbh, mbl, p, n_chunks, s);
 }
 
 }  // namespace kge

@@ -50,6 +50,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -116,9 +122,22 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
     d |= static_cast<uint64_t>(2) << 61;                        // bits [61,64) SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: fp32 accumulate, A/B format (0 f16, 1 bf16, 2 tf32), both K-major, M x N.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_format, uint32_t M, uint32_t N) {
-    return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+// MN-major operand of a 32-bit type: the only shared-memory layout the tensor core accepts is the 128-byte swizzle
+// with 32-byte atoms (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): 32 fp32 (128 bytes) contiguous along M/N per
+// K-row, swizzle groups of 4 K-rows (512 bytes, stride byte offset), "slabs" of 32 M/N-columns `slab_bytes` apart
+// (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t slab_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((slab_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>(512 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(1) << 61;                        // SWIZZLE_128B_BASE32B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, A/B format (0 f16, 1 bf16, 2 tf32), operand majors (0 K, 1 MN), M x N.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_format, uint32_t M, uint32_t N, uint32_t a_mn = 0, uint32_t b_mn = 0) {
+    return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
 }  // namespace umma
@@ -127,5 +146,9 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_format, uint32_t M
 // (box_cols * elem_bytes must be 128), out-of-range elements read as zero.  elem_bytes 4 (fp32) or 2 (bf16).
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols);
+// 3-D variant: (batch, rows, cols) with a (1, box_rows, box_cols) box; rows beyond a batch's extent read as zero.
+int make_tensor_map_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t batch, uint64_t rows, uint64_t cols,
+                       uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                       bool atom32 = false);
 
 }  // namespace kge

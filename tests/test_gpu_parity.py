@@ -85,7 +85,7 @@ def test_score_forward_chunk_shared(model, d, chunk, nchunks, nn, head):
     assert rel_err(negs.reshape(len(rpos), -1).cpu().numpy(), rneg) < FP32_TOL
 
 
-@pytest.mark.parametrize("model", ["DistMult", "ComplEx", "RESCAL"])
+@pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx", "RESCAL"])
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (64, 128, 2, 256, 0), (400, 256, 2, 384, 0),
                                                      (200, 130, 2, 150, 1), (36, 7, 3, 9, 0), (512, 1024, 1, 1024, 0)])
 def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
@@ -108,6 +108,53 @@ def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
     assert torch.equal(negs, negs2)
 
 
+@pytest.mark.parametrize("frac,overflow", [(0.004, False), (0.05, False), (0.5, True)])
+def test_transe_tensor_cores_cancellation(frac, overflow):
+    """TransE on the tensor cores uses |a|^2+|x|^2-2a.x; negatives that (nearly) coincide with the anchor cancel there
+    and must come out exact through the fix-up list - or, when the list overflows, through the exact kernel."""
+    from cuke_b200 import scoring
+    d, chunk, nchunks, nn = 128, 256, 2, 512
+    p = make_problem("TransE", seed=5, ne=4000, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk)
+    g = p["g"]
+    E, R = p["E"], p["R"]
+    # plant rows equal (or within 1e-3 relative) to anchors h + r of triples of the same chunk
+    n_plant = int(frac * nn)
+    for c in range(nchunks):
+        for k in range(n_plant):
+            i = c * chunk + int(g.integers(0, chunk))
+            anchor = E[p["h"][i]] + R[p["r"][i]]
+            row = 3000 + (c * n_plant + k) % 1000
+            E[row] = anchor * (1.0 + (1e-3 * g.standard_normal(d)).astype(np.float32) * (k % 2))
+            p["neg"][c, k] = row
+    if overflow:          # every negative row within 1e-3 of every anchor: all pairs cancel, the fix-up list overflows
+        anchor0 = E[p["h"][0]] + R[p["r"][0]]
+        E[3000:4000] = anchor0[None, :] * (1.0 + 1e-3 * g.standard_normal((1000, d))).astype(np.float32)
+        p["h"][:] = p["h"][0]; p["r"][:] = p["r"][0]
+        p["neg"][:] = g.integers(3000, 4000, p["neg"].shape)
+    sc = gpu_scorer(p, 0, precision="tensor")
+    pos, negs, _ = sc.forward(*gpu_ids(p))
+    assert scoring.device_flags() == 0
+    rpos, rneg = oracle.scores("TransE", E, R, None, p["h"], p["r"], p["t"], p["neg"], "chunk_shared", 0, chunk)
+    got = negs.reshape(len(rpos), -1).cpu().numpy()
+    assert rel_err(got, rneg) < FP32_TOL
+    small = np.abs(rneg) < (2.0 if overflow else 0.05) * np.abs(rneg).max()   # the cancelling entries, on their own scale
+    assert small.any()
+    assert np.abs(got[small] - rneg[small]).max() <= 1e-4 * max(np.abs(rneg[small]).max(), 1e-6) + 1e-6
+
+
+@pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx", "RESCAL"])
+@pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
+                                                     (36, 7, 4, 12, 0), (512, 512, 1, 1024, 0)])
+def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
+    from cuke_b200 import scoring
+    if model == "RESCAL":
+        head = 0
+        d = min(d, 200)
+    p = make_problem(model, seed=11 * d + chunk, ne=600, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    _check_grads(p, nn if head else 0, chunk, precision="tensor")
+    assert scoring.device_flags() == 0
+
+
 @pytest.mark.parametrize("model", ["TransE", "TransH", "DistMult", "ComplEx", "RESCAL", "TransR"])
 def test_score_forward_bf16(model):
     d = 200 if model != "ComplEx" else 256
@@ -124,9 +171,9 @@ def test_score_forward_bf16(model):
 
 
 # ---- gradients -------------------------------------------------------------------------------------------------
-def _check_grads(p, nnh, chunk, bf16=False, tol=FP32_TOL):
+def _check_grads(p, nnh, chunk, bf16=False, tol=FP32_TOL, precision="fp32"):
     model = p["model"]
-    sc = gpu_scorer(p, nnh, bf16=bf16)
+    sc = gpu_scorer(p, nnh, bf16=bf16, precision=precision)
     h, r, t, neg = gpu_ids(p)
     g = p["g"]
     B = len(p["h"])
