@@ -243,7 +243,7 @@ int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t*
     const char* fn = "kge_segment_reduce";
     if (n < 0 || n > 2147483647LL || n_out < 0) { set_error("%s: bad sizes", fn); return KGE_E_RANGE; }
     if (dim <= 0 || dim > 1024) { set_error("%s: dim %d outside [1, 1024]", fn, dim); return KGE_E_UNSUPPORTED; }
-    if (n_out > 0) KGE_REQUIRE_PTR(out, "out");
+    if (n_out > 0 || n > 0) KGE_REQUIRE_PTR(out, "out");
     if (n > 0) {
         KGE_REQUIRE_PTR(rows, "rows"); KGE_REQUIRE_PTR(perm, "perm"); KGE_REQUIRE_PTR(seg, "seg");
         KGE_REQUIRE_PTR(n_unique, "n_unique"); KGE_REQUIRE_PTR(workspace, "workspace");

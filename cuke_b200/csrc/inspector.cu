@@ -218,28 +218,49 @@ __global__ void __launch_bounds__(256) segred_window_kernel(const float* rows, i
     (void)piece_start;
 }
 
-// One warp per window boundary b (between windows b and b+1): if a segment crosses it and starts in window b,
-// this warp sums trail[b] + lead[b+1] + ... + lead[last] in order.
+// One CTA per window boundary b (between windows b and b+1): if a segment crosses it and starts in window b, the
+// CTA sums trail[b] + lead[b+1] + ... + lead[last].  Warp w takes parts w, w+8, ... in order, then warp 0 adds the
+// eight partial rows in order: a fixed summation order, and the hottest row of a Zipf batch (hundreds of windows)
+// is spread over eight warps instead of one.
 template <int NV, bool VEC>
 __global__ void __launch_bounds__(256) segred_span_kernel(int dim, long long n, const int* seg, const long long* n_unique,
                                                           float* out, const float* lead, const float* trail) {
-    const int lane = threadIdx.x & 31;
-    const long long b = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    extern __shared__ __align__(16) float part[];          // 8 x dim
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const long long b = blockIdx.x;
     const long long edge = (b + 1) * 32;            // first position of window b+1
     if (edge >= n) return;
     const int U = (int)*n_unique;
     const int u = seg_of_position(seg, U, (int)edge - 1);
     const int s = seg[u], e = seg[u + 1];
-    if (e <= edge || s < b * 32) return;            // does not cross here, or started in an earlier window
+    if (e <= edge || s < b * 32) return;            // does not cross here, or started in an earlier window (block-uniform)
+    const long long parts = (e - 1) / 32 - b + 1;   // part 0 = trail[b], part k = lead[b + k]
     Row<NV> acc, x;
-    load_row_f32<NV, VEC>(acc, trail + b * dim, dim, lane);
-    const long long last = (e - 1) / 32;
-    for (long long w = b + 1; w <= last; ++w) {
-        load_row_f32<NV, VEC>(x, lead + w * dim, dim, lane);
+    row_zero<NV>(acc);
+    for (long long k = w; k < parts; k += 8) {
+        load_row_f32<NV, VEC>(x, (k == 0 ? trail + b * dim : lead + (b + k) * dim), dim, lane);
 #pragma unroll
         for (int q = 0; q < NV; ++q) acc.v[q] = acc.v[q] + x.v[q];
     }
-    store_row<NV, VEC>(out + (long long)u * dim, acc, dim, lane);
+    store_row<NV, VEC>(part + w * dim, acc, dim, lane);
+    __syncthreads();
+    if (w == 0) {      // shared-memory reads: plain loads (the row helpers use the read-only global path)
+        row_zero<NV>(acc);
+        for (int k = 0; k < 8; ++k) {
+            const float* pr = part + k * dim;
+#pragma unroll
+            for (int q = 0; q < NV; ++q) {
+                const int e0 = 4 * (lane + 32 * q);
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e0 + 0 < dim) v.x = pr[e0 + 0];
+                if (e0 + 1 < dim) v.y = pr[e0 + 1];
+                if (e0 + 2 < dim) v.z = pr[e0 + 2];
+                if (e0 + 3 < dim) v.w = pr[e0 + 3];
+                acc.v[q] = acc.v[q] + v;
+            }
+        }
+        store_row<NV, VEC>(out + (long long)u * dim, acc, dim, lane);
+    }
 }
 
 __global__ void zero_tail_rows_kernel(float* out, int dim, const long long* n_unique, long long n_out) {
@@ -359,13 +380,27 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(
 __global__ void __launch_bounds__(256) loss_partial_kernel(const float* pos, long long n_pos, const float* neg, long long n_neg,
                                                            float neg_w, float* dpos, float* dneg, float* partial) {
     __shared__ float red[256];
-    const long long total = n_pos + n_neg;
-    const long long per = (total + gridDim.x - 1) / gridDim.x;
-    const long long lo = (long long)blockIdx.x * per, hi = min(total, lo + per);
+    // each block owns a contiguous slice of quads of `neg` (and of `pos`), so the partial sums have a fixed order
+    const bool vec = (n_neg % 4 == 0) && ((reinterpret_cast<uintptr_t>(neg) | reinterpret_cast<uintptr_t>(dneg)) & 15u) == 0;
     float s = 0.f;
-    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        if (i < n_pos) { float x = pos[i]; s += softplusf(-x); dpos[i] = -sigmoidf(-x); }
-        else { float x = neg[i - n_pos]; s += neg_w * softplusf(x); dneg[i - n_pos] = neg_w * sigmoidf(x); }
+    {
+        const long long per = (n_pos + gridDim.x - 1) / gridDim.x;
+        const long long lo = (long long)blockIdx.x * per, hi = min(n_pos, lo + per);
+        for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) { const float x = pos[i]; s += softplusf(-x); dpos[i] = -sigmoidf(-x); }
+    }
+    if (vec) {
+        const long long nq = n_neg / 4;
+        const long long per = (nq + gridDim.x - 1) / gridDim.x;
+        const long long lo = (long long)blockIdx.x * per, hi = min(nq, lo + per);
+        for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(neg) + i);
+            s += neg_w * ((softplusf(x.x) + softplusf(x.y)) + (softplusf(x.z) + softplusf(x.w)));
+            reinterpret_cast<float4*>(dneg)[i] = make_float4(neg_w * sigmoidf(x.x), neg_w * sigmoidf(x.y), neg_w * sigmoidf(x.z), neg_w * sigmoidf(x.w));
+        }
+    } else {
+        const long long per = (n_neg + gridDim.x - 1) / gridDim.x;
+        const long long lo = (long long)blockIdx.x * per, hi = min(n_neg, lo + per);
+        for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) { const float x = neg[i]; s += neg_w * softplusf(x); dneg[i] = neg_w * sigmoidf(x); }
     }
     red[threadIdx.x] = s;
     __syncthreads();
@@ -468,10 +503,14 @@ static int segred_go(const float* rows, int dim, long long n, const int* perm, c
     const unsigned blocks = (unsigned)((nwin + wpb - 1) / wpb);
     segred_window_kernel<NV, VEC><<<blocks, wpb * 32, 0, s>>>(rows, dim, n, perm, seg, n_unique, out, lead, trail);
     KGE_LAUNCH_CHECK("segred_window_kernel");
-    segred_span_kernel<NV, VEC><<<blocks, wpb * 32, 0, s>>>(dim, n, seg, n_unique, out, lead, trail);
-    KGE_LAUNCH_CHECK("segred_span_kernel");
-    zero_tail_rows_kernel<<<296, 256, 0, s>>>(out, dim, n_unique, n_out);
-    KGE_LAUNCH_CHECK("zero_tail_rows_kernel");
+    if (nwin > 1) {
+        segred_span_kernel<NV, VEC><<<(unsigned)(nwin - 1), 256, 8 * dim * sizeof(float), s>>>(dim, n, seg, n_unique, out, lead, trail);
+        KGE_LAUNCH_CHECK("segred_span_kernel");
+    }
+    if (n_out > 0) {
+        zero_tail_rows_kernel<<<296, 256, 0, s>>>(out, dim, n_unique, n_out);
+        KGE_LAUNCH_CHECK("zero_tail_rows_kernel");
+    }
     return 0;
 }
 

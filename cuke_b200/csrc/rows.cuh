@@ -23,10 +23,21 @@ __device__ __forceinline__ void store_row(float* row, const Row<NV>& x, int dim,
 }
 template <int NV, bool VEC>
 __device__ __forceinline__ void add_row(float* row, const Row<NV>& x, int dim, int lane) {
+    // read-modify-write of a row this warp wrote earlier in the same kernel: coherent (plain) loads, not the read-only path
 #pragma unroll
     for (int q = 0; q < NV; ++q) {
-        float4 o = load_quad<float, VEC>(row, lane + 32 * q, dim);   // own row, written earlier by this warp
-        store_quad<VEC>(row, lane + 32 * q, dim, o + x.v[q]);
+        const int k = 4 * (lane + 32 * q);
+        if (VEC) {
+            if (k < dim) {
+                float4* p = reinterpret_cast<float4*>(row + k);
+                *p = *p + x.v[q];
+            }
+        } else {
+            if (k + 0 < dim) row[k + 0] += x.v[q].x;
+            if (k + 1 < dim) row[k + 1] += x.v[q].y;
+            if (k + 2 < dim) row[k + 2] += x.v[q].z;
+            if (k + 3 < dim) row[k + 3] += x.v[q].w;
+        }
     }
 }
 template <int NV> __device__ __forceinline__ float row_dot(const Row<NV>& a, const Row<NV>& b) {

@@ -165,7 +165,15 @@ struct GemmTc {
     int32_t* err;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__device__ __forceinline__ float sqrt_approx(float x) {       // MUFU square root, relative error ~2^-23
+    float r;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+constexpr int UM_THREADS = 320;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2..9: epilogue
+
+__global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
@@ -256,8 +264,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             umma::mma_commit(acc_ready);              // accumulator complete (or abandoned)
         }
     } else {
-        // ---- epilogue: warps 2..5 own TMEM lane quarters (warp % 4) ----------------------------------------------------
+        // ---- epilogue: a warp may only read the TMEM lane quarter (warp % 4); two warps share each quarter and take
+        //      alternate 32-column chunks ---------------------------------------------------------------------------------
         const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = q * 32 + lane;                 // row of the tile held by this thread
         const bool ok = umma::mbar_wait(acc_ready, 0);
         if (!ok && lane == 0) atomicOr(p.err, 2);
@@ -270,7 +280,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
         const int n_chunks32 = (p.bn + 31) / 32;
 #pragma unroll 1
-        for (int c = 0; c < n_chunks32; ++c) {
+        for (int c = half; c < n_chunks32; c += 2) {
             float v[32];
             umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);   // warp-collective
             if (!row_ok) continue;
@@ -288,7 +298,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                             const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
                             if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + (nbase + j);
                         }
-                        v[j] = -sqrtf(fmaxf(d2, 0.f));
+                        v[j] = -sqrt_approx(fmaxf(d2, 0.f));
                     }
                 }
             } else if (p.ep == EP_RANK1) {
@@ -446,7 +456,7 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     const int b_bytes = p.b_mn ? ((p.bn + 31) / 32) * UM_SLAB_BYTES : p.bn * 128;
     const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + 256;
     const dim3 grid((p.n_cols + p.bn - 1) / p.bn, (p.m_rows + UM_BM - 1) / UM_BM, (unsigned)batch);
-    umma_gemm_kernel<<<grid, 192, smem, s>>>(ah, al, bh, bl, p);
+    umma_gemm_kernel<<<grid, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
     KGE_LAUNCH_CHECK("umma_gemm_kernel");
     return 0;
 }

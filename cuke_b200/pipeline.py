@@ -128,10 +128,10 @@ class KgeStep:
             if not backward:
                 continue
             sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
-            grad_rows = scoring.segment_reduce(sg.ent_slots, insp)            # aligned with insp.uniq
+            grad_rows = scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)     # aligned with insp.uniq
             if rinsp is None:
                 rinsp = scoring.inspect(r32, self.n_rel[m])
-            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp)
+            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp, zero_tail=False)
             dense_rel = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
             scoring.scatter_rows(rel_rows, rinsp.uniq, dense_rel, n_dev=rinsp.n_unique)
             if self.exchange is None:

@@ -150,8 +150,9 @@ def fma_peak_tflops(device=None, iters: int = 4096) -> float:
 
 
 def segment_reduce(rows: torch.Tensor, insp: Inspection, out: Optional[torch.Tensor] = None,
-                   n_out: Optional[int] = None) -> torch.Tensor:
-    """One fp32 row per distinct id: out[u] = sum of rows[slot] over the slots holding uniq[u] (fixed order)."""
+                   n_out: Optional[int] = None, zero_tail: bool = True) -> torch.Tensor:
+    """One fp32 row per distinct id: out[u] = sum of rows[slot] over the slots holding uniq[u] (fixed order).
+    Rows of `out` past the number of distinct ids are zero-filled unless zero_tail is False."""
     _need_cuda(rows)
     n, dim = rows.shape
     if n != insp.n:
@@ -162,7 +163,7 @@ def segment_reduce(rows: torch.Tensor, insp: Inspection, out: Optional[torch.Ten
     need = L.kge_segment_reduce_workspace_bytes(n, dim)
     ws = workspace(need, rows.device, "segred")
     check(L.kge_segment_reduce(_ptr(rows), dim, n, _ptr(insp.perm), _ptr(insp.seg), _ptr(insp.n_unique), _ptr(out),
-                               out.shape[0], _ptr(ws), ws.numel(), _stream()))
+                               out.shape[0] if zero_tail else 0, _ptr(ws), ws.numel(), _stream()))
     return out
 
 

@@ -189,8 +189,8 @@ KGE_API int kge_scatter_rows(const float* rows, int32_t dim, const int64_t* ids,
                              int64_t first_row, float* out, kge_stream_t stream);
 
 /* Segmented sum: out[u][:] = sum over sorted positions p in [seg[u], seg[u+1]) of rows[perm[p]][:],
- * added in ascending p (deterministic, no atomics).  rows (n, dim) fp32; out (n_out, dim) fp32 where
- * n_out >= U; rows u in [U, n_out) are zero-filled.  The backward "scatter-add" of per-slot gradient rows
+ * added in a fixed order (deterministic, no atomics).  rows (n, dim) fp32; out fp32 with room for
+ * max(U, n_out) rows (n rows always suffice); rows u in [U, n_out) are zero-filled, n_out = 0 skips that.  The backward "scatter-add" of per-slot gradient rows
  * into one row per distinct id (replaces the un-aggregated outputs of apps/kge/kge.py:393-515). */
 KGE_API size_t kge_segment_reduce_workspace_bytes(int64_t n, int32_t dim);
 KGE_API int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t* perm, const int32_t* seg,
