@@ -62,6 +62,8 @@ SIGNATURES = {
     "kge_legacy_inspect": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "kge_gather_rows": (C.c_int, [_vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp]),
     "kge_scatter_rows": (C.c_int, [_vp, _i32, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "kge_profile_gemm": (C.c_int, [_i32]),
+    "kge_profile_gemm_read": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
     "kge_probe_fma": (C.c_int, [_vp, _i32, _i32, C.POINTER(C.c_double), _vp]),
     "kge_segment_reduce_workspace_bytes": (_sz, [_i64, _i32]),
     "kge_segment_reduce": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _vp]),

@@ -56,8 +56,13 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s);
 int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
+size_t transr_backward_workspace_bytes(const kge_problem* p);
+int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const float* pos, const float* negs, const float* dpos,
+                           const float* dneg, const kge_grads* g, void* ws, cudaStream_t s);
 size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int backward);
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
+void gemm_profile_enable(int on);
+int gemm_profile_read(double* ms, long long* launches, double* flops);
 int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, size_t ws_bytes, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
@@ -255,6 +260,7 @@ int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t*
 size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
     if (!p || p->batch <= 0) return 256;
     const size_t rb = rows_bytes(p);
+    if (backward && p->model == KGE_TRANSR) return transr_backward_workspace_bytes(p) + 256;
     if (backward) return 3 * rb + tc_bytes(p, 1) + 256;
     return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + 256;
 }
@@ -301,13 +307,13 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     int rc = check_problem(fn, p, t, true);
     if (rc) return rc;
     if (p->batch == 0) return 0;
-    if (p->model == KGE_TRANSR) { set_error("%s: TransR backward is not available", fn); return KGE_E_UNSUPPORTED; }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }
     KGE_REQUIRE_PTR(dpos, "dpos");
     KGE_REQUIRE_PTR(g->g_head, "g_head"); KGE_REQUIRE_PTR(g->g_tail, "g_tail");
     if (p->model != KGE_RESCAL) KGE_REQUIRE_PTR(g->g_rel, "g_rel");
-    if (p->model == KGE_TRANSH || p->model == KGE_RESCAL) KGE_REQUIRE_PTR(g->g_rel2, "g_rel2");
+    if (p->model == KGE_TRANSH || p->model == KGE_RESCAL || p->model == KGE_TRANSR) KGE_REQUIRE_PTR(g->g_rel2, "g_rel2");
+    if (p->model == KGE_TRANSR) { KGE_REQUIRE_PTR(pos_score, "pos_score"); if (p->neg_mode != KGE_NEG_NONE) KGE_REQUIRE_PTR(neg_score, "neg_score"); }
     if (p->neg_mode != KGE_NEG_NONE) {
         KGE_REQUIRE_PTR(dneg, "dneg"); KGE_REQUIRE_PTR(g->g_neg, "g_neg");
         if (p->neg_mode == KGE_NEG_CHUNK_SHARED && p->model == KGE_TRANSE) KGE_REQUIRE_PTR(neg_score, "neg_score");
@@ -316,6 +322,8 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     const size_t need = kge_score_workspace_bytes(p, 1);
     KGE_REQUIRE_PTR(workspace, "workspace");
     if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    if (p->model == KGE_TRANSR)
+        return launch_transr_backward(p, t, pos_score, neg_score, dpos, dneg, g, workspace, s);
     const size_t rb = rows_bytes(p);
     float* ws0 = static_cast<float*>(workspace);                                          // anchors
     float* ws1 = reinterpret_cast<float*>(static_cast<char*>(workspace) + rb);            // chunk-shared anchor gradients
@@ -364,6 +372,14 @@ int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg, int64_t
     if (n_neg_total > 0) { KGE_REQUIRE_PTR(neg, "neg"); KGE_REQUIRE_PTR(dneg, "dneg"); }
     return launch_logistic_loss(pos, n_pos, neg, n_neg_total, neg_weight, dpos, dneg, loss_out, workspace, workspace_bytes,
                                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_profile_gemm(int32_t enable) { gemm_profile_enable(enable); return 0; }
+int kge_profile_gemm_read(double* ms, int64_t* launches, double* flops) {
+    long long n = 0;
+    int rc = gemm_profile_read(ms, &n, flops);
+    if (launches) *launches = n;
+    return rc;
 }
 
 int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank, int32_t world,

@@ -10,7 +10,7 @@
 //           g_head[i]   = GA[i] . P[r_i]^T                               (rescal_ghead_kernel)
 //           dP[g]       = sum_{i in group g} E[h_i] (x) GA[i]            (rescal_dproj_kernel)
 //   TransR  score(i,j)  = -|| (a - b) . P[r_i] + R[r_i] ||  for the positive (j = 0) and every negative
-//                                                                        (transr_fwd_kernel)
+//                                                                        (transr_fwd_kernel; backward: transr_gv/gd/dproj/reduce)
 #include "tile_gemm.cuh"
 
 namespace kge {
@@ -314,4 +314,244 @@ int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos
     return 0;
 }
 
+
+// ---- TransR backward ---------------------------------------------------------------------------------------------
+// With v = diff . P + R and score = -||v||, dL/dv = (dS / S) v.  Four launches:
+//   transr_gv_kernel      GV[row]  = (dS/S) (diff . P[r] + R[r])                       (recomputes the forward product)
+//   transr_gd_kernel      GD[row]  = GV[row] . P[r]^T ; negatives' rows go to g_neg with their sign, positives' to GD0
+//   transr_dproj_kernel   dP[g]    = sum_rows diff^T (x) GV[row]
+//   transr_reduce_kernel  per triple: g_head, g_tail from GD0 and its g_neg rows, g_rel = sum of its GV rows
+// Rows are numbered as in the forward: row = triple_in_group * (1 + n_neg) + j, GV is stored triple-major
+// (global row i * (1 + n_neg) + j) so that the per-triple pass reads contiguous rows.
+struct TransRBwd {
+    const float* pos; const float* negs; const float* dpos; const float* dneg;
+    float* gv; float* gd0; float* g_neg; float* g_head; float* g_tail; float* g_rel; float* dproj;
+};
+
+template <typename T, typename I>
+__device__ __forceinline__ void transr_row(const GroupArgs& a, int s, int per, long long row, int& i, int& j,
+                                           const T*& pa, const T*& pb) {
+    const T* E = reinterpret_cast<const T*>(a.ent);
+    i = a.rel_perm[s + (int)(row / per)];
+    j = (int)(row % per);
+    const T* hrow = E + load_id<I>(a.h, i) * a.dim;
+    const T* trow = E + load_id<I>(a.t, i) * a.dim;
+    if (j == 0) { pa = hrow; pb = trow; }
+    else {
+        const T* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * a.dim;
+        if (j - 1 < a.n_neg_head) { pa = x; pb = trow; } else { pa = hrow; pb = x; }
+    }
+}
+
+template <typename T, typename I, bool VEC>
+__global__ void __launch_bounds__(256) transr_gv_kernel(GroupArgs a, TransRBwd w) {
+    __shared__ __align__(16) TileSmem sm;
+    __shared__ float coef[TG_BM];
+    __shared__ long long grow[TG_BM];
+    const int g = blockIdx.x;
+    if (g >= *a.n_groups) return;
+    const int tid = threadIdx.x, dim = a.dim;
+    const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    const long long rid = a.rel_uniq[g];
+    const int per = 1 + a.n_neg;
+    const long long rows = (long long)(e - s) * per;
+    const T* Rv = reinterpret_cast<const T*>(a.rel) + rid * dim;
+    const T* P = reinterpret_cast<const T*>(a.proj) + rid * (long long)dim * dim;
+    for (long long m0 = (long long)blockIdx.y * TG_BM; m0 < rows; m0 += (long long)gridDim.y * TG_BM) {
+        DiffK<T, VEC> al;
+        al.dim = dim;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const long long row = m0 + (tid >> 2) + 64 * u;
+            al.a[u] = nullptr; al.b[u] = nullptr;
+            if (row < rows) { int i, j; transr_row<T, I>(a, s, per, row, i, j, al.a[u], al.b[u]); }
+        }
+        if (tid < TG_BM) {
+            const long long row = m0 + tid;
+            float c = 0.f; long long gr = -1;
+            if (row < rows) {
+                const int i = a.rel_perm[s + (int)(row / per)];
+                const int j = (int)(row % per);
+                const float sc = j == 0 ? w.pos[i] : w.negs[(long long)i * a.n_neg + (j - 1)];
+                const float ds = j == 0 ? w.dpos[i] : w.dneg[(long long)i * a.n_neg + (j - 1)];
+                c = sc != 0.f ? ds / sc : 0.f;
+                gr = (long long)i * per + j;
+            }
+            coef[tid] = c; grow[tid] = gr;
+        }
+        __syncthreads();
+        for (int n0 = 0; n0 < dim; n0 += TG_BN) {
+            MatRowsDirect<T, VEC> bl;
+            bl.base = P; bl.n_rows = dim; bl.dim = dim; bl.n0 = n0;
+            float acc[8][8];
+            tile_mainloop<OP_DOT>(al, bl, dim, sm, acc);
+            auto ep = [&](int row, int col4, float4 v) {
+                const int n = n0 + col4;
+                if (grow[row] < 0 || n >= dim) return;
+                const float4 r = load_quad<T, VEC>(Rv, n >> 2, dim);
+                const float c = coef[row];
+                store_quad<VEC>(w.gv + grow[row] * dim, n >> 2, dim,
+                                make_float4(c * (v.x + r.x), c * (v.y + r.y), c * (v.z + r.z), c * (v.w + r.w)));
+            };
+            tile_epilogue(acc, ep);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T, typename I, bool VEC>
+__global__ void __launch_bounds__(256) transr_gd_kernel(GroupArgs a, TransRBwd w) {
+    __shared__ __align__(16) TileSmem sm;
+    __shared__ int row_i[TG_BM], row_j[TG_BM];
+    const int g = blockIdx.x;
+    if (g >= *a.n_groups) return;
+    const int tid = threadIdx.x, dim = a.dim;
+    const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    const long long rid = a.rel_uniq[g];
+    const int per = 1 + a.n_neg;
+    const long long rows = (long long)(e - s) * per;
+    const T* P = reinterpret_cast<const T*>(a.proj) + rid * (long long)dim * dim;
+    for (long long m0 = (long long)blockIdx.y * TG_BM; m0 < rows; m0 += (long long)gridDim.y * TG_BM) {
+        GatherK<float, VEC> al;
+        al.dim = dim;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const long long row = m0 + (tid >> 2) + 64 * u;
+            al.row[u] = nullptr;
+            if (row < rows) {
+                const int i = a.rel_perm[s + (int)(row / per)];
+                al.row[u] = w.gv + ((long long)i * per + (row % per)) * dim;
+            }
+        }
+        if (tid < TG_BM) {
+            const long long row = m0 + tid;
+            row_i[tid] = row < rows ? a.rel_perm[s + (int)(row / per)] : -1;
+            row_j[tid] = (int)(row % per);
+        }
+        __syncthreads();
+        for (int n0 = 0; n0 < dim; n0 += TG_BN) {
+            MatRowsK<T, VEC> bl;
+            bl.base = P; bl.n_rows = dim; bl.dim = dim; bl.n0 = n0;
+            float acc[8][8];
+            tile_mainloop<OP_DOT>(al, bl, dim, sm, acc);
+            auto ep = [&](int row, int col4, float4 v) {
+                const int n = n0 + col4, i = row_i[row], j = row_j[row];
+                if (i < 0 || n >= dim) return;
+                if (j == 0) store_quad<VEC>(w.gd0 + (long long)i * dim, n >> 2, dim, v);
+                else {
+                    if (j - 1 >= a.n_neg_head) v = make_float4(-v.x, -v.y, -v.z, -v.w);     // diff = h - x: dL/dx = -GD
+                    store_quad<VEC>(w.g_neg + ((long long)i * a.n_neg + (j - 1)) * dim, n >> 2, dim, v);
+                }
+            };
+            tile_epilogue(acc, ep);
+        }
+        __syncthreads();
+    }
+}
+
+// A(m, k) = diff(row k)[m0 + m]; rows of one relation group, numbered as in the forward.
+template <typename T, typename I, bool VEC>
+struct DiffColsDirect {
+    static constexpr bool K_CONTIG = false;
+    GroupArgs a; int s; int per; long long rows; int m0;
+    __device__ __forceinline__ float4 get(int r4, int k) const {
+        if (k >= rows) return f4(0.f);
+        int i, j; const T* pa; const T* pb;
+        transr_row<T, I>(a, s, per, k, i, j, pa, pb);
+        return load_quad<T, VEC>(pa, (m0 + r4) >> 2, a.dim) - load_quad<T, VEC>(pb, (m0 + r4) >> 2, a.dim);
+    }
+};
+// B(k, n) = GV[global row of group row k][n0 + n]
+template <bool VEC>
+struct GvRowsDirect {
+    static constexpr bool K_CONTIG = false;
+    const float* gv; const int* perm; int per; long long rows; int dim; int n0;
+    __device__ __forceinline__ float4 get(int r4, int k) const {
+        if (k >= rows) return f4(0.f);
+        const long long gr = (long long)perm[k / per] * per + (k % per);
+        return load_quad<float, VEC>(gv + gr * dim, (n0 + r4) >> 2, dim);
+    }
+};
+
+template <typename T, typename I, bool VEC>
+__global__ void __launch_bounds__(256) transr_dproj_kernel(GroupArgs a, TransRBwd w) {
+    __shared__ __align__(16) TileSmem sm;
+    const int g = blockIdx.x;
+    if (g >= *a.n_groups) return;
+    const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.z * TG_BN, dim = a.dim;
+    const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    const int per = 1 + a.n_neg;
+    const long long rows = (long long)(e - s) * per;
+    DiffColsDirect<T, I, VEC> al;
+    al.a = a; al.s = s; al.per = per; al.rows = rows; al.m0 = m0;
+    GvRowsDirect<VEC> bl;
+    bl.gv = w.gv; bl.perm = a.rel_perm + s; bl.per = per; bl.rows = rows; bl.dim = dim; bl.n0 = n0;
+    float acc[8][8];
+    tile_mainloop<OP_DOT>(al, bl, (int)rows, sm, acc);
+    float* out = w.dproj + (long long)g * dim * dim;
+    auto ep = [&](int row, int col4, float4 v) {
+        const int m = m0 + row, n = n0 + col4;
+        if (m >= dim || n >= dim) return;
+        store_quad<VEC>(out + (long long)m * dim, n >> 2, dim, v);
+    };
+    tile_epilogue(acc, ep);
+}
+
+// One warp per triple: g_head = GD0 - sum of its tail-replaced g_neg rows, g_tail = -GD0 - sum of its head-replaced
+// g_neg rows, g_rel = sum of its GV rows; all in ascending j.
+__global__ void __launch_bounds__(256) transr_reduce_kernel(long long batch, int dim, int n_neg, int n_neg_head, TransRBwd w) {
+    const int lane = threadIdx.x & 31;
+    const long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= batch) return;
+    const int per = 1 + n_neg;
+    for (int k = lane; k < dim; k += 32) {
+        const float g0 = w.gd0[i * dim + k];
+        float gh = g0, gt = -g0, gr = w.gv[(i * per) * dim + k];
+        for (int j = 0; j < n_neg; ++j) {
+            const float gx = w.g_neg[(i * n_neg + j) * dim + k];
+            if (j < n_neg_head) gt -= gx; else gh -= gx;
+            gr += w.gv[(i * per + 1 + j) * dim + k];
+        }
+        w.g_head[i * dim + k] = gh;
+        w.g_tail[i * dim + k] = gt;
+        w.g_rel[i * dim + k] = gr;
+    }
+}
+
+size_t transr_backward_workspace_bytes(const kge_problem* p) {
+    const size_t rows = (size_t)p->batch * (1 + (p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg));
+    return (rows * p->dim * 4 + 255) / 256 * 256 + ((size_t)p->batch * p->dim * 4 + 255) / 256 * 256;
+}
+
+int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const float* pos, const float* negs, const float* dpos,
+                           const float* dneg, const kge_grads* g, void* ws, cudaStream_t s) {
+    if (p->batch <= 0) return 0;
+    GroupArgs a = group_args(p, t);
+    if (p->neg_mode == KGE_NEG_NONE) { a.n_neg = 0; a.n_neg_head = 0; }
+    const size_t rows = (size_t)p->batch * (1 + a.n_neg);
+    TransRBwd w;
+    w.pos = pos; w.negs = negs; w.dpos = dpos; w.dneg = dneg;
+    w.gv = static_cast<float*>(ws);
+    w.gd0 = reinterpret_cast<float*>(static_cast<char*>(ws) + (rows * p->dim * 4 + 255) / 256 * 256);
+    w.g_neg = g->g_neg; w.g_head = g->g_head; w.g_tail = g->g_tail; w.g_rel = g->g_rel; w.dproj = g->g_rel2;
+    const unsigned nt = (p->dim + TG_BN - 1) / TG_BN;
+    const dim3 grid_rows(group_bound(p), 8);
+    const dim3 grid_dp(group_bound(p), nt, nt);
+#define KGE_CALL(T, I, V) transr_gv_kernel<T, I, V><<<grid_rows, 256, 0, s>>>(a, w)
+    KGE_TI_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+    KGE_LAUNCH_CHECK("transr_gv_kernel");
+#define KGE_CALL(T, I, V) transr_gd_kernel<T, I, V><<<grid_rows, 256, 0, s>>>(a, w)
+    KGE_TI_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+    KGE_LAUNCH_CHECK("transr_gd_kernel");
+#define KGE_CALL(T, I, V) transr_dproj_kernel<T, I, V><<<grid_dp, 256, 0, s>>>(a, w)
+    KGE_TI_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+    KGE_LAUNCH_CHECK("transr_dproj_kernel");
+    const int wpb = 8;
+    transr_reduce_kernel<<<(unsigned)((p->batch + wpb - 1) / wpb), wpb * 32, 0, s>>>(p->batch, p->dim, a.n_neg, a.n_neg_head, w);
+    KGE_LAUNCH_CHECK("transr_reduce_kernel");
+    return 0;
+}
 }  // namespace kge

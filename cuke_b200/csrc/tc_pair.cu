@@ -11,7 +11,8 @@
 //     ring; an operand is used K-major (rows of 32 k-values) or MN-major (32 m/n-values per k-row) as it lies in
 //     memory, so W, X and A are never transposed;
 //   * one elected thread issues tcgen05.mma kind::tf32 for lo*hi + hi*lo + hi*hi into an fp32 accumulator in tensor
-//     memory; four epilogue warps read it back with tcgen05.ld and apply the scorer's epilogue.
+//     memory; eight epilogue warps read it back with tcgen05.ld and apply the scorer's epilogue; the kernel is
+//     persistent with two accumulators, so that epilogue overlaps the next tile's main loop.
 //   The split makes products exact to ~2^-20 relative, inside the 1e-4 tolerance of the fp32 path (a single tf32
 //   pass, 2^-11, would not be).  TransE's distance uses |a|^2 + |x|^2 - 2 a.x; entries where that form cancels
 //   (d^2 < 2^-6 (|a|^2 + |x|^2)) are listed by the epilogue and recomputed exactly from the rows by a fix-up kernel;
@@ -152,6 +153,7 @@ enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2 };
 
 struct GemmTc {
     int m_rows, n_cols, k_len;        // extents per batch
+    int batch;
     int bn;                           // tile width (multiple of 16, <= 256)
     int a_mn, b_mn;                   // operand majors: 0 K-major, 1 MN-major
     int stages;
@@ -172,7 +174,11 @@ __device__ __forceinline__ float sqrt_approx(float x) {       // MUFU square roo
 }
 
 constexpr int UM_THREADS = 320;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2..9: epilogue
+constexpr int UM_EPI_WARPS = 8;
 
+// Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
+// working at the same time share A rows in L2).  Two accumulators in tensor memory alternate, so the epilogue of tile i
+// (tcgen05.ld, scorer epilogue, global stores) overlaps the TMA/MMA main loop of tile i+1.
 __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
@@ -183,17 +189,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     const int stage_bytes = 2 * UM_A_BYTES + 2 * b_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
     uint64_t* empty = full + p.stages;
-    uint64_t* acc_ready = empty + p.stages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + p.stages;          // [2] accumulator written  (MMA -> epilogue)
+    uint64_t* acc_empty = acc_full + 2;             // [2] accumulator drained  (epilogue -> MMA)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * p.bn, m0 = blockIdx.y * UM_BM, b = blockIdx.z;
     const int num_kb = (p.k_len + UM_BK - 1) / UM_BK;
-    const uint32_t tmem_cols = p.bn <= 32 ? 32u : p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
+    const uint32_t acc_cols = p.bn <= 32 ? 32u : p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
+    const uint32_t tmem_cols = 2 * acc_cols;        // <= 512, the whole tensor memory at bn > 128
+    const int tiles_n = (p.n_cols + p.bn - 1) / p.bn;
+    const int tiles_m = (p.m_rows + UM_BM - 1) / UM_BM;
+    const long long n_tiles = static_cast<long long>(tiles_n) * tiles_m * p.batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
-        umma::mbar_init(acc_ready, 1);
+        for (int s = 0; s < 2; ++s) { umma::mbar_init(&acc_full[s], 1); umma::mbar_init(&acc_empty[s], UM_EPI_WARPS); }
         umma::fence_barrier_init();
     }
     if (warp == 1) { umma::tmem_alloc(tmem_slot, tmem_cols); umma::tmem_relinquish(); }
@@ -207,30 +217,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         if (lane == 0) {
             umma::prefetch_tensormap(&map_a_hi); umma::prefetch_tensormap(&map_a_lo);
             umma::prefetch_tensormap(&map_b_hi); umma::prefetch_tensormap(&map_b_lo);
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % p.stages;
-                const uint32_t ph = (kb / p.stages) & 1;
-                if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); break; }
-                uint8_t* st = smem + s * stage_bytes;
-                uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + 2 * UM_A_BYTES, *b_lo = b_hi + b_bytes;
-                umma::mbar_expect_tx(&full[s], stage_bytes);
-                const int k0 = kb * UM_BK;
-                if (!p.a_mn) {
-                    umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, b, &full[s]);
-                    umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, b, &full[s]);
-                } else {
-                    for (int sl = 0; sl < UM_BM / 32; ++sl) {
-                        umma::tma_load_3d(a_hi + sl * UM_SLAB_BYTES, &map_a_hi, m0 + 32 * sl, k0, b, &full[s]);
-                        umma::tma_load_3d(a_lo + sl * UM_SLAB_BYTES, &map_a_lo, m0 + 32 * sl, k0, b, &full[s]);
+            long long it = 0;                      // k-blocks issued so far (ring position)
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int n0 = static_cast<int>(tile % tiles_n) * p.bn;
+                const int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
+                const int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = static_cast<int>(it % p.stages);
+                    const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                    uint8_t* st = smem + s * stage_bytes;
+                    uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + 2 * UM_A_BYTES, *b_lo = b_hi + b_bytes;
+                    umma::mbar_expect_tx(&full[s], stage_bytes);
+                    const int k0 = kb * UM_BK;
+                    if (!p.a_mn) {
+                        umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, b, &full[s]);
+                        umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, b, &full[s]);
+                    } else {
+                        for (int sl = 0; sl < UM_BM / 32; ++sl) {
+                            umma::tma_load_3d(a_hi + sl * UM_SLAB_BYTES, &map_a_hi, m0 + 32 * sl, k0, b, &full[s]);
+                            umma::tma_load_3d(a_lo + sl * UM_SLAB_BYTES, &map_a_lo, m0 + 32 * sl, k0, b, &full[s]);
+                        }
                     }
-                }
-                if (!p.b_mn) {
-                    umma::tma_load_3d(b_hi, &map_b_hi, k0, n0, b, &full[s]);
-                    umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
-                } else {
-                    for (int sl = 0; sl < b_slabs; ++sl) {
-                        umma::tma_load_3d(b_hi + sl * UM_SLAB_BYTES, &map_b_hi, n0 + 32 * sl, k0, b, &full[s]);
-                        umma::tma_load_3d(b_lo + sl * UM_SLAB_BYTES, &map_b_lo, n0 + 32 * sl, k0, b, &full[s]);
+                    if (!p.b_mn) {
+                        umma::tma_load_3d(b_hi, &map_b_hi, k0, n0, b, &full[s]);
+                        umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
+                    } else {
+                        for (int sl = 0; sl < b_slabs; ++sl) {
+                            umma::tma_load_3d(b_hi + sl * UM_SLAB_BYTES, &map_b_hi, n0 + 32 * sl, k0, b, &full[s]);
+                            umma::tma_load_3d(b_lo + sl * UM_SLAB_BYTES, &map_b_lo, n0 + 32 * sl, k0, b, &full[s]);
+                        }
                     }
                 }
             }
@@ -239,29 +256,39 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         // ---- MMA issuer -----------------------------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc = umma::instr_desc(2 /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % p.stages;
-                const uint32_t ph = (kb / p.stages) & 1;
-                if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); break; }
+            long long it = 0;
+            long long lt = 0;                      // tiles done by this CTA
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+                const int buf = static_cast<int>(lt & 1);
+                const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
+                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }   // drained?
                 umma::tc_fence_after();
-                const uint32_t st = umma::smem_u32(smem + s * stage_bytes);
-                const uint32_t a_hi = st, a_lo = st + UM_A_BYTES, b_hi = st + 2 * UM_A_BYTES, b_lo = b_hi + b_bytes;
+                const uint32_t tmem_d = tmem_base + buf * acc_cols;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = static_cast<int>(it % p.stages);
+                    const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
+                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
+                    umma::tc_fence_after();
+                    const uint32_t st = umma::smem_u32(smem + s * stage_bytes);
+                    const uint32_t a_hi = st, a_lo = st + UM_A_BYTES, b_hi = st + 2 * UM_A_BYTES, b_lo = b_hi + b_bytes;
 #pragma unroll
-                for (int k8 = 0; k8 < UM_BK / 8; ++k8) {
-                    // K-major: 8 k-values = 32 bytes further along the swizzled row; MN-major: the next 8-row group
-                    const uint32_t ao = p.a_mn ? k8 * 1024 : k8 * 32;
-                    const uint32_t bo = p.b_mn ? k8 * 1024 : k8 * 32;
-                    const uint64_t dah = p.a_mn ? umma::smem_desc_mn_sw128(a_hi + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_hi + ao);
-                    const uint64_t dal = p.a_mn ? umma::smem_desc_mn_sw128(a_lo + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_lo + ao);
-                    const uint64_t dbh = p.b_mn ? umma::smem_desc_mn_sw128(b_hi + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_hi + bo);
-                    const uint64_t dbl = p.b_mn ? umma::smem_desc_mn_sw128(b_lo + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_lo + bo);
-                    umma::mma_tf32(tmem_base, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                    umma::mma_tf32(tmem_base, dah, dbl, idesc, 1u);
-                    umma::mma_tf32(tmem_base, dah, dbh, idesc, 1u);
+                    for (int k8 = 0; k8 < UM_BK / 8; ++k8) {
+                        // K-major: 8 k-values = 32 bytes further along the swizzled row; MN-major: the next 8 k-rows
+                        const uint32_t ao = p.a_mn ? k8 * 1024 : k8 * 32;
+                        const uint32_t bo = p.b_mn ? k8 * 1024 : k8 * 32;
+                        const uint64_t dah = p.a_mn ? umma::smem_desc_mn_sw128(a_hi + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_hi + ao);
+                        const uint64_t dal = p.a_mn ? umma::smem_desc_mn_sw128(a_lo + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_lo + ao);
+                        const uint64_t dbh = p.b_mn ? umma::smem_desc_mn_sw128(b_hi + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_hi + bo);
+                        const uint64_t dbl = p.b_mn ? umma::smem_desc_mn_sw128(b_lo + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_lo + bo);
+                        umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
+                        umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+                        umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                    }
+                    umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
                 }
-                umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
+                umma::mma_commit(&acc_full[buf]);         // accumulator complete (or abandoned)
             }
-            umma::mma_commit(acc_ready);              // accumulator complete (or abandoned)
         }
     } else {
         // ---- epilogue: a warp may only read the TMEM lane quarter (warp % 4); two warps share each quarter and take
@@ -269,54 +296,68 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;
         const int row = q * 32 + lane;                 // row of the tile held by this thread
-        const bool ok = umma::mbar_wait(acc_ready, 0);
-        if (!ok && lane == 0) atomicOr(p.err, 2);
-        umma::tc_fence_after();
-        const int m = m0 + row;
-        const bool row_ok = ok && (m < p.m_rows);
-        const long long grow = static_cast<long long>(b) * p.m_rows + m;           // row of A-side per-row vectors
-        float* orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld + n0;
-        const float sa = (p.ep == EP_DIST && row_ok) ? p.sq_a[grow] : 0.f;
-        const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
         const int n_chunks32 = (p.bn + 31) / 32;
+        long long lt = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+            const int n0 = static_cast<int>(tile % tiles_n) * p.bn;
+            const int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
+            const int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+            const int buf = static_cast<int>(lt & 1);
+            const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
+            if (ok && !umma::mbar_wait(&acc_full[buf], aph)) { ok = false; if (lane == 0) atomicOr(p.err, 2); }
+            if (!ok) break;                                // warp-uniform: the wait result is the same for all lanes
+            umma::tc_fence_after();
+            const uint32_t tmem_d = tmem_base + buf * acc_cols;
+            const int m = m0 + row;
+            const bool row_ok = m < p.m_rows;
+            const long long grow = static_cast<long long>(b) * p.m_rows + m;           // row of A-side per-row vectors
+            float* orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld + n0;
+            const float sa = (p.ep == EP_DIST && row_ok) ? p.sq_a[grow] : 0.f;
+            const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
 #pragma unroll 1
-        for (int c = half; c < n_chunks32; c += 2) {
-            float v[32];
-            umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);   // warp-collective
-            if (!row_ok) continue;
-            const int nbase = n0 + c * 32;
-            const int lim = min(32, min(p.bn - c * 32, p.n_cols - nbase));                    // valid columns of this chunk
-            if (lim <= 0) continue;
-            if (p.ep == EP_DIST) {
-                const float* sb = p.sq_b + static_cast<long long>(b) * p.n_cols + nbase;
+            for (int c = half; c < n_chunks32; c += 2) {
+                float v[32];
+                umma::tmem_ld32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);   // warp-collective
+                if (!row_ok) continue;
+                const int nbase = n0 + c * 32;
+                const int lim = min(32, min(p.bn - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
+                if (lim <= 0) continue;
+                if (p.ep == EP_DIST) {
+                    const float* sb = p.sq_b + static_cast<long long>(b) * p.n_cols + nbase;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    if (j < lim) {
-                        const float nn = sa + sb[j];
-                        const float d2 = fmaf(-2.f, v[j], nn);
-                        if (d2 < 0.015625f * nn) {       // cancellation: list for exact recomputation
-                            const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
-                            if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + (nbase + j);
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < lim) {
+                            const float nn = sa + sb[j];
+                            const float d2 = fmaf(-2.f, v[j], nn);
+                            if (d2 < 0.015625f * nn) {       // cancellation: list for exact recomputation
+                                const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
+                                if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + (nbase + j);
+                            }
+                            v[j] = -sqrt_approx(fmaxf(d2, 0.f));
                         }
-                        v[j] = -sqrt_approx(fmaxf(d2, 0.f));
                     }
+                } else if (p.ep == EP_RANK1) {
+                    const float* yh = p.y_hi + grow * p.out_ld + nbase;
+                    const float* yl = p.y_lo + grow * p.out_ld + nbase;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < lim) v[j] = fmaf(rs, yh[j] + yl[j], -v[j]);
                 }
-            } else if (p.ep == EP_RANK1) {
-                const float* yh = p.y_hi + grow * p.out_ld + nbase;
-                const float* yl = p.y_lo + grow * p.out_ld + nbase;
+                if (lim == 32 && (p.out_ld & 3) == 0) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (j < lim) v[j] = fmaf(rs, yh[j] + yl[j], -v[j]);
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(orow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < lim) orow[c * 32 + j] = v[j];
+                }
             }
-            if (lim == 32 && (p.out_ld & 3) == 0) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(orow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (j < lim) orow[c * 32 + j] = v[j];
-            }
+            // this warp is done reading the accumulator: hand it back to the MMA warp
+            umma::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
         }
     }
     umma::tc_fence_before();
@@ -446,6 +487,31 @@ static int pick_bn(int n) {
     return bn < 16 ? 16 : bn;
 }
 
+// ---- optional live timing of the tile kernel (CUDA events on the launching stream) ---------------------------------
+static bool g_prof_on = false;
+static double g_prof_flops = 0.0;
+static long long g_prof_launches = 0;
+static cudaEvent_t g_prof_ev[2 * 64];
+static int g_prof_n = 0;                 // events pairs recorded and not yet read
+static bool g_prof_events_made = false;
+
+void gemm_profile_enable(int on) { g_prof_on = on != 0; g_prof_n = 0; g_prof_flops = 0.0; g_prof_launches = 0; }
+int gemm_profile_read(double* ms, long long* launches, double* flops) {
+    double total = 0.0;
+    for (int i = 0; i < g_prof_n; ++i) {
+        cudaError_t e = cudaEventSynchronize(g_prof_ev[2 * i + 1]);
+        float t = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]);
+        if (e != cudaSuccess) return cuda_status(e, "gemm_profile_read");
+        total += t;
+    }
+    if (ms) *ms = total;
+    if (launches) *launches = g_prof_launches;
+    if (flops) *flops = g_prof_flops;
+    g_prof_n = 0; g_prof_flops = 0.0; g_prof_launches = 0;
+    return 0;
+}
+
 static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, GemmTc& p,
                     long long batch, cudaStream_t s) {
     p.stages = p.bn <= 128 ? 3 : 2;
@@ -455,9 +521,28 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
     const int b_bytes = p.b_mn ? ((p.bn + 31) / 32) * UM_SLAB_BYTES : p.bn * 128;
     const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + 256;
-    const dim3 grid((p.n_cols + p.bn - 1) / p.bn, (p.m_rows + UM_BM - 1) / UM_BM, (unsigned)batch);
+    p.batch = (int)batch;
+    const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + UM_BM - 1) / UM_BM) * batch;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return cuda_status(cudaGetLastError(), "cudaDeviceGetAttribute(multiprocessor count)");
+    const dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms));     // persistent: one CTA per SM walks the tile list
+    const bool prof = g_prof_on && g_prof_n < 64;
+    if (prof) {
+        if (!g_prof_events_made) {
+            for (int i = 0; i < 128; ++i)
+                if (cudaEventCreate(&g_prof_ev[i]) != cudaSuccess) return cuda_status(cudaGetLastError(), "cudaEventCreate");
+            g_prof_events_made = true;
+        }
+        cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
+    }
     umma_gemm_kernel<<<grid, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
     KGE_LAUNCH_CHECK("umma_gemm_kernel");
+    if (prof) {
+        cudaEventRecord(g_prof_ev[2 * g_prof_n + 1], s);
+        ++g_prof_n; ++g_prof_launches;
+        g_prof_flops += 2.0 * p.m_rows * (double)p.n_cols * p.k_len * (double)batch;
+    }
     return 0;
 }
 

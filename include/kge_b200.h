@@ -253,6 +253,12 @@ KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64
  * Launches `blocks` x 256 threads of independent fp32 FMA chains (iters x 128 FMAs per thread) and returns the
  * flop count (2 per FMA) in *flops_out; time it with CUDA events to get this GPU's attainable fp32 FMA rate,
  * the roofline denominator of the CUDA-core contraction kernels.  No counterpart in the reference. */
+/* Live timing of the tensor-core tile kernel: after kge_profile_gemm(1) every launch of that kernel (up to 64 between
+ * reads) is bracketed by CUDA events on its stream; kge_profile_gemm_read waits for them and returns the summed
+ * duration, the number of launches and their useful flops (2 M N K per contraction), then resets the counters. */
+KGE_API int kge_profile_gemm(int32_t enable);
+KGE_API int kge_profile_gemm_read(double* ms, int64_t* launches, double* flops);
+
 KGE_API int kge_probe_fma(float* out, int32_t blocks, int32_t iters, double* flops_out, kge_stream_t stream);
 
 #ifdef __cplusplus

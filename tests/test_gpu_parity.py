@@ -13,7 +13,7 @@ from tests.kge_testlib import (BF16_TOL, FP32_TOL, MODELS, bf16_round, gpu_grads
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 CHUNK_MODELS = ["TransE", "DistMult", "ComplEx", "RESCAL"]
-BWD_MODELS = ["TransE", "TransH", "TransF", "DistMult", "RESCAL", "ComplEx"]
+BWD_MODELS = ["TransE", "TransH", "TransR", "TransF", "DistMult", "RESCAL", "ComplEx"]
 
 
 # ---- reference-compatible forward against the reference's own golden outputs ------------------------------
