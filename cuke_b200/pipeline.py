@@ -39,6 +39,7 @@ class RowExchange:
         self.dim = ent_local.shape[1]
         self.need = self.serve = None
         self.req_ids = None
+        self.owner_insp = None        # inspection of the ids this rank serves, shared by every gradient return of a step
 
     def stage(self, insp: Inspection) -> torch.Tensor:
         """Compact buffer holding row uniq[u] of the global table at position u (u < U)."""
@@ -57,6 +58,7 @@ class RowExchange:
             send_rows = self.ops.gather_rows(self.ent_local, self.req_ids[:S], first_row=self.rank * self.rows_per_rank)
         else:
             send_rows = torch.empty((0, self.dim), dtype=self.ent_local.dtype, device=dev)
+        self.owner_insp = None
         staged = torch.empty((max(U, 1), self.dim), dtype=self.ent_local.dtype, device=dev)
         dist.all_to_all_single(staged[:U], send_rows, output_split_sizes=self.need, input_split_sizes=self.serve,
                                group=self.group)
@@ -72,7 +74,9 @@ class RowExchange:
                                input_split_sizes=self.need, group=self.group)
         if S == 0:
             return self.req_ids[:0], torch.zeros(1, dtype=torch.int64, device=grad_rows.device), recv[:0]
-        oinsp = self.ops.inspect(self.req_ids[:S], self.n_ent)
+        if self.owner_insp is None:
+            self.owner_insp = self.ops.inspect(self.req_ids[:S], self.n_ent)
+        oinsp = self.owner_insp
         return oinsp.uniq, oinsp.n_unique, self.ops.segment_reduce(recv[:S], oinsp)
 
 
@@ -105,6 +109,8 @@ class KgeStep:
             if m in ("TransH", "TransR", "RESCAL"):
                 raise NotImplementedError("KgeStep covers the vector-relation scorers (TransE, DistMult, ComplEx, TransF)")
         self.exchange = RowExchange(ent_local, n_ent, rank, world, group) if world > 1 else None
+        # gradient rows travel home on a side stream while the next scorer computes
+        self.comm_stream = torch.cuda.Stream(device=ent_local.device) if world > 1 else None
 
     def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True) -> StepOutput:
         import torch.distributed as dist
@@ -137,7 +143,16 @@ class KgeStep:
             if self.exchange is None:
                 out.ent_ids, out.n_ent_rows, out.ent_grad[m] = insp.uniq, insp.n_unique, grad_rows
             else:
-                out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
-                dist.all_reduce(dense_rel, group=self.group)
+                main = torch.cuda.current_stream()
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ready)
+                    grad_rows.record_stream(self.comm_stream)
+                    dense_rel.record_stream(self.comm_stream)
+                    out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
+                    dist.all_reduce(dense_rel, group=self.group)
             out.rel_grad[m] = dense_rel
+        if self.exchange is not None and backward:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
         return out

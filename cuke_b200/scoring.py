@@ -50,8 +50,9 @@ _ws_cache = {}
 
 
 def workspace(nbytes: int, device, tag: str = "") -> torch.Tensor:
-    """A reusable scratch buffer per (device, tag); grown on demand, never shrunk."""
-    key = (str(device), tag)
+    """A reusable scratch buffer per (device, current stream, tag); grown on demand, never shrunk.  Keyed by stream
+    so that calls issued on different streams never share scratch."""
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream, tag)
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
