@@ -217,7 +217,8 @@ def side_config(args):
     for model in (cfg.model,) + tuple(cfg.extra_models):
         ent, rel, rel2 = synth.make_tables(cfg, model)
         to = lambda a: None if a is None else torch.from_numpy(a).to(dev).to(torch.bfloat16 if cfg.dtype == "bf16" else torch.float32).contiguous()
-        sc = scoring.Scorer(model, to(ent), to(rel), to(rel2), cfg.neg_mode, cfg.n_neg_head if model != "RESCAL" else 0, cfg.chunk)
+        sc = scoring.Scorer(model, to(ent), to(rel), to(rel2), cfg.neg_mode, cfg.n_neg_head if model != "RESCAL" else 0, cfg.chunk,
+                            args.precision)
         h, r, t, neg = (torch.from_numpy(x).to(dev) for x in synth.make_batch(cfg, 0, 0))
         backward = cfg.backward and model != "TransR"
         d = synth.row_floats(cfg, model)
@@ -257,7 +258,7 @@ def side_config(args):
         print(json.dumps({"metric": METRIC if backward else "scored_triples_per_sec_fwd", "side_measurement": True,
                           "value": S / (ms_cold * 1e-3), "value_warm_l2": S / (ms_warm * 1e-3), "unit": "triples/s", "n_gpus": 1,
                           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm,
-                          "dtype": cfg.dtype, "data": "synthetic",
+                          "dtype": cfg.dtype, "data": "synthetic", "precision": args.precision,
                           "config": {"workload": f"{cfg.name}: {model} {'fwd+bwd' if backward else 'fwd'}, entities {cfg.n_ent}x{d}, "
                                                  f"batch {cfg.batch}, {cfg.n_neg} negatives ({cfg.neg_mode})",
                                      "l2": "384 MB written between timed iterations (cold L2); warm figure beside it"},

@@ -56,6 +56,9 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s);
 int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
+size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel);
+int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s);
 size_t transr_backward_workspace_bytes(const kge_problem* p);
 int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const float* pos, const float* negs, const float* dpos,
                            const float* dneg, const kge_grads* g, void* ws, cudaStream_t s);
@@ -146,6 +149,11 @@ static inline size_t rows_bytes(const kge_problem* p) { return ((size_t)p->batch
 static bool tc_forward(const kge_problem* p) {
     return p->precision == KGE_PREC_TENSOR && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 &&
            (p->model == KGE_TRANSE || p->model == KGE_DISTMULT || p->model == KGE_COMPLEX || p->model == KGE_RESCAL);
+}
+// TransR forward on the tensor cores: bf16 tables, one n-tile per row.
+static bool tc_transr(const kge_problem* p) {
+    return p->precision == KGE_PREC_TENSOR && p->model == KGE_TRANSR && p->dtype == KGE_BF16 && p->dim % 8 == 0 && p->dim <= 256 &&
+           p->neg_mode != KGE_NEG_CHUNK_SHARED;
 }
 static bool tc_backward(const kge_problem* p) { return tc_forward(p) && p->n_neg % 4 == 0; }
 static size_t tc_bytes(const kge_problem* p, int backward) {
@@ -262,6 +270,7 @@ size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
     const size_t rb = rows_bytes(p);
     if (backward && p->model == KGE_TRANSR) return transr_backward_workspace_bytes(p) + 256;
     if (backward) return 3 * rb + tc_bytes(p, 1) + 256;
+    if (tc_transr(p)) return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel) + 256;
     return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + 256;
 }
 
@@ -281,6 +290,9 @@ int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_sco
     }
     ScoreArgs a = score_args(p, t);
     a.pos = pos_score; a.negs = neg_score;
+    if (tc_transr(p))
+        return launch_transr_forward_tc(a, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq, (const long long*)t->n_rel_groups,
+                                        p->n_rel, workspace, workspace_bytes, s);
     if (p->model == KGE_TRANSR) return launch_transr_forward(p, t, pos_score, neg_score, s);
     if (p->model == KGE_RESCAL) {
         float* anchors = static_cast<float*>(workspace);

@@ -147,9 +147,10 @@ __global__ void __launch_bounds__(256) tc_colsum_kernel(const float* hi, const f
 constexpr int UM_BM = 128, UM_BK = 32;                       // 32 fp32 = one 128-byte swizzle row
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 4;                // 16 KiB per A tile (either major)
 constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major slab: 32 k-rows x 128 bytes
-constexpr int UM_MAX_SMEM = 2 * (2 * UM_A_BYTES + 2 * 256 * 128) + 1024 + 256;      // 2 stages at BN = 256
+constexpr int UM_TAIL_BYTES = 256 + 2048;                   // barriers, tensor-memory slot, EP_NORM partial sums
+constexpr int UM_MAX_SMEM = 2 * (2 * UM_A_BYTES + 2 * 256 * 128) + 1024 + UM_TAIL_BYTES;      // 2 stages at BN = 256
 
-enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2 };
+enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3 };
 
 struct GemmTc {
     int m_rows, n_cols, k_len;        // extents per batch
@@ -164,6 +165,12 @@ struct GemmTc {
     unsigned long long* fix_count; unsigned long long* fix_list; unsigned long long fix_cap;
     // EP_RANK1: out = scale[b * m_rows + m] * (y_hi + y_lo)[(b * m_rows + m) * out_ld + n] - acc
     const float* scale; const float* y_hi; const float* y_lo;
+    // element type and split: elem_bytes 4 (tf32) or 2 (bf16); passes 3 (hi/lo split) or 1 (hi only)
+    int elem_bytes; int passes;
+    // grouped mode (relation-grouped projections): tile list in device memory, one n-tile
+    const int2* tile_tab; const long long* n_tiles_dev; long long tile_cap;
+    // EP_NORM: score = -|| acc + rel_vec[z] ||, scattered through row_dst
+    const long long* row_dst; float* pos_out; float* neg_out; const void* rel_vec; int rel_is_bf16;
     int32_t* err;
 };
 
@@ -184,22 +191,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const int b_slabs = (p.bn + 31) / 32;
-    const int b_bytes = p.b_mn ? b_slabs * UM_SLAB_BYTES : p.bn * 128;       // one B tile (hi or lo)
+    // element size 4: tf32 (fp32 storage), 2: bf16.  A shared-memory row is always 128 bytes of K (K-major) or of M/N (MN-major).
+    const int bk = 128 / p.elem_bytes;                  // k-values per stage
+    const int slab_cols = 128 / p.elem_bytes;           // M/N-columns per MN-major slab
+    const int slab_bytes = bk * 128;                    // MN-major slab: bk k-rows x 128 bytes
+    const int a_slabs = UM_BM / slab_cols;
+    const int b_slabs = (p.bn + slab_cols - 1) / slab_cols;
+    const int b_bytes = p.b_mn ? b_slabs * slab_bytes : p.bn * 128;       // one B tile (hi or lo)
     const int stage_bytes = 2 * UM_A_BYTES + 2 * b_bytes;
+    const int tx_bytes = p.passes == 1 ? UM_A_BYTES + b_bytes : stage_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
     uint64_t* empty = full + p.stages;
     uint64_t* acc_full = empty + p.stages;          // [2] accumulator written  (MMA -> epilogue)
     uint64_t* acc_empty = acc_full + 2;             // [2] accumulator drained  (epilogue -> MMA)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* ssq_part = reinterpret_cast<float*>(tmem_slot + 4);       // EP_NORM: [2 accumulators][2 halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (p.k_len + UM_BK - 1) / UM_BK;
+    const int num_kb = (p.k_len + bk - 1) / bk;
     const uint32_t acc_cols = p.bn <= 32 ? 32u : p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
     const uint32_t tmem_cols = 2 * acc_cols;        // <= 512, the whole tensor memory at bn > 128
     const int tiles_n = (p.n_cols + p.bn - 1) / p.bn;
     const int tiles_m = (p.m_rows + UM_BM - 1) / UM_BM;
-    const long long n_tiles = static_cast<long long>(tiles_n) * tiles_m * p.batch;
+    // grouped mode: the tile list comes from device memory (one n-tile; rows of A are absolute; z selects the B matrix)
+    const long long n_tiles = p.tile_tab ? min(*p.n_tiles_dev, p.tile_cap) : static_cast<long long>(tiles_n) * tiles_m * p.batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
@@ -220,33 +235,36 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             long long it = 0;                      // k-blocks issued so far (ring position)
             bool ok = true;
             for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int n0 = static_cast<int>(tile % tiles_n) * p.bn;
-                const int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
-                const int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+                int n0 = static_cast<int>(tile % tiles_n) * p.bn;
+                int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
+                int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+                int za = b;
+                if (p.tile_tab) { const int2 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; za = 0; }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = static_cast<int>(it % p.stages);
                     const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + 2 * UM_A_BYTES, *b_lo = b_hi + b_bytes;
-                    umma::mbar_expect_tx(&full[s], stage_bytes);
-                    const int k0 = kb * UM_BK;
+                    umma::mbar_expect_tx(&full[s], tx_bytes);
+                    const int k0 = kb * bk;
+                    const bool lo = p.passes != 1;
                     if (!p.a_mn) {
-                        umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, b, &full[s]);
-                        umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, b, &full[s]);
+                        umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, za, &full[s]);
+                        if (lo) umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, za, &full[s]);
                     } else {
-                        for (int sl = 0; sl < UM_BM / 32; ++sl) {
-                            umma::tma_load_3d(a_hi + sl * UM_SLAB_BYTES, &map_a_hi, m0 + 32 * sl, k0, b, &full[s]);
-                            umma::tma_load_3d(a_lo + sl * UM_SLAB_BYTES, &map_a_lo, m0 + 32 * sl, k0, b, &full[s]);
+                        for (int sl = 0; sl < a_slabs; ++sl) {
+                            umma::tma_load_3d(a_hi + sl * slab_bytes, &map_a_hi, m0 + slab_cols * sl, k0, za, &full[s]);
+                            if (lo) umma::tma_load_3d(a_lo + sl * slab_bytes, &map_a_lo, m0 + slab_cols * sl, k0, za, &full[s]);
                         }
                     }
                     if (!p.b_mn) {
                         umma::tma_load_3d(b_hi, &map_b_hi, k0, n0, b, &full[s]);
-                        umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
+                        if (lo) umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
                     } else {
                         for (int sl = 0; sl < b_slabs; ++sl) {
-                            umma::tma_load_3d(b_hi + sl * UM_SLAB_BYTES, &map_b_hi, n0 + 32 * sl, k0, b, &full[s]);
-                            umma::tma_load_3d(b_lo + sl * UM_SLAB_BYTES, &map_b_lo, n0 + 32 * sl, k0, b, &full[s]);
+                            umma::tma_load_3d(b_hi + sl * slab_bytes, &map_b_hi, n0 + slab_cols * sl, k0, b, &full[s]);
+                            if (lo) umma::tma_load_3d(b_lo + sl * slab_bytes, &map_b_lo, n0 + slab_cols * sl, k0, b, &full[s]);
                         }
                     }
                 }
@@ -255,7 +273,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     } else if (warp == 1) {
         // ---- MMA issuer -----------------------------------------------------------------------------------------
         if (lane == 0) {
-            const uint32_t idesc = umma::instr_desc(2 /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+            const bool f16 = p.elem_bytes == 2;
+            const uint32_t idesc = umma::instr_desc(f16 ? 1u /* bf16 */ : 2u /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+            const uint32_t mn_adv = f16 ? 2048u : 1024u;      // bytes per MMA step (16 or 8 k-rows of 128 bytes)
+            const uint32_t mn_sbo = f16 ? 1024u : 512u, mn_layout = f16 ? 2u : 1u;
             long long it = 0;
             long long lt = 0;                      // tiles done by this CTA
             bool ok = true;
@@ -273,17 +294,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     const uint32_t st = umma::smem_u32(smem + s * stage_bytes);
                     const uint32_t a_hi = st, a_lo = st + UM_A_BYTES, b_hi = st + 2 * UM_A_BYTES, b_lo = b_hi + b_bytes;
 #pragma unroll
-                    for (int k8 = 0; k8 < UM_BK / 8; ++k8) {
-                        // K-major: 8 k-values = 32 bytes further along the swizzled row; MN-major: the next 8 k-rows
-                        const uint32_t ao = p.a_mn ? k8 * 1024 : k8 * 32;
-                        const uint32_t bo = p.b_mn ? k8 * 1024 : k8 * 32;
-                        const uint64_t dah = p.a_mn ? umma::smem_desc_mn_sw128(a_hi + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_hi + ao);
-                        const uint64_t dal = p.a_mn ? umma::smem_desc_mn_sw128(a_lo + ao, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(a_lo + ao);
-                        const uint64_t dbh = p.b_mn ? umma::smem_desc_mn_sw128(b_hi + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_hi + bo);
-                        const uint64_t dbl = p.b_mn ? umma::smem_desc_mn_sw128(b_lo + bo, UM_SLAB_BYTES) : umma::smem_desc_k_sw128(b_lo + bo);
-                        umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                        umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
-                        umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                    for (int k8 = 0; k8 < 4; ++k8) {      // 4 MMA steps of 32 bytes of K per stage
+                        // K-major: 32 bytes further along the swizzled row; MN-major: the next 8 (tf32) or 16 (bf16) k-rows
+                        const uint32_t ao = p.a_mn ? k8 * mn_adv : k8 * 32;
+                        const uint32_t bo = p.b_mn ? k8 * mn_adv : k8 * 32;
+                        const uint64_t dah = p.a_mn ? umma::smem_desc_mn(a_hi + ao, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(a_hi + ao);
+                        const uint64_t dbh = p.b_mn ? umma::smem_desc_mn(b_hi + bo, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(b_hi + bo);
+                        const uint32_t first = (kb > 0 || k8 > 0) ? 1u : 0u;
+                        if (p.passes == 1) {
+                            if (f16) umma::mma_f16(tmem_d, dah, dbh, idesc, first); else umma::mma_tf32(tmem_d, dah, dbh, idesc, first);
+                        } else {
+                            const uint64_t dal = p.a_mn ? umma::smem_desc_mn(a_lo + ao, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(a_lo + ao);
+                            const uint64_t dbl = p.b_mn ? umma::smem_desc_mn(b_lo + bo, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(b_lo + bo);
+                            umma::mma_tf32(tmem_d, dal, dbh, idesc, first);     // small terms first
+                            umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+                            umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                        }
                     }
                     umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
                 }
@@ -300,9 +326,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         long long lt = 0;
         bool ok = true;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
-            const int n0 = static_cast<int>(tile % tiles_n) * p.bn;
-            const int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
-            const int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+            int n0 = static_cast<int>(tile % tiles_n) * p.bn;
+            int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
+            int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+            if (p.tile_tab) { const int2 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; }
             const int buf = static_cast<int>(lt & 1);
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (ok && !umma::mbar_wait(&acc_full[buf], aph)) { ok = false; if (lane == 0) atomicOr(p.err, 2); }
@@ -315,6 +342,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             float* orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld + n0;
             const float sa = (p.ep == EP_DIST && row_ok) ? p.sq_a[grow] : 0.f;
             const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
+            float ssq = 0.f;
 #pragma unroll 1
             for (int c = half; c < n_chunks32; c += 2) {
                 float v[32];
@@ -323,6 +351,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 const int nbase = n0 + c * 32;
                 const int lim = min(32, min(p.bn - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
                 if (lim <= 0) continue;
+                if (p.ep == EP_NORM) {          // squared norm of (acc + R[z]) over the row; nothing is stored per element
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < lim) {
+                            const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
+                            const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
+                                                           : reinterpret_cast<const float*>(p.rel_vec)[ri];
+                            const float t = v[j] + rv;
+                            ssq = fmaf(t, t, ssq);
+                        }
+                    }
+                    continue;
+                }
                 if (p.ep == EP_DIST) {
                     const float* sb = p.sq_b + static_cast<long long>(b) * p.n_cols + nbase;
 #pragma unroll
@@ -358,6 +399,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             umma::tc_fence_before();
             __syncwarp();
             if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
+            if (p.ep == EP_NORM) {          // the two warps of a lane quarter hold the two halves of each row's sum
+                ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
+                asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight epilogue warps
+                if (half == 0) {
+                    const long long dst = p.row_dst[m];               // >= 0: negative score index, <= -2: positive -2-i, -1: padding
+                    const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
+                    if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
+                }
+            }
         }
     }
     umma::tc_fence_before();
@@ -514,19 +564,23 @@ int gemm_profile_read(double* ms, long long* launches, double* flops) {
 
 static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, GemmTc& p,
                     long long batch, cudaStream_t s) {
+    if (p.elem_bytes == 0) p.elem_bytes = 4;
+    if (p.passes == 0) p.passes = 3;
     p.stages = p.bn <= 128 ? 3 : 2;
     p.err = device_error_word();
     if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
     cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
-    const int b_bytes = p.b_mn ? ((p.bn + 31) / 32) * UM_SLAB_BYTES : p.bn * 128;
-    const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + 256;
+    const int slab_cols = 128 / p.elem_bytes;
+    const int b_bytes = p.b_mn ? ((p.bn + slab_cols - 1) / slab_cols) * (slab_cols * 128) : p.bn * 128;
+    const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + UM_TAIL_BYTES;
     p.batch = (int)batch;
     const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + UM_BM - 1) / UM_BM) * batch;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
         return cuda_status(cudaGetLastError(), "cudaDeviceGetAttribute(multiprocessor count)");
-    const dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms));     // persistent: one CTA per SM walks the tile list
+    const long long bound = p.tile_tab ? p.tile_cap : n_tiles;      // grouped mode: the tile count is only known on the device
+    const dim3 grid((unsigned)(bound < sms ? bound : sms));         // persistent: one CTA per SM walks the tile list
     const bool prof = g_prof_on && g_prof_n < 64;
     if (prof) {
         if (!g_prof_events_made) {
@@ -657,4 +711,130 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
     return run_gemm(mah, mal, mbh, mbl, p, n_chunks, s);
 }
 
+
+// ---- TransR forward on the tensor cores (bf16 tables) ---------------------------------------------------------------
+// score(i, j) = -|| (a - b) . P[r_i] + R[r_i] ||.  The inspector has grouped the triples by relation; every group's
+// difference rows (1 + n_neg per triple, positive first) are packed as bf16 into one matrix, each group padded to a
+// multiple of 128 rows, so a 128-row tile never mixes relations.  The tile list (row offset, relation id) is built on the
+// device; umma_gemm_kernel runs it in grouped mode with B = P[relation] read straight from the table by TMA (MN-major:
+// out[j] = sum_i x[i] P[r][i][j] needs no transpose) and the EP_NORM epilogue.  Needs dim <= 256 (one n-tile per row).
+struct TransRPlan {
+    const int* rel_perm; const int* rel_seg; const long long* rel_uniq; const long long* n_groups;
+    int per;                    // rows per triple: 1 + n_neg
+    int2* tile_tab; long long* n_tiles; int* goff;      // goff[g]: first padded row of group g
+    long long tile_cap;
+};
+
+__global__ void transr_plan_kernel(TransRPlan pl) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int G = (int)*pl.n_groups;
+    long long tiles = 0;
+    for (int g = 0; g < G; ++g) {
+        const long long rows = (long long)(pl.rel_seg[g + 1] - pl.rel_seg[g]) * pl.per;
+        const long long nt = (rows + UM_BM - 1) / UM_BM;
+        pl.goff[g] = (int)(tiles * UM_BM);
+        const int z = (int)pl.rel_uniq[g];
+        for (long long t = 0; t < nt && tiles + t < pl.tile_cap; ++t) pl.tile_tab[tiles + t] = make_int2((int)((tiles + t) * UM_BM), z);
+        tiles += nt;
+    }
+    *pl.n_tiles = tiles < pl.tile_cap ? tiles : pl.tile_cap;
+}
+
+// One warp per difference row, in relation-sorted order: sorted triple position p, row j of that triple.
+template <typename I, int NV>
+__global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPlan pl, __nv_bfloat16* rows_out, long long* row_dst) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= a.batch * pl.per) return;
+    const int p = (int)(w / pl.per), j = (int)(w % pl.per);
+    const int G = (int)*pl.n_groups;
+    int lo = 0, hi = G - 1;                       // group of sorted position p: largest g with rel_seg[g] <= p
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (pl.rel_seg[mid] <= p) lo = mid; else hi = mid - 1; }
+    const long long prow = (long long)pl.goff[lo] + (long long)(p - pl.rel_seg[lo]) * pl.per + j;
+    const int i = pl.rel_perm[p];
+    const int dim = a.dim;
+    const __nv_bfloat16* E = reinterpret_cast<const __nv_bfloat16*>(a.ent);
+    const __nv_bfloat16* hrow = E + load_id<I>(a.h, i) * dim;
+    const __nv_bfloat16* trow = E + load_id<I>(a.t, i) * dim;
+    const __nv_bfloat16 *pa = hrow, *pb = trow;
+    if (j > 0) {
+        const __nv_bfloat16* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * dim;
+        if (j - 1 < a.n_neg_head) pa = x; else pb = x;
+    }
+    Row<NV> ra, rb;
+    load_row<__nv_bfloat16, NV, true>(ra, pa, dim, lane);
+    load_row<__nv_bfloat16, NV, true>(rb, pb, dim, lane);
+    __nv_bfloat16* out = rows_out + prow * dim;
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+        const int k = 4 * (lane + 32 * q);
+        if (k < dim) {
+            const float4 d = ra.v[q] - rb.v[q];
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(d.x, d.y), p1 = __floats2bfloat162_rn(d.z, d.w);
+            uint2 u;
+            u.x = *reinterpret_cast<unsigned*>(&p0); u.y = *reinterpret_cast<unsigned*>(&p1);
+            *reinterpret_cast<uint2*>(out + k) = u;
+        }
+    }
+    if (lane == 0) row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
+}
+
+struct TransRLayout { size_t off_rows, off_dst, off_tab, off_goff, off_nt, total; long long rows_cap, tile_cap; };
+static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel) {
+    TransRLayout L;
+    const long long gmax = n_rel < batch ? n_rel : batch;
+    L.rows_cap = batch * (1 + n_neg) + gmax * UM_BM;
+    L.tile_cap = L.rows_cap / UM_BM + 1;
+    size_t o = 0;
+    L.off_rows = o; o += al256((size_t)L.rows_cap * dim * 2);
+    L.off_dst = o; o += al256((size_t)L.rows_cap * 8);
+    L.off_tab = o; o += al256((size_t)L.tile_cap * 8);
+    L.off_goff = o; o += al256((size_t)(gmax + 1) * 4);
+    L.off_nt = o; o += 256;
+    L.total = o;
+    return L;
+}
+size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel) { return transr_layout(batch, n_neg, dim, n_rel).total; }
+
+// a: ScoreArgs of the problem (bf16 tables); rel grouping from the inspector over r.
+int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (a.batch <= 0) return 0;
+    const TransRLayout L = transr_layout(a.batch, a.n_neg, a.dim, n_rel);
+    if (ws_bytes < L.total) { set_error("TransR tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = static_cast<char*>(ws);
+    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(w + L.off_rows);
+    long long* dst = reinterpret_cast<long long*>(w + L.off_dst);
+    TransRPlan pl;
+    pl.rel_perm = rel_perm; pl.rel_seg = rel_seg; pl.rel_uniq = rel_uniq; pl.n_groups = n_groups; pl.per = 1 + a.n_neg;
+    pl.tile_tab = reinterpret_cast<int2*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
+    pl.goff = reinterpret_cast<int*>(w + L.off_goff); pl.tile_cap = L.tile_cap;
+    cudaError_t e = cudaMemsetAsync(dst, 0xFF, (size_t)L.rows_cap * 8, s);       // -1: padding rows produce no score
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(row_dst)");
+    transr_plan_kernel<<<1, 32, 0, s>>>(pl);
+    KGE_LAUNCH_CHECK("transr_plan_kernel");
+    {
+        const int wpb = 8;
+        const unsigned blocks = (unsigned)((a.batch * pl.per + wpb - 1) / wpb);
+        const int nv = quads_per_lane(a.dim);
+#define KGE_TP(N)                                                                                          \
+        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, wpb * 32, 0, s>>>(a, pl, rows, dst);  \
+                else transr_pack_kernel<int32_t, N><<<blocks, wpb * 32, 0, s>>>(a, pl, rows, dst); break;
+        switch (nv) { KGE_TP(1) KGE_TP(2) default: set_error("TransR tensor-core path needs dim <= 256"); return KGE_E_UNSUPPORTED; }
+#undef KGE_TP
+        KGE_LAUNCH_CHECK("transr_pack_kernel");
+    }
+    CUtensorMap ma, mb;
+    int rc;
+    const uint64_t lda = (uint64_t)a.dim * 2;
+    if ((rc = make_tensor_map_3d(&ma, rows, 2, 1, L.rows_cap, a.dim, lda, lda * L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mb, a.rel2, 2, n_rel, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
+    GemmTc p;
+    memset(&p, 0, sizeof(p));
+    p.m_rows = (int)L.rows_cap; p.n_cols = a.dim; p.k_len = a.dim; p.bn = (a.dim + 15) / 16 * 16;
+    p.a_mn = 0; p.b_mn = 1; p.elem_bytes = 2; p.passes = 1; p.ep = EP_NORM;
+    p.tile_tab = pl.tile_tab; p.n_tiles_dev = pl.n_tiles; p.tile_cap = L.tile_cap;
+    p.row_dst = dst; p.pos_out = a.pos; p.neg_out = a.negs; p.rel_vec = a.rel; p.rel_is_bf16 = 1;
+    return run_gemm(ma, ma, mb, mb, p, 1, s);
+}
 }  // namespace kge

@@ -135,6 +135,17 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t 
     d |= static_cast<uint64_t>(1) << 61;                        // SWIZZLE_128B_BASE32B
     return d;
 }
+// General MN-major descriptor: leading byte offset = distance between slabs of 128 bytes of M/N, stride byte offset =
+// distance between swizzle groups of K-rows (512 bytes for 32-bit types, layout 1; 1024 bytes for 16-bit types, layout 2).
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(layout) << 61;
+    return d;
+}
 // Instruction descriptor: fp32 accumulate, A/B format (0 f16, 1 bf16, 2 tf32), operand majors (0 K, 1 MN), M x N.
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_format, uint32_t M, uint32_t N, uint32_t a_mn = 0, uint32_t b_mn = 0) {
     return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);

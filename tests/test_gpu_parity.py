@@ -155,6 +155,26 @@ def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
     assert scoring.device_flags() == 0
 
 
+@pytest.mark.parametrize("d,B,nn,nnh,nr", [(200, 64, 16, 8, 11), (64, 300, 5, 0, 3), (256, 40, 33, 33, 40), (200, 500, 0, 0, 1),
+                                           (200, 1024, 128, 64, 50)])
+def test_transr_tensor_cores_bf16(d, B, nn, nnh, nr):
+    """TransR over bf16 tables on the tensor cores (relation-grouped tiles, bf16 MMA, fp32 accumulate): 2e-2 relative
+    against the oracle run on the bf16-rounded tables."""
+    from cuke_b200 import scoring
+    p = make_problem("TransR", seed=d + B, nr=nr, d=d, B=B, nn=max(nn, 1), neg_mode="per_triple" if nn else "none")
+    sc = gpu_scorer(p, nnh, bf16=True, precision="tensor")
+    h, r, t, neg = gpu_ids(p)
+    pos, negs, _ = sc.forward(h, r, t, neg if nn else None)
+    assert scoring.device_flags() == 0
+    rpos, rneg = oracle.scores("TransR", bf16_round(p["E"]), bf16_round(p["R"]), bf16_round(p["P2"]), p["h"], p["r"], p["t"],
+                               p["neg"] if nn else None, "per_triple" if nn else "none", nnh)
+    assert rel_err(pos.cpu().numpy(), rpos) < BF16_TOL
+    if nn:
+        assert rel_err(negs.cpu().numpy(), rneg) < BF16_TOL
+    pos2, negs2, _ = sc.forward(h, r, t, neg if nn else None)
+    assert torch.equal(pos, pos2)
+
+
 @pytest.mark.parametrize("model", ["TransE", "TransH", "DistMult", "ComplEx", "RESCAL", "TransR"])
 def test_score_forward_bf16(model):
     d = 200 if model != "ComplEx" else 256
