@@ -220,34 +220,34 @@ def side_config(args):
         sc = scoring.Scorer(model, to(ent), to(rel), to(rel2), cfg.neg_mode, cfg.n_neg_head if model != "RESCAL" else 0, cfg.chunk,
                             args.precision)
         h, r, t, neg = (torch.from_numpy(x).to(dev) for x in synth.make_batch(cfg, 0, 0))
-        backward = cfg.backward and model != "TransR"
+        backward = cfg.backward
         d = synth.row_floats(cfg, model)
         ids = scoring.entity_id_list(h, t, neg)
 
-        def step():
+        def step(bwd=True):
             pos, negs, rinsp = sc.forward(h, r, t, neg)
-            if backward:
+            if backward and bwd:
                 loss, dpos, dneg = scoring.logistic_loss(pos, negs)
                 sg = sc.backward(h, r, t, neg, pos, negs, dpos, dneg, rinsp)
                 insp = scoring.inspect(ids, cfg.n_ent)
                 scoring.segment_reduce(sg.ent_slots, insp)
             return pos
 
-        def timed(cold):
+        def timed(cold, bwd=True):
             for _ in range(max(args.warmup, 3)):
-                step()
+                step(bwd)
             torch.cuda.synchronize()
             tot = 0.0
             for _ in range(args.steps):
                 if cold:
                     flush.fill_(1)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(); step(); e1.record()
+                e0.record(); step(bwd); e1.record()
                 torch.cuda.synchronize()
                 tot += e0.elapsed_time(e1)
             return tot / args.steps
 
-        ms_cold, ms_warm = timed(True), timed(False)
+        ms_cold, ms_warm, ms_fwd = timed(True), timed(False), timed(True, False)
         S = synth.scored_triples(cfg)
         U_e = int(torch.unique(ids).numel()); U_r = int(torch.unique(r).numel())
         es = 2 if cfg.dtype == "bf16" else 4
@@ -257,7 +257,7 @@ def side_config(args):
         bytes_alg = bytes_fwd + bytes_bwd
         print(json.dumps({"metric": METRIC if backward else "scored_triples_per_sec_fwd", "side_measurement": True,
                           "value": S / (ms_cold * 1e-3), "value_warm_l2": S / (ms_warm * 1e-3), "unit": "triples/s", "n_gpus": 1,
-                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm, "ms_fwd_only": ms_fwd,
                           "dtype": cfg.dtype, "data": "synthetic", "precision": args.precision,
                           "config": {"workload": f"{cfg.name}: {model} {'fwd+bwd' if backward else 'fwd'}, entities {cfg.n_ent}x{d}, "
                                                  f"batch {cfg.batch}, {cfg.n_neg} negatives ({cfg.neg_mode})",

@@ -148,7 +148,7 @@ constexpr int UM_BM = 128, UM_BK = 32;                       // 32 fp32 = one 12
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 4;                // 16 KiB per A tile (either major)
 constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major slab: 32 k-rows x 128 bytes
 constexpr int UM_TAIL_BYTES = 256 + 2048;                   // barriers, tensor-memory slot, EP_NORM partial sums
-constexpr int UM_MAX_SMEM = 2 * (2 * UM_A_BYTES + 2 * 256 * 128) + 1024 + UM_TAIL_BYTES;      // 2 stages at BN = 256
+constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
 enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3 };
 
@@ -168,7 +168,7 @@ struct GemmTc {
     // element type and split: elem_bytes 4 (tf32) or 2 (bf16); passes 3 (hi/lo split) or 1 (hi only)
     int elem_bytes; int passes;
     // grouped mode (relation-grouped projections): tile list in device memory, one n-tile
-    const int2* tile_tab; const long long* n_tiles_dev; long long tile_cap;
+    const int4* tile_tab; const long long* n_tiles_dev; long long tile_cap;       // (first row, z, group, valid rows)
     // EP_NORM: score = -|| acc + rel_vec[z] ||, scattered through row_dst
     const long long* row_dst; float* pos_out; float* neg_out; const void* rel_vec; int rel_is_bf16;
     int32_t* err;
@@ -198,8 +198,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     const int a_slabs = UM_BM / slab_cols;
     const int b_slabs = (p.bn + slab_cols - 1) / slab_cols;
     const int b_bytes = p.b_mn ? b_slabs * slab_bytes : p.bn * 128;       // one B tile (hi or lo)
-    const int stage_bytes = 2 * UM_A_BYTES + 2 * b_bytes;
-    const int tx_bytes = p.passes == 1 ? UM_A_BYTES + b_bytes : stage_bytes;
+    const int n_parts = p.passes == 1 ? 1 : 2;          // hi only, or hi and lo
+    const int stage_bytes = n_parts * (UM_A_BYTES + b_bytes);
+    const int tx_bytes = stage_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
     uint64_t* empty = full + p.stages;
     uint64_t* acc_full = empty + p.stages;          // [2] accumulator written  (MMA -> epilogue)
@@ -239,13 +240,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
                 int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
                 int za = b;
-                if (p.tile_tab) { const int2 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; za = 0; }
+                if (p.tile_tab) { const int4 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; za = 0; }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = static_cast<int>(it % p.stages);
                     const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
-                    uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + 2 * UM_A_BYTES, *b_lo = b_hi + b_bytes;
+                    uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
                     umma::mbar_expect_tx(&full[s], tx_bytes);
                     const int k0 = kb * bk;
                     const bool lo = p.passes != 1;
@@ -275,8 +276,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         if (lane == 0) {
             const bool f16 = p.elem_bytes == 2;
             const uint32_t idesc = umma::instr_desc(f16 ? 1u /* bf16 */ : 2u /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
-            const uint32_t mn_adv = f16 ? 2048u : 1024u;      // bytes per MMA step (16 or 8 k-rows of 128 bytes)
+            // Descriptor templates: everything but the start address is fixed for the whole kernel, so the issuing thread
+            // only adds an address per MMA (it is the one thread feeding the tensor core; its instruction count matters).
             const uint32_t mn_sbo = f16 ? 1024u : 512u, mn_layout = f16 ? 2u : 1u;
+            const uint64_t a_tmpl = p.a_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
+            const uint64_t b_tmpl = p.b_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
+            // per MMA step (32 bytes of K): K-major moves 32 bytes along the swizzled row, MN-major 8 (tf32) / 16 (bf16) k-rows
+            const uint32_t a_step = (p.a_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
+            const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
+            const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
+            const bool single = p.passes == 1;
             long long it = 0;
             long long lt = 0;                      // tiles done by this CTA
             bool ok = true;
@@ -291,22 +300,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
                     if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
                     umma::tc_fence_after();
-                    const uint32_t st = umma::smem_u32(smem + s * stage_bytes);
-                    const uint32_t a_hi = st, a_lo = st + UM_A_BYTES, b_hi = st + 2 * UM_A_BYTES, b_lo = b_hi + b_bytes;
+                    const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;     // start address field
+                    uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
+                    if (single) {
+                        if (f16) {
 #pragma unroll
-                    for (int k8 = 0; k8 < 4; ++k8) {      // 4 MMA steps of 32 bytes of K per stage
-                        // K-major: 32 bytes further along the swizzled row; MN-major: the next 8 (tf32) or 16 (bf16) k-rows
-                        const uint32_t ao = p.a_mn ? k8 * mn_adv : k8 * 32;
-                        const uint32_t bo = p.b_mn ? k8 * mn_adv : k8 * 32;
-                        const uint64_t dah = p.a_mn ? umma::smem_desc_mn(a_hi + ao, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(a_hi + ao);
-                        const uint64_t dbh = p.b_mn ? umma::smem_desc_mn(b_hi + bo, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(b_hi + bo);
-                        const uint32_t first = (kb > 0 || k8 > 0) ? 1u : 0u;
-                        if (p.passes == 1) {
-                            if (f16) umma::mma_f16(tmem_d, dah, dbh, idesc, first); else umma::mma_tf32(tmem_d, dah, dbh, idesc, first);
+                            for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
+                                umma::mma_f16(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
                         } else {
-                            const uint64_t dal = p.a_mn ? umma::smem_desc_mn(a_lo + ao, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(a_lo + ao);
-                            const uint64_t dbl = p.b_mn ? umma::smem_desc_mn(b_lo + bo, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(b_lo + bo);
-                            umma::mma_tf32(tmem_d, dal, dbh, idesc, first);     // small terms first
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
+                                umma::mma_tf32(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                        }
+                    } else {
+                        uint64_t dal = a_tmpl | (st + a_lo_off), dbl = b_tmpl | (st + b_lo_off);
+#pragma unroll
+                        for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
+                            umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
                             umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
                             umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
                         }
@@ -329,7 +339,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             int n0 = static_cast<int>(tile % tiles_n) * p.bn;
             int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
             int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
-            if (p.tile_tab) { const int2 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; }
+            if (p.tile_tab) { const int4 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; }
             const int buf = static_cast<int>(lt & 1);
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (ok && !umma::mbar_wait(&acc_full[buf], aph)) { ok = false; if (lane == 0) atomicOr(p.err, 2); }
@@ -566,14 +576,16 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
                     long long batch, cudaStream_t s) {
     if (p.elem_bytes == 0) p.elem_bytes = 4;
     if (p.passes == 0) p.passes = 3;
-    p.stages = p.bn <= 128 ? 3 : 2;
     p.err = device_error_word();
     if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
     cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
     const int slab_cols = 128 / p.elem_bytes;
     const int b_bytes = p.b_mn ? ((p.bn + slab_cols - 1) / slab_cols) * (slab_cols * 128) : p.bn * 128;
-    const size_t smem = static_cast<size_t>(p.stages) * (2 * UM_A_BYTES + 2 * b_bytes) + 1024 + UM_TAIL_BYTES;
+    const int stage_bytes = (p.passes == 1 ? 1 : 2) * (UM_A_BYTES + b_bytes);
+    p.stages = (UM_MAX_SMEM - 1024 - UM_TAIL_BYTES) / stage_bytes;
+    if (p.stages > 6) p.stages = 6;
+    const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024 + UM_TAIL_BYTES;
     p.batch = (int)batch;
     const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + UM_BM - 1) / UM_BM) * batch;
     int dev = 0, sms = 0;
@@ -721,65 +733,89 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
 struct TransRPlan {
     const int* rel_perm; const int* rel_seg; const long long* rel_uniq; const long long* n_groups;
     int per;                    // rows per triple: 1 + n_neg
-    int2* tile_tab; long long* n_tiles; int* goff;      // goff[g]: first padded row of group g
+    int4* tile_tab; long long* n_tiles;
     long long tile_cap;
 };
 
-__global__ void transr_plan_kernel(TransRPlan pl) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// One block: tiles per group, exclusive scan, tile table (first padded row, relation id, group, valid rows).
+__global__ void __launch_bounds__(1024) transr_plan_kernel(TransRPlan pl) {
+    __shared__ long long part[1024];
     const int G = (int)*pl.n_groups;
-    long long tiles = 0;
-    for (int g = 0; g < G; ++g) {
+    const int tid = threadIdx.x;
+    const int chunk = (G + 1023) / 1024;
+    const int g0 = min(G, tid * chunk), g1 = min(G, g0 + chunk);
+    long long mine = 0;
+    for (int g = g0; g < g1; ++g) mine += ((long long)(pl.rel_seg[g + 1] - pl.rel_seg[g]) * pl.per + UM_BM - 1) / UM_BM;
+    part[tid] = mine;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {            // Hillis-Steele inclusive scan, double-synchronised
+        const long long v = tid >= o ? part[tid - o] : 0;
+        __syncthreads();
+        part[tid] += v;
+        __syncthreads();
+    }
+    long long t0 = part[tid] - mine;
+    if (tid == 1023) *pl.n_tiles = part[1023] < pl.tile_cap ? part[1023] : pl.tile_cap;
+    for (int g = g0; g < g1; ++g) {
         const long long rows = (long long)(pl.rel_seg[g + 1] - pl.rel_seg[g]) * pl.per;
         const long long nt = (rows + UM_BM - 1) / UM_BM;
-        pl.goff[g] = (int)(tiles * UM_BM);
         const int z = (int)pl.rel_uniq[g];
-        for (long long t = 0; t < nt && tiles + t < pl.tile_cap; ++t) pl.tile_tab[tiles + t] = make_int2((int)((tiles + t) * UM_BM), z);
-        tiles += nt;
+        for (long long t = 0; t < nt && t0 + t < pl.tile_cap; ++t)
+            pl.tile_tab[t0 + t] = make_int4((int)((t0 + t) * UM_BM), z, g, (int)min((long long)UM_BM, rows - t * UM_BM));
+        t0 += nt;
     }
-    *pl.n_tiles = tiles < pl.tile_cap ? tiles : pl.tile_cap;
 }
 
-// One warp per difference row, in relation-sorted order: sorted triple position p, row j of that triple.
+// One CTA per tile (8 warps x 16 rows): difference rows of the tile's group as bf16, and where each row's score goes.
 template <typename I, int NV>
 __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPlan pl, __nv_bfloat16* rows_out, long long* row_dst) {
-    const int lane = threadIdx.x & 31;
-    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (w >= a.batch * pl.per) return;
-    const int p = (int)(w / pl.per), j = (int)(w % pl.per);
-    const int G = (int)*pl.n_groups;
-    int lo = 0, hi = G - 1;                       // group of sorted position p: largest g with rel_seg[g] <= p
-    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (pl.rel_seg[mid] <= p) lo = mid; else hi = mid - 1; }
-    const long long prow = (long long)pl.goff[lo] + (long long)(p - pl.rel_seg[lo]) * pl.per + j;
-    const int i = pl.rel_perm[p];
+    const long long tile = blockIdx.x;
+    if (tile >= *pl.n_tiles) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int4 tt = pl.tile_tab[tile];
+    const int g = tt.z, valid = tt.w;
+    // first group-local row of this tile: tiles of a group are consecutive, the group's first tile starts at its first row
+    long long first = tt.x;
+    {   // walk back to the group's first tile (a group has few tiles)
+        long long t = tile;
+        while (t > 0 && pl.tile_tab[t - 1].z == g) --t;
+        first = (long long)tt.x - pl.tile_tab[t].x;
+    }
     const int dim = a.dim;
     const __nv_bfloat16* E = reinterpret_cast<const __nv_bfloat16*>(a.ent);
-    const __nv_bfloat16* hrow = E + load_id<I>(a.h, i) * dim;
-    const __nv_bfloat16* trow = E + load_id<I>(a.t, i) * dim;
-    const __nv_bfloat16 *pa = hrow, *pb = trow;
-    if (j > 0) {
-        const __nv_bfloat16* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * dim;
-        if (j - 1 < a.n_neg_head) pa = x; else pb = x;
-    }
-    Row<NV> ra, rb;
-    load_row<__nv_bfloat16, NV, true>(ra, pa, dim, lane);
-    load_row<__nv_bfloat16, NV, true>(rb, pb, dim, lane);
-    __nv_bfloat16* out = rows_out + prow * dim;
-#pragma unroll
-    for (int q = 0; q < NV; ++q) {
-        const int k = 4 * (lane + 32 * q);
-        if (k < dim) {
-            const float4 d = ra.v[q] - rb.v[q];
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(d.x, d.y), p1 = __floats2bfloat162_rn(d.z, d.w);
-            uint2 u;
-            u.x = *reinterpret_cast<unsigned*>(&p0); u.y = *reinterpret_cast<unsigned*>(&p1);
-            *reinterpret_cast<uint2*>(out + k) = u;
+    for (int rr = warp; rr < UM_BM; rr += 8) {
+        const long long prow = (long long)tt.x + rr;
+        if (rr >= valid) { if (lane == 0) row_dst[prow] = -1; continue; }       // padding row: no score
+        const long long rho = first + rr;                                        // row within the group
+        const int p = pl.rel_seg[g] + (int)(rho / pl.per), j = (int)(rho % pl.per);
+        const int i = pl.rel_perm[p];
+        const __nv_bfloat16* hrow = E + load_id<I>(a.h, i) * dim;
+        const __nv_bfloat16* trow = E + load_id<I>(a.t, i) * dim;
+        const __nv_bfloat16 *pa = hrow, *pb = trow;
+        if (j > 0) {
+            const __nv_bfloat16* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * dim;
+            if (j - 1 < a.n_neg_head) pa = x; else pb = x;
         }
+        Row<NV> ra, rb;
+        load_row<__nv_bfloat16, NV, true>(ra, pa, dim, lane);
+        load_row<__nv_bfloat16, NV, true>(rb, pb, dim, lane);
+        __nv_bfloat16* out = rows_out + prow * dim;
+#pragma unroll
+        for (int q = 0; q < NV; ++q) {
+            const int k = 4 * (lane + 32 * q);
+            if (k < dim) {
+                const float4 d = ra.v[q] - rb.v[q];
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(d.x, d.y), p1 = __floats2bfloat162_rn(d.z, d.w);
+                uint2 u;
+                u.x = *reinterpret_cast<unsigned*>(&p0); u.y = *reinterpret_cast<unsigned*>(&p1);
+                *reinterpret_cast<uint2*>(out + k) = u;
+            }
+        }
+        if (lane == 0) row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
     }
-    if (lane == 0) row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
 }
 
-struct TransRLayout { size_t off_rows, off_dst, off_tab, off_goff, off_nt, total; long long rows_cap, tile_cap; };
+struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, total; long long rows_cap, tile_cap; };
 static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel) {
     TransRLayout L;
     const long long gmax = n_rel < batch ? n_rel : batch;
@@ -788,8 +824,7 @@ static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long
     size_t o = 0;
     L.off_rows = o; o += al256((size_t)L.rows_cap * dim * 2);
     L.off_dst = o; o += al256((size_t)L.rows_cap * 8);
-    L.off_tab = o; o += al256((size_t)L.tile_cap * 8);
-    L.off_goff = o; o += al256((size_t)(gmax + 1) * 4);
+    L.off_tab = o; o += al256((size_t)L.tile_cap * 16);
     L.off_nt = o; o += 256;
     L.total = o;
     return L;
@@ -807,19 +842,16 @@ int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int*
     long long* dst = reinterpret_cast<long long*>(w + L.off_dst);
     TransRPlan pl;
     pl.rel_perm = rel_perm; pl.rel_seg = rel_seg; pl.rel_uniq = rel_uniq; pl.n_groups = n_groups; pl.per = 1 + a.n_neg;
-    pl.tile_tab = reinterpret_cast<int2*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
-    pl.goff = reinterpret_cast<int*>(w + L.off_goff); pl.tile_cap = L.tile_cap;
-    cudaError_t e = cudaMemsetAsync(dst, 0xFF, (size_t)L.rows_cap * 8, s);       // -1: padding rows produce no score
-    if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(row_dst)");
-    transr_plan_kernel<<<1, 32, 0, s>>>(pl);
+    pl.tile_tab = reinterpret_cast<int4*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
+    pl.tile_cap = L.tile_cap;
+    transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
     KGE_LAUNCH_CHECK("transr_plan_kernel");
     {
-        const int wpb = 8;
-        const unsigned blocks = (unsigned)((a.batch * pl.per + wpb - 1) / wpb);
+        const unsigned blocks = (unsigned)L.tile_cap;            // one CTA per tile; CTAs past the device-side tile count exit
         const int nv = quads_per_lane(a.dim);
 #define KGE_TP(N)                                                                                          \
-        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, wpb * 32, 0, s>>>(a, pl, rows, dst);  \
-                else transr_pack_kernel<int32_t, N><<<blocks, wpb * 32, 0, s>>>(a, pl, rows, dst); break;
+        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst);  \
+                else transr_pack_kernel<int32_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst); break;
         switch (nv) { KGE_TP(1) KGE_TP(2) default: set_error("TransR tensor-core path needs dim <= 256"); return KGE_E_UNSUPPORTED; }
 #undef KGE_TP
         KGE_LAUNCH_CHECK("transr_pack_kernel");
