@@ -56,7 +56,9 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s);
 int launch_transr_forward(const kge_problem* p, const kge_tensors* t, float* pos, float* negs, cudaStream_t s);
-size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel);
+size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel, int backward);
+int launch_transr_backward_tc(const ScoreArgs& a, float* dproj, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                              const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                              const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s);
 size_t transr_backward_workspace_bytes(const kge_problem* p);
@@ -268,9 +270,11 @@ int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t*
 size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
     if (!p || p->batch <= 0) return 256;
     const size_t rb = rows_bytes(p);
+    if (backward && tc_transr(p))
+        return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 1) + 256;
     if (backward && p->model == KGE_TRANSR) return transr_backward_workspace_bytes(p) + 256;
     if (backward) return 3 * rb + tc_bytes(p, 1) + 256;
-    if (tc_transr(p)) return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel) + 256;
+    if (tc_transr(p)) return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 0) + 256;
     return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + 256;
 }
 
@@ -334,6 +338,13 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     const size_t need = kge_score_workspace_bytes(p, 1);
     KGE_REQUIRE_PTR(workspace, "workspace");
     if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    if (tc_transr(p)) {
+        ScoreArgs a = score_args(p, t);
+        a.pos = const_cast<float*>(pos_score); a.negs = const_cast<float*>(neg_score); a.dpos = dpos; a.dneg = dneg;
+        a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel;
+        return launch_transr_backward_tc(a, g->g_rel2, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq,
+                                         (const long long*)t->n_rel_groups, p->n_rel, workspace, workspace_bytes, s);
+    }
     if (p->model == KGE_TRANSR)
         return launch_transr_backward(p, t, pos_score, neg_score, dpos, dneg, g, workspace, s);
     const size_t rb = rows_bytes(p);

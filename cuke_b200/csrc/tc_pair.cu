@@ -150,7 +150,7 @@ constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major sla
 constexpr int UM_TAIL_BYTES = 256 + 2048;                   // barriers, tensor-memory slot, EP_NORM partial sums
 constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
-enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3 };
+enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3, EP_GV = 4, EP_SCATTER = 5 };
 
 struct GemmTc {
     int m_rows, n_cols, k_len;        // extents per batch
@@ -171,6 +171,10 @@ struct GemmTc {
     const int4* tile_tab; const long long* n_tiles_dev; long long tile_cap;       // (first row, z, group, valid rows)
     // EP_NORM: score = -|| acc + rel_vec[z] ||, scattered through row_dst
     const long long* row_dst; float* pos_out; float* neg_out; const void* rel_vec; int rel_is_bf16;
+    // grouped-K mode (sum over the rows of a relation group): tile = (first k-row, k-rows, m0, output batch)
+    int group_k;
+    // EP_GV: gv_out[row] = bf16(coef[row] * (acc + rel_vec[z]));  EP_SCATTER: rows go to neg_out (signed by side) / pos_out
+    const float* coef; __nv_bfloat16* gv_out; int sc_n_neg; int sc_n_neg_head;
     int32_t* err;
 };
 
@@ -240,15 +244,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
                 int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
                 int za = b;
-                if (p.tile_tab) { const int4 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; za = 0; }
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                int kbase = 0, nkb = num_kb;
+                if (p.tile_tab) {
+                    const int4 tt = p.tile_tab[tile];
+                    n0 = 0; za = 0;
+                    if (p.group_k) { kbase = tt.x; nkb = tt.y / bk; m0 = tt.z; b = 0; } else { m0 = tt.x; b = tt.y; }
+                }
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = static_cast<int>(it % p.stages);
                     const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
                     umma::mbar_expect_tx(&full[s], tx_bytes);
-                    const int k0 = kb * bk;
+                    const int k0 = kbase + kb * bk;
                     const bool lo = p.passes != 1;
                     if (!p.a_mn) {
                         umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, za, &full[s]);
@@ -295,7 +304,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }   // drained?
                 umma::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * acc_cols;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int nkb = (p.tile_tab && p.group_k) ? p.tile_tab[tile].y / bk : num_kb;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = static_cast<int>(it % p.stages);
                     const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
                     if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
@@ -339,7 +349,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             int n0 = static_cast<int>(tile % tiles_n) * p.bn;
             int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
             int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
-            if (p.tile_tab) { const int4 tt = p.tile_tab[tile]; n0 = 0; m0 = tt.x; b = tt.y; }
+            if (p.tile_tab) {
+                const int4 tt = p.tile_tab[tile];
+                n0 = 0;
+                if (p.group_k) { m0 = tt.z; b = tt.w; } else { m0 = tt.x; b = tt.y; }
+            }
             const int buf = static_cast<int>(lt & 1);
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (ok && !umma::mbar_wait(&acc_full[buf], aph)) { ok = false; if (lane == 0) atomicOr(p.err, 2); }
@@ -372,6 +386,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                             ssq = fmaf(t, t, ssq);
                         }
                     }
+                    continue;
+                }
+                if (p.ep == EP_GV) {            // dL/dv rows for the backward products, stored as bf16
+                    const float cf = p.coef[m];
+                    __nv_bfloat16* go = p.gv_out + static_cast<long long>(m) * p.n_cols + nbase;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < lim) {
+                            const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
+                            const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
+                                                           : reinterpret_cast<const float*>(p.rel_vec)[ri];
+                            go[j] = __float2bfloat16_rn(cf * (v[j] + rv));
+                        }
+                    }
+                    continue;
+                }
+                if (p.ep == EP_SCATTER) {       // gradient of the difference row: to the replaced row's slot (signed) or to GD0
+                    const long long dst = p.row_dst[m];
+                    if (dst == -1) continue;
+                    float* go; float sg = 1.f;
+                    if (dst >= 0) { go = p.neg_out + dst * p.n_cols + nbase; if ((int)(dst % p.sc_n_neg) >= p.sc_n_neg_head) sg = -1.f; }
+                    else go = p.pos_out + (-2 - dst) * p.n_cols + nbase;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < lim) go[j] = sg * v[j];
                     continue;
                 }
                 if (p.ep == EP_DIST) {
@@ -735,6 +774,7 @@ struct TransRPlan {
     int per;                    // rows per triple: 1 + n_neg
     int4* tile_tab; long long* n_tiles;
     long long tile_cap;
+    int4* tile_tab2; long long* n_tiles2; int tiles_m2;     // grouped-K tiles of the dP product (backward), or NULL
 };
 
 // One block: tiles per group, exclusive scan, tile table (first padded row, relation id, group, valid rows).
@@ -762,13 +802,18 @@ __global__ void __launch_bounds__(1024) transr_plan_kernel(TransRPlan pl) {
         const int z = (int)pl.rel_uniq[g];
         for (long long t = 0; t < nt && t0 + t < pl.tile_cap; ++t)
             pl.tile_tab[t0 + t] = make_int4((int)((t0 + t) * UM_BM), z, g, (int)min((long long)UM_BM, rows - t * UM_BM));
+        if (pl.tile_tab2)
+            for (int mt = 0; mt < pl.tiles_m2; ++mt)
+                pl.tile_tab2[(long long)g * pl.tiles_m2 + mt] = make_int4((int)(t0 * UM_BM), (int)(nt * UM_BM), mt * UM_BM, g);
         t0 += nt;
     }
+    if (pl.tile_tab2 && tid == 0) *pl.n_tiles2 = (long long)G * pl.tiles_m2;
 }
 
 // One CTA per tile (8 warps x 16 rows): difference rows of the tile's group as bf16, and where each row's score goes.
 template <typename I, int NV>
-__global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPlan pl, __nv_bfloat16* rows_out, long long* row_dst) {
+__global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPlan pl, __nv_bfloat16* rows_out, long long* row_dst,
+                                                          float* coef, int* trow0) {
     const long long tile = blockIdx.x;
     if (tile >= *pl.n_tiles) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -785,7 +830,11 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
     const __nv_bfloat16* E = reinterpret_cast<const __nv_bfloat16*>(a.ent);
     for (int rr = warp; rr < UM_BM; rr += 8) {
         const long long prow = (long long)tt.x + rr;
-        if (rr >= valid) { if (lane == 0) row_dst[prow] = -1; continue; }       // padding row: no score
+        if (rr >= valid) {                                                       // padding row: zeros, no score, no gradient
+            for (int k = lane * 4; k < dim; k += 128) *reinterpret_cast<uint2*>(rows_out + prow * dim + k) = make_uint2(0u, 0u);
+            if (lane == 0) { row_dst[prow] = -1; if (coef) coef[prow] = 0.f; }
+            continue;
+        }
         const long long rho = first + rr;                                        // row within the group
         const int p = pl.rel_seg[g] + (int)(rho / pl.per), j = (int)(rho % pl.per);
         const int i = pl.rel_perm[p];
@@ -811,12 +860,43 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
                 *reinterpret_cast<uint2*>(out + k) = u;
             }
         }
-        if (lane == 0) row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
+        if (lane == 0) {
+            row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
+            if (coef) {      // dL/dv = (dS / S) v
+                const float sc = j == 0 ? a.pos[i] : a.negs[(long long)i * a.n_neg + (j - 1)];
+                const float ds = j == 0 ? a.dpos[i] : a.dneg[(long long)i * a.n_neg + (j - 1)];
+                coef[prow] = sc != 0.f ? ds / sc : 0.f;
+                if (j == 0) trow0[i] = (int)prow;
+            }
+        }
     }
 }
 
-struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, total; long long rows_cap, tile_cap; };
-static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel) {
+// Per triple: g_head = GD0 - sum of its tail-replaced g_neg rows, g_tail = -GD0 - sum of its head-replaced g_neg rows,
+// g_rel = sum of its dL/dv rows (bf16, consecutive in the packed order), all in ascending j.
+__global__ void __launch_bounds__(256) transr_reduce_tc_kernel(ScoreArgs a, const __nv_bfloat16* gv, const float* gd0, const int* trow0) {
+    const int lane = threadIdx.x & 31;
+    const long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= a.batch) return;
+    const int dim = a.dim, n_neg = a.n_neg;
+    const long long r0 = trow0[i];
+    for (int k = lane; k < dim; k += 32) {
+        const float g0 = gd0[i * dim + k];
+        float gh = g0, gt = -g0, gr = __bfloat162float(gv[r0 * dim + k]);
+        for (int j = 0; j < n_neg; ++j) {
+            const float gx = a.g_neg[(i * n_neg + j) * dim + k];
+            if (j < a.n_neg_head) gt -= gx; else gh -= gx;
+            gr += __bfloat162float(gv[(r0 + 1 + j) * dim + k]);
+        }
+        a.g_head[i * dim + k] = gh;
+        a.g_tail[i * dim + k] = gt;
+        a.g_rel[i * dim + k] = gr;
+    }
+}
+
+struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, off_tab2, off_coef, off_trow0, off_gv, off_gd0, total;
+                      long long rows_cap, tile_cap, gmax; int tiles_m2; };
+static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel, bool backward = false) {
     TransRLayout L;
     const long long gmax = n_rel < batch ? n_rel : batch;
     L.rows_cap = batch * (1 + n_neg) + gmax * UM_BM;
@@ -826,32 +906,48 @@ static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long
     L.off_dst = o; o += al256((size_t)L.rows_cap * 8);
     L.off_tab = o; o += al256((size_t)L.tile_cap * 16);
     L.off_nt = o; o += 256;
+    L.gmax = gmax; L.tiles_m2 = (dim + UM_BM - 1) / UM_BM;
+    L.off_tab2 = o; o += backward ? al256((size_t)gmax * L.tiles_m2 * 16) : 0;
+    L.off_coef = o; o += backward ? al256((size_t)L.rows_cap * 4) : 0;
+    L.off_trow0 = o; o += backward ? al256((size_t)batch * 4) : 0;
+    L.off_gv = o; o += backward ? al256((size_t)L.rows_cap * dim * 2) : 0;
+    L.off_gd0 = o; o += backward ? al256((size_t)batch * dim * 4) : 0;
     L.total = o;
     return L;
 }
-size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel) { return transr_layout(batch, n_neg, dim, n_rel).total; }
+size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel, int backward) {
+    return transr_layout(batch, n_neg, dim, n_rel, backward != 0).total;
+}
 
-// a: ScoreArgs of the problem (bf16 tables); rel grouping from the inspector over r.
-int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
-                             const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+// a: ScoreArgs of the problem (bf16 tables); rel grouping from the inspector over r.  backward == false: scores into
+// a.pos / a.negs.  backward == true: a.pos/a.negs/a.dpos/a.dneg are inputs, gradients go to a.g_head, a.g_tail, a.g_neg,
+// a.g_rel and dproj (n_groups, dim, dim).
+static int transr_tc(const ScoreArgs& a, bool backward, float* dproj, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                     const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
     if (a.batch <= 0) return 0;
-    const TransRLayout L = transr_layout(a.batch, a.n_neg, a.dim, n_rel);
+    const TransRLayout L = transr_layout(a.batch, a.n_neg, a.dim, n_rel, backward);
     if (ws_bytes < L.total) { set_error("TransR tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
     __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(w + L.off_rows);
     long long* dst = reinterpret_cast<long long*>(w + L.off_dst);
+    float* coef = backward ? reinterpret_cast<float*>(w + L.off_coef) : nullptr;
+    int* trow0 = backward ? reinterpret_cast<int*>(w + L.off_trow0) : nullptr;
+    __nv_bfloat16* gv = reinterpret_cast<__nv_bfloat16*>(w + L.off_gv);
+    float* gd0 = reinterpret_cast<float*>(w + L.off_gd0);
     TransRPlan pl;
     pl.rel_perm = rel_perm; pl.rel_seg = rel_seg; pl.rel_uniq = rel_uniq; pl.n_groups = n_groups; pl.per = 1 + a.n_neg;
     pl.tile_tab = reinterpret_cast<int4*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
     pl.tile_cap = L.tile_cap;
+    pl.tile_tab2 = backward ? reinterpret_cast<int4*>(w + L.off_tab2) : nullptr;
+    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2;
     transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
     KGE_LAUNCH_CHECK("transr_plan_kernel");
     {
         const unsigned blocks = (unsigned)L.tile_cap;            // one CTA per tile; CTAs past the device-side tile count exit
         const int nv = quads_per_lane(a.dim);
 #define KGE_TP(N)                                                                                          \
-        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst);  \
-                else transr_pack_kernel<int32_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst); break;
+        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, coef, trow0);  \
+                else transr_pack_kernel<int32_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, coef, trow0); break;
         switch (nv) { KGE_TP(1) KGE_TP(2) default: set_error("TransR tensor-core path needs dim <= 256"); return KGE_E_UNSUPPORTED; }
 #undef KGE_TP
         KGE_LAUNCH_CHECK("transr_pack_kernel");
@@ -859,14 +955,51 @@ int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int*
     CUtensorMap ma, mb;
     int rc;
     const uint64_t lda = (uint64_t)a.dim * 2;
+    const int bn = (a.dim + 15) / 16 * 16;
+    // v = diff . P[r]: A = packed rows (K-major), B = P[r] as stored (MN-major)
     if ((rc = make_tensor_map_3d(&ma, rows, 2, 1, L.rows_cap, a.dim, lda, lda * L.rows_cap, UM_BM, 64))) return rc;
     if ((rc = make_tensor_map_3d(&mb, a.rel2, 2, n_rel, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
-    p.m_rows = (int)L.rows_cap; p.n_cols = a.dim; p.k_len = a.dim; p.bn = (a.dim + 15) / 16 * 16;
-    p.a_mn = 0; p.b_mn = 1; p.elem_bytes = 2; p.passes = 1; p.ep = EP_NORM;
+    p.m_rows = (int)L.rows_cap; p.n_cols = a.dim; p.k_len = a.dim; p.bn = bn;
+    p.a_mn = 0; p.b_mn = 1; p.elem_bytes = 2; p.passes = 1;
     p.tile_tab = pl.tile_tab; p.n_tiles_dev = pl.n_tiles; p.tile_cap = L.tile_cap;
-    p.row_dst = dst; p.pos_out = a.pos; p.neg_out = a.negs; p.rel_vec = a.rel; p.rel_is_bf16 = 1;
-    return run_gemm(ma, ma, mb, mb, p, 1, s);
+    p.row_dst = dst; p.rel_vec = a.rel; p.rel_is_bf16 = 1;
+    if (!backward) {
+        p.ep = EP_NORM; p.pos_out = a.pos; p.neg_out = a.negs;
+        return run_gemm(ma, ma, mb, mb, p, 1, s);
+    }
+    p.ep = EP_GV; p.coef = coef; p.gv_out = gv;
+    if ((rc = run_gemm(ma, ma, mb, mb, p, 1, s))) return rc;
+    // GD = GV . P[r]^T: A = GV rows (K-major over j), B[n = i'][k = j] = P[r][i'][j] (K-major as stored); rows scatter to slots
+    CUtensorMap mg, mp;
+    if ((rc = make_tensor_map_3d(&mg, gv, 2, 1, L.rows_cap, a.dim, lda, lda * L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mp, a.rel2, 2, n_rel, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
+    p.b_mn = 0; p.ep = EP_SCATTER; p.neg_out = a.g_neg; p.pos_out = gd0; p.sc_n_neg = a.n_neg > 0 ? a.n_neg : 1; p.sc_n_neg_head = a.n_neg_head;
+    if ((rc = run_gemm(mg, mg, mp, mp, p, 1, s))) return rc;
+    // dP[g] = sum over the group's rows of diff^T (x) GV: both operands MN-major, K runs over the (zero-padded) rows
+    CUtensorMap md, mv;
+    if ((rc = make_tensor_map_3d(&md, rows, 2, 1, L.rows_cap, a.dim, lda, lda * L.rows_cap, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mv, gv, 2, 1, L.rows_cap, a.dim, lda, lda * L.rows_cap, 64, 64))) return rc;
+    GemmTc q;
+    memset(&q, 0, sizeof(q));
+    q.m_rows = a.dim; q.n_cols = a.dim; q.k_len = UM_BM; q.bn = bn; q.a_mn = 1; q.b_mn = 1; q.elem_bytes = 2; q.passes = 1;
+    q.tile_tab = pl.tile_tab2; q.n_tiles_dev = pl.n_tiles2; q.tile_cap = L.gmax * L.tiles_m2; q.group_k = 1;
+    q.ep = EP_STORE; q.out = dproj; q.out_ld = a.dim; q.out_batch_rows = a.dim;
+    if ((rc = run_gemm(md, md, mv, mv, q, 1, s))) return rc;
+    const int wpb = 8;
+    transr_reduce_tc_kernel<<<(unsigned)((a.batch + wpb - 1) / wpb), wpb * 32, 0, s>>>(a, gv, gd0, trow0);
+    KGE_LAUNCH_CHECK("transr_reduce_tc_kernel");
+    return 0;
 }
+
+int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+    return transr_tc(a, false, nullptr, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+}
+int launch_transr_backward_tc(const ScoreArgs& a, float* dproj, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                              const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+    return transr_tc(a, true, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+}
+
 }  // namespace kge

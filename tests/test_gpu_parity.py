@@ -198,9 +198,12 @@ def _check_grads(p, nnh, chunk, bf16=False, tol=FP32_TOL, precision="fp32"):
     g = p["g"]
     B = len(p["h"])
     dpos_np = g.standard_normal(B).astype(np.float32)
-    nshape = (B, p["neg"].shape[1])
-    dneg_np = g.standard_normal(nshape).astype(np.float32)
-    dneg = to_dev(dneg_np if p["neg_mode"] == "per_triple" else dneg_np.reshape(B // chunk, chunk, -1))
+    if p["neg"] is None:
+        dneg_np, dneg = None, None
+    else:
+        nshape = (B, p["neg"].shape[1])
+        dneg_np = g.standard_normal(nshape).astype(np.float32)
+        dneg = to_dev(dneg_np if p["neg_mode"] == "per_triple" else dneg_np.reshape(B // chunk, chunk, -1))
     pos, negs, gE, gR, gP = gpu_grads_dense(p, sc, h, r, t, neg, to_dev(dpos_np), dneg)
     E, R, P2 = (bf16_round(p[k]) for k in ("E", "R", "P2")) if bf16 else (p["E"], p["R"], p["P2"])
     oE, oR, oP = oracle.grads(model, E, R, P2, p["h"], p["r"], p["t"], dpos_np, p["neg"], dneg_np, p["neg_mode"], nnh, chunk)
@@ -229,6 +232,17 @@ def test_backward_chunk_shared(model, d, chunk, nchunks, nn, head):
         d = min(d, 200)
     p = make_problem(model, seed=5 * d + chunk, ne=150, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
     _check_grads(p, nn if head else 0, chunk)
+
+
+@pytest.mark.parametrize("d,B,nn,nnh,nr", [(200, 64, 16, 8, 11), (64, 300, 5, 0, 3), (256, 40, 33, 33, 40), (200, 96, 0, 0, 2)])
+def test_transr_backward_tensor_cores_bf16(d, B, nn, nnh, nr):
+    """TransR gradients over bf16 tables on the tensor cores (three relation-grouped bf16 products): 2e-2 relative."""
+    from cuke_b200 import scoring
+    p = make_problem("TransR", seed=2 * d + B, ne=120, nr=nr, d=d, B=B, nn=max(nn, 1), neg_mode="per_triple" if nn else "none", zipf=True)
+    if not nn:
+        p["neg"] = None
+    _check_grads(p, nnh, 0, bf16=True, tol=BF16_TOL, precision="tensor")
+    assert scoring.device_flags() == 0
 
 
 @pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx"])
