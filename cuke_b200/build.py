@@ -4,7 +4,7 @@
 
 Every .cu is compiled to an object under cuke_b200/csrc/build/ (in parallel) and linked into one shared
 library with C linkage entry points only (include/kge_b200.h).  `-Xptxas -v` output (registers, spills,
-shared memory per kernel) is kept in cuke_b200/csrc/build/ptxas.log.
+shared memory per kernel) is kept per source file in cuke_b200/csrc/build/<name>.ptxas.log.
 """
 from __future__ import annotations
 
@@ -60,18 +60,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, r.returncode, r.stdout + r.stderr
 
-    logs = []
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for src, rc, out in ex.map(compile_one, jobs):
-                logs.append(f"==== {os.path.basename(src)}\n{out}")
+                with open(os.path.join(BUILD, os.path.basename(src)[:-3] + ".ptxas.log"), "w") as f:
+                    f.write(out)
                 if rc != 0:
                     sys.stderr.write(out)
                     raise RuntimeError(f"nvcc failed on {src}")
                 if verbose:
                     print(out)
-        with open(os.path.join(BUILD, "ptxas.log"), "a") as f:
-            f.write("\n".join(logs))
     objs = [os.path.join(BUILD, os.path.basename(s)[:-3] + ".o") for s in sources]
     if force or jobs or _stale(LIB, objs):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]

@@ -143,11 +143,12 @@ __global__ void __launch_bounds__(256) tc_colsum_kernel(const float* hi, const f
     colsum[(long long)c * n_neg + j] = s;
 }
 
-// ---- the tensor-core tile kernel -------------------------------------------------------------------------------
+// ---- the tensor-core tile kernels ------------------------------------------------------------------------------
 constexpr int UM_BM = 128, UM_BK = 32;                       // 32 fp32 = one 128-byte swizzle row
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 4;                // 16 KiB per A tile (either major)
 constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major slab: 32 k-rows x 128 bytes
-constexpr int UM_TAIL_BYTES = 256 + 2048;                   // barriers, tensor-memory slot, EP_NORM partial sums
+constexpr int UM_EPI_BYTES = 8 * 32 * 32 * 4;                // epilogue staging: one 32x32 fp32 square per epilogue warp
+constexpr int UM_TAIL_BYTES = 256 + UM_EPI_BYTES;            // barriers and tensor-memory slot, then the staging squares
 constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
 enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3, EP_GV = 4, EP_SCATTER = 5 };
@@ -175,6 +176,7 @@ struct GemmTc {
     int group_k;
     // EP_GV: gv_out[row] = bf16(coef[row] * (acc + rel_vec[z]));  EP_SCATTER: rows go to neg_out (signed by side) / pos_out
     const float* coef; __nv_bfloat16* gv_out; int sc_n_neg; int sc_n_neg_head;
+    int pair;                         // 1: CTA pairs (256-row tiles, umma_pair_kernel)
     int32_t* err;
 };
 
@@ -186,6 +188,164 @@ __device__ __forceinline__ float sqrt_approx(float x) {       // MUFU square roo
 
 constexpr int UM_THREADS = 320;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2..9: epilogue
 constexpr int UM_EPI_WARPS = 8;
+
+// Epilogue of one 128-row x bn_tile accumulator, run by the eight epilogue warps of a CTA.  A warp may only read the
+// tensor-memory lane quarter (warp % 4); the two warps of a quarter take alternate 32-column chunks.  m0 is the first
+// row of THIS CTA's 128 rows.  `drained` is the (shared::cluster) address of the barrier that hands the accumulator
+// back to the MMA thread; every warp arrives on it once its tensor-memory reads are done.
+//
+// tcgen05.ld hands each thread one ROW of the chunk (32 consecutive columns).  Written out like that, a warp's store
+// instruction would touch 32 different rows, and every per-column operand would be a separate load per element.  So the
+// chunk goes through a 32x32 XOR-swizzled shared-memory staging square (conflict-free both ways) and comes back with
+// lane = COLUMN: global loads and stores are then 128-byte row segments, per-column operands are one register per lane,
+// per-row operands one shuffle per row, and the fix-up test is a mask bit instead of a branch per element.
+__device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
+                                              int bn_tile, int buf, uint32_t drained, float* epi_smem) {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = q * 32 + lane;                 // row of the tile held by this thread after tcgen05.ld
+    const int n_chunks32 = (bn_tile + 31) / 32;
+    const int m = m0 + row;
+    const bool row_ok = m < p.m_rows;
+    const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
+    if (p.ep == EP_NORM) {
+        // squared norm of (acc + R[z]) over the row: nothing is stored per element, the thread-per-row form is kept
+        float* ssq_part = epi_smem;                // [2 accumulators][2 halves][128 rows]
+        float ssq = 0.f;
+#pragma unroll 1
+        for (int c = half; c < n_chunks32; c += 2) {
+            float v[32];
+            umma::tmem_ld32(t_row + c * 32, v);     // warp-collective
+            const int nbase = n0 + c * 32;
+            const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < lim) {
+                    const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
+                    const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
+                                                   : reinterpret_cast<const float*>(p.rel_vec)[ri];
+                    const float t = v[j] + rv;
+                    ssq = fmaf(t, t, ssq);
+                }
+            }
+        }
+        umma::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive_cluster(drained);
+        ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
+        asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight epilogue warps
+        if (half == 0) {
+            const long long dst = p.row_dst[m];               // >= 0: negative score index, <= -2: positive -2-i, -1: padding
+            const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
+            if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
+        }
+        return;
+    }
+
+    float* stg = epi_smem + (warp - 2) * 1024;                  // this warp's 32x32 staging square
+    const int mq = m0 + q * 32;                                  // first row of this warp's quarter
+    const int rows_here = min(32, p.m_rows - mq);               // rows of the quarter that exist (may be <= 0)
+    const long long grow0 = static_cast<long long>(b) * p.m_rows + mq;        // row of A-side per-row vectors
+    // per-row operands live in the lane that owns the row and are broadcast by shuffle
+    float row_op = 0.f;
+    if (row_ok) {
+        if (p.ep == EP_DIST) row_op = p.sq_a[grow0 + lane];
+        else if (p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
+        else if (p.ep == EP_GV) row_op = p.coef[m];
+    }
+#pragma unroll 1
+    for (int c = half; c < n_chunks32; c += 2) {
+        float v[32];
+        umma::tmem_ld32(t_row + c * 32, v);         // warp-collective
+        const int nbase = n0 + c * 32;
+        const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
+        if (rows_here <= 0 || lim <= 0) continue;    // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
+        __syncwarp();
+        const bool col_ok = lane < lim;
+        const int col = nbase + lane;
+        if (p.ep == EP_DIST) {
+            const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
+            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
+            uint32_t bad = 0;
+#pragma unroll 8
+            for (int r = 0; r < rows_here; ++r, o += p.out_ld) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
+                const float d2 = fmaf(-2.f, x, nn);
+                bad |= (d2 < 0.015625f * nn ? 1u : 0u) << r;       // cancellation: listed for exact recomputation
+                if (col_ok) *o = -sqrt_approx(fmaxf(d2, 0.f));
+            }
+            if (!col_ok) bad = 0;
+            if (__any_sync(0xffffffffu, bad != 0)) {
+                while (bad) {
+                    const int r = __ffs(bad) - 1;
+                    bad &= bad - 1;
+                    const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
+                    if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow0 + r) * p.n_cols + col;
+                }
+            }
+        } else if (p.ep == EP_RANK1) {
+            const float* yh = p.y_hi + grow0 * p.out_ld + col;
+            const float* yl = p.y_lo + grow0 * p.out_ld + col;
+            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
+            // the y rows come from memory: all loads of a 16-row batch are issued before the first store
+#pragma unroll 1
+            for (int r0 = 0; r0 < rows_here; r0 += 16) {
+                float y[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const bool ok = col_ok && r0 + i < rows_here;
+                    const long long off = static_cast<long long>(r0 + i) * p.out_ld;
+                    y[i] = ok ? __ldg(yh + off) + __ldg(yl + off) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int r = r0 + i;
+                    const float x = stg[r * 32 + (lane ^ r)];
+                    const float rs = __shfl_sync(0xffffffffu, row_op, r);
+                    if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[i], -x);
+                }
+            }
+        } else if (p.ep == EP_GV) {          // dL/dv rows for the backward products, stored as bf16
+            float rv = 0.f;
+            if (col_ok) {
+                const long long ri = static_cast<long long>(b) * p.n_cols + col;
+                rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
+                                   : reinterpret_cast<const float*>(p.rel_vec)[ri];
+            }
+            __nv_bfloat16* go = p.gv_out + static_cast<long long>(mq) * p.n_cols + col;
+#pragma unroll 8
+            for (int r = 0; r < rows_here; ++r, go += p.n_cols) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                const float cf = __shfl_sync(0xffffffffu, row_op, r);
+                if (col_ok) *go = __float2bfloat16_rn(cf * (x + rv));
+            }
+        } else if (p.ep == EP_SCATTER) {     // gradient of the difference row: to the replaced row's slot (signed) or to GD0
+#pragma unroll 4
+            for (int r = 0; r < rows_here; ++r) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                const long long dst = p.row_dst[mq + r];          // same address in every lane: one broadcast load
+                if (dst == -1 || !col_ok) continue;
+                if (dst >= 0) p.neg_out[dst * p.n_cols + col] = ((int)(dst % p.sc_n_neg) >= p.sc_n_neg_head) ? -x : x;
+                else p.pos_out[(-2 - dst) * p.n_cols + col] = x;
+            }
+        } else {                             // EP_STORE
+            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
+#pragma unroll 8
+            for (int r = 0; r < rows_here; ++r, o += p.out_ld) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                if (col_ok) *o = x;
+            }
+        }
+        __syncwarp();                            // the square is rewritten by the next chunk
+    }
+    // this warp is done reading the accumulator: hand it back to the MMA thread
+    umma::tc_fence_before();
+    __syncwarp();
+    if (lane == 0) umma::mbar_arrive_cluster(drained);
+}
 
 // Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
 // working at the same time share A rows in L2).  Two accumulators in tensor memory alternate, so the epilogue of tile i
@@ -210,7 +370,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     uint64_t* acc_full = empty + p.stages;          // [2] accumulator written  (MMA -> epilogue)
     uint64_t* acc_empty = acc_full + 2;             // [2] accumulator drained  (epilogue -> MMA)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    float* ssq_part = reinterpret_cast<float*>(tmem_slot + 4);       // EP_NORM: [2 accumulators][2 halves][128 rows]
+    float* epi_smem = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + 256);      // staging squares (EP_NORM: partial sums)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (p.k_len + bk - 1) / bk;
@@ -218,8 +378,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     const uint32_t tmem_cols = 2 * acc_cols;        // <= 512, the whole tensor memory at bn > 128
     const int tiles_n = (p.n_cols + p.bn - 1) / p.bn;
     const int tiles_m = (p.m_rows + UM_BM - 1) / UM_BM;
-    // grouped mode: the tile list comes from device memory (one n-tile; rows of A are absolute; z selects the B matrix)
-    const long long n_tiles = p.tile_tab ? min(*p.n_tiles_dev, p.tile_cap) : static_cast<long long>(tiles_n) * tiles_m * p.batch;
+    // grouped mode: the tile list comes from device memory (one n-tile; rows of A are absolute; z selects the B matrix).
+    // The host keeps the tile count below 2^31, so 32-bit tile arithmetic is exact.
+    const int n_tiles = static_cast<int>(p.tile_tab ? min(*p.n_tiles_dev, p.tile_cap)
+                                                    : static_cast<long long>(tiles_n) * tiles_m * p.batch);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
@@ -237,12 +399,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         if (lane == 0) {
             umma::prefetch_tensormap(&map_a_hi); umma::prefetch_tensormap(&map_a_lo);
             umma::prefetch_tensormap(&map_b_hi); umma::prefetch_tensormap(&map_b_lo);
-            long long it = 0;                      // k-blocks issued so far (ring position)
+            int s = 0; uint32_t ph = 0;            // ring position: stage and its phase bit
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                int n0 = static_cast<int>(tile % tiles_n) * p.bn;
-                int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
-                int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int tq = tile / tiles_n;
+                int n0 = (tile - tq * tiles_n) * p.bn;
+                int b = tq / tiles_m;
+                int m0 = (tq - b * tiles_m) * UM_BM;
                 int za = b;
                 int kbase = 0, nkb = num_kb;
                 if (p.tile_tab) {
@@ -250,9 +413,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     n0 = 0; za = 0;
                     if (p.group_k) { kbase = tt.x; nkb = tt.y / bk; m0 = tt.z; b = 0; } else { m0 = tt.x; b = tt.y; }
                 }
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = static_cast<int>(it % p.stages);
-                    const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
+                for (int kb = 0; kb < nkb; ++kb) {
                     if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
@@ -277,6 +438,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                             if (lo) umma::tma_load_3d(b_lo + sl * slab_bytes, &map_b_lo, n0 + slab_cols * sl, k0, b, &full[s]);
                         }
                     }
+                    if (++s == p.stages) { s = 0; ph ^= 1; }
                 }
             }
         }
@@ -295,19 +457,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
             const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
             const bool single = p.passes == 1;
-            long long it = 0;
-            long long lt = 0;                      // tiles done by this CTA
+            int s = 0; uint32_t ph = 0;
+            int lt = 0;                            // tiles done by this CTA
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
-                const int buf = static_cast<int>(lt & 1);
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+                const int buf = lt & 1;
                 const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
                 if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }   // drained?
                 umma::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * acc_cols;
                 const int nkb = (p.tile_tab && p.group_k) ? p.tile_tab[tile].y / bk : num_kb;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = static_cast<int>(it % p.stages);
-                    const uint32_t ph = static_cast<uint32_t>(it / p.stages) & 1;
+                for (int kb = 0; kb < nkb; ++kb) {
                     if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
                     umma::tc_fence_after();
                     const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;     // start address field
@@ -332,136 +492,216 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                         }
                     }
                     umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
+                    if (++s == p.stages) { s = 0; ph ^= 1; }
                 }
                 umma::mma_commit(&acc_full[buf]);         // accumulator complete (or abandoned)
             }
         }
     } else {
-        // ---- epilogue: a warp may only read the TMEM lane quarter (warp % 4); two warps share each quarter and take
-        //      alternate 32-column chunks ---------------------------------------------------------------------------------
-        const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int row = q * 32 + lane;                 // row of the tile held by this thread
-        const int n_chunks32 = (p.bn + 31) / 32;
-        long long lt = 0;
-        bool ok = true;
-        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
-            int n0 = static_cast<int>(tile % tiles_n) * p.bn;
-            int m0 = static_cast<int>((tile / tiles_n) % tiles_m) * UM_BM;
-            int b = static_cast<int>(tile / (static_cast<long long>(tiles_n) * tiles_m));
+        // ---- epilogue ---------------------------------------------------------------------------------------------
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+            const int tq = tile / tiles_n;
+            int n0 = (tile - tq * tiles_n) * p.bn;
+            int b = tq / tiles_m;
+            int m0 = (tq - b * tiles_m) * UM_BM;
             if (p.tile_tab) {
                 const int4 tt = p.tile_tab[tile];
                 n0 = 0;
                 if (p.group_k) { m0 = tt.z; b = tt.w; } else { m0 = tt.x; b = tt.y; }
             }
-            const int buf = static_cast<int>(lt & 1);
+            const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-            if (ok && !umma::mbar_wait(&acc_full[buf], aph)) { ok = false; if (lane == 0) atomicOr(p.err, 2); }
-            if (!ok) break;                                // warp-uniform: the wait result is the same for all lanes
+            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }   // warp-uniform result
             umma::tc_fence_after();
-            const uint32_t tmem_d = tmem_base + buf * acc_cols;
-            const int m = m0 + row;
-            const bool row_ok = m < p.m_rows;
-            const long long grow = static_cast<long long>(b) * p.m_rows + m;           // row of A-side per-row vectors
-            float* orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld + n0;
-            const float sa = (p.ep == EP_DIST && row_ok) ? p.sq_a[grow] : 0.f;
-            const float rs = (p.ep == EP_RANK1 && row_ok) ? p.scale[grow] : 0.f;
-            float ssq = 0.f;
-#pragma unroll 1
-            for (int c = half; c < n_chunks32; c += 2) {
-                float v[32];
-                umma::tmem_ld32(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);   // warp-collective
-                if (!row_ok) continue;
-                const int nbase = n0 + c * 32;
-                const int lim = min(32, min(p.bn - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
-                if (lim <= 0) continue;
-                if (p.ep == EP_NORM) {          // squared norm of (acc + R[z]) over the row; nothing is stored per element
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < lim) {
-                            const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
-                            const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
-                                                           : reinterpret_cast<const float*>(p.rel_vec)[ri];
-                            const float t = v[j] + rv;
-                            ssq = fmaf(t, t, ssq);
-                        }
-                    }
-                    continue;
-                }
-                if (p.ep == EP_GV) {            // dL/dv rows for the backward products, stored as bf16
-                    const float cf = p.coef[m];
-                    __nv_bfloat16* go = p.gv_out + static_cast<long long>(m) * p.n_cols + nbase;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < lim) {
-                            const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
-                            const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
-                                                           : reinterpret_cast<const float*>(p.rel_vec)[ri];
-                            go[j] = __float2bfloat16_rn(cf * (v[j] + rv));
-                        }
-                    }
-                    continue;
-                }
-                if (p.ep == EP_SCATTER) {       // gradient of the difference row: to the replaced row's slot (signed) or to GD0
-                    const long long dst = p.row_dst[m];
-                    if (dst == -1) continue;
-                    float* go; float sg = 1.f;
-                    if (dst >= 0) { go = p.neg_out + dst * p.n_cols + nbase; if ((int)(dst % p.sc_n_neg) >= p.sc_n_neg_head) sg = -1.f; }
-                    else go = p.pos_out + (-2 - dst) * p.n_cols + nbase;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < lim) go[j] = sg * v[j];
-                    continue;
-                }
-                if (p.ep == EP_DIST) {
-                    const float* sb = p.sq_b + static_cast<long long>(b) * p.n_cols + nbase;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < lim) {
-                            const float nn = sa + sb[j];
-                            const float d2 = fmaf(-2.f, v[j], nn);
-                            if (d2 < 0.015625f * nn) {       // cancellation: list for exact recomputation
-                                const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
-                                if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + (nbase + j);
-                            }
-                            v[j] = -sqrt_approx(fmaxf(d2, 0.f));
-                        }
-                    }
-                } else if (p.ep == EP_RANK1) {
-                    const float* yh = p.y_hi + grow * p.out_ld + nbase;
-                    const float* yl = p.y_lo + grow * p.out_ld + nbase;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < lim) v[j] = fmaf(rs, yh[j] + yl[j], -v[j]);
-                }
-                if (lim == 32 && (p.out_ld & 3) == 0) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(orow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < lim) orow[c * 32 + j] = v[j];
-                }
-            }
-            // this warp is done reading the accumulator: hand it back to the MMA warp
-            umma::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
-            if (p.ep == EP_NORM) {          // the two warps of a lane quarter hold the two halves of each row's sum
-                ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
-                asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight epilogue warps
-                if (half == 0) {
-                    const long long dst = p.row_dst[m];               // >= 0: negative score index, <= -2: positive -2-i, -1: padding
-                    const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
-                    if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
-                }
-            }
+            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem);
         }
     }
     umma::tc_fence_before();
     __syncthreads();
     if (warp == 1) { umma::tc_fence_after(); umma::tmem_dealloc(tmem_base, tmem_cols); }
+}
+
+// CTA-pair variant (cluster of two, tcgen05 cta_group::2): one 256-row x bn tile per pair.  Each CTA stages its own 128
+// rows of A and its own half of the bn columns of B, so a stage carries half the operand bytes per flop of the one-CTA
+// kernel; the one-CTA kernel is bound by shared-memory bandwidth (TMA writes + operand reads of three MMAs per k-step),
+// this one by the tensor pipe.  The even CTA issues the MMAs for both and commits to the barriers of both; each CTA
+// drains its own 128 accumulator rows.  Dense (non-grouped) products only.  With an MN-major B the last n-tile is
+// narrowed to the columns that exist (in units of two slabs), so a width like 400 costs 448 columns, not 512.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(UM_THREADS, 1)
+umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
+    extern __shared__ uint8_t smem_raw[];
+    // the same offset in both CTAs: the dynamic shared-memory window starts at the same address in every CTA of a launch
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int bk = 128 / p.elem_bytes;
+    const int slab_cols = 128 / p.elem_bytes;
+    const int slab_bytes = bk * 128;
+    const int a_slabs = UM_BM / slab_cols;
+    const int half_n = p.bn / 2;                                          // B columns staged by each CTA (full-width tile)
+    const int b_bytes = p.b_mn ? (half_n / slab_cols) * slab_bytes : half_n * 128;
+    const int n_parts = p.passes == 1 ? 1 : 2;
+    const int stage_bytes = n_parts * (UM_A_BYTES + b_bytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
+    uint64_t* empty = full + p.stages;
+    uint64_t* acc_full = empty + p.stages;
+    uint64_t* acc_empty = acc_full + 2;             // only the leader's are waited on; both CTAs' epilogue warps arrive there
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* epi_smem = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = umma::cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int num_kb = (p.k_len + bk - 1) / bk;
+    const uint32_t acc_cols = p.bn <= 32 ? 32u : p.bn <= 64 ? 64u : p.bn <= 128 ? 128u : 256u;
+    const uint32_t tmem_cols = 2 * acc_cols;
+    const int tiles_n = (p.n_cols + p.bn - 1) / p.bn;
+    const int tiles_m = (p.m_rows + 2 * UM_BM - 1) / (2 * UM_BM);
+    const int n_tiles = tiles_n * tiles_m * p.batch;          // the host keeps this below 2^31
+    const int unit = 2 * slab_cols;                          // MN-major B: a tile is a whole number of slabs per CTA
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { umma::mbar_init(&acc_full[s], 1); umma::mbar_init(&acc_empty[s], 2 * UM_EPI_WARPS); }
+        umma::fence_barrier_init();
+    }
+    if (warp == 1) { umma::tmem_alloc_pair(tmem_slot, tmem_cols); umma::tmem_relinquish_pair(); }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::cluster_sync();          // the peer's barriers exist before anything is signalled across the pair
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer (both CTAs; all bytes are counted on the leader's `full` barrier) -------------------------
+        if (lane == 0) {
+            umma::prefetch_tensormap(&map_a_hi); umma::prefetch_tensormap(&map_a_lo);
+            umma::prefetch_tensormap(&map_b_hi); umma::prefetch_tensormap(&map_b_lo);
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            const bool lo = p.passes != 1;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int tq = tile / tiles_n;
+                const int n0 = (tile - tq * tiles_n) * p.bn;
+                const int b = tq / tiles_m;
+                const int m0 = (tq - b * tiles_m) * (2 * UM_BM) + static_cast<int>(rank) * UM_BM;      // this CTA's rows
+                const int bnt = p.b_mn ? min(p.bn, (p.n_cols - n0 + unit - 1) / unit * unit) : p.bn;
+                const int hn = bnt / 2;
+                const int nb0 = n0 + static_cast<int>(rank) * hn;                                      // this CTA's columns
+                const int b_slabs = hn / slab_cols;
+                const uint32_t tx_pair = 2u * n_parts * (UM_A_BYTES + (p.b_mn ? b_slabs * slab_bytes : hn * 128));
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                    uint8_t* st = smem + s * stage_bytes;
+                    uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
+                    const uint32_t lead_full = umma::map_to_cta(umma::smem_u32(&full[s]), 0);
+                    if (rank == 0) umma::mbar_expect_tx(&full[s], tx_pair);
+                    const int k0 = kb * bk;
+                    if (!p.a_mn) {
+                        umma::tma_load_3d_pair(a_hi, &map_a_hi, k0, m0, b, lead_full);
+                        if (lo) umma::tma_load_3d_pair(a_lo, &map_a_lo, k0, m0, b, lead_full);
+                    } else {
+                        for (int sl = 0; sl < a_slabs; ++sl) {
+                            umma::tma_load_3d_pair(a_hi + sl * slab_bytes, &map_a_hi, m0 + slab_cols * sl, k0, b, lead_full);
+                            if (lo) umma::tma_load_3d_pair(a_lo + sl * slab_bytes, &map_a_lo, m0 + slab_cols * sl, k0, b, lead_full);
+                        }
+                    }
+                    if (!p.b_mn) {
+                        umma::tma_load_3d_pair(b_hi, &map_b_hi, k0, nb0, b, lead_full);
+                        if (lo) umma::tma_load_3d_pair(b_lo, &map_b_lo, k0, nb0, b, lead_full);
+                    } else {
+                        for (int sl = 0; sl < b_slabs; ++sl) {
+                            umma::tma_load_3d_pair(b_hi + sl * slab_bytes, &map_b_hi, nb0 + slab_cols * sl, k0, b, lead_full);
+                            if (lo) umma::tma_load_3d_pair(b_lo + sl * slab_bytes, &map_b_lo, nb0 + slab_cols * sl, k0, b, lead_full);
+                        }
+                    }
+                    if (++s == p.stages) { s = 0; ph ^= 1; }
+                }
+            }
+            // tail: every commit aimed at this CTA's `empty` barriers has landed before the CTA may exit
+            for (int i = 0; i < p.stages && ok; ++i) {
+                if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; }
+                if (++s == p.stages) { s = 0; ph ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: the leader only --------------------------------------------------------------------------------
+        if (lane == 0 && rank == 0) {
+            const bool f16 = p.elem_bytes == 2;
+            const uint32_t mn_sbo = f16 ? 1024u : 512u, mn_layout = f16 ? 2u : 1u;
+            const uint64_t a_tmpl = p.a_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
+            const uint64_t b_tmpl = p.b_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
+            const uint32_t a_step = (p.a_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
+            const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
+            const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
+            const bool single = p.passes == 1;
+            int s = 0; uint32_t ph = 0;
+            int lt = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++lt) {
+                const int n0 = (tile % tiles_n) * p.bn;
+                const int bnt = p.b_mn ? min(p.bn, (p.n_cols - n0 + unit - 1) / unit * unit) : p.bn;
+                const uint32_t idesc = umma::instr_desc(f16 ? 1u : 2u, 2 * UM_BM, (uint32_t)bnt, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+                const int buf = lt & 1;
+                const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
+                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                umma::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * acc_cols;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
+                    umma::tc_fence_after();
+                    const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;
+                    uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
+                    if (single) {
+                        if (f16) {
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
+                                umma::mma_f16_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                        } else {
+#pragma unroll
+                            for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
+                                umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                        }
+                    } else {
+                        uint64_t dal = a_tmpl | (st + a_lo_off), dbl = b_tmpl | (st + b_lo_off);
+#pragma unroll
+                        for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
+                            umma::mma_tf32_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
+                            umma::mma_tf32_pair(tmem_d, dah, dbl, idesc, 1u);
+                            umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, 1u);
+                        }
+                    }
+                    const uint32_t e0 = umma::smem_u32(&empty[s]);
+                    umma::mma_commit_pair(e0);                              // frees the stage in this CTA ...
+                    umma::mma_commit_pair(umma::map_to_cta(e0, 1));         // ... and in the peer
+                    if (++s == p.stages) { s = 0; ph ^= 1; }
+                }
+                const uint32_t f0 = umma::smem_u32(&acc_full[buf]);
+                umma::mma_commit_pair(f0);
+                umma::mma_commit_pair(umma::map_to_cta(f0, 1));
+            }
+        }
+    } else {
+        // ---- epilogue (both CTAs, each its own 128 rows) -------------------------------------------------------------------
+        int lt = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++lt) {
+            const int tq = tile / tiles_n;
+            const int n0 = (tile - tq * tiles_n) * p.bn;
+            const int b = tq / tiles_m;
+            const int m0 = (tq - b * tiles_m) * (2 * UM_BM) + static_cast<int>(rank) * UM_BM;
+            const int bnt = p.b_mn ? min(p.bn, (p.n_cols - n0 + unit - 1) / unit * unit) : p.bn;
+            const int buf = lt & 1;
+            const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
+            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }
+            umma::tc_fence_after();
+            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
+                          umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem);
+        }
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::cluster_sync();          // neither CTA frees tensor memory or exits while the other may still signal it
+    if (warp == 1) { umma::tc_fence_after(); umma::tmem_dealloc_pair(tmem_base, tmem_cols); }
 }
 
 // Exact recomputation of the listed TransE scores from the table rows (one warp per entry).
@@ -617,21 +857,30 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     if (p.passes == 0) p.passes = 3;
     p.err = device_error_word();
     if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
-    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(umma_gemm_kernel)");
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(tile kernels)");
+        attr_set = true;
+    }
     const int slab_cols = 128 / p.elem_bytes;
-    const int b_bytes = p.b_mn ? ((p.bn + slab_cols - 1) / slab_cols) * (slab_cols * 128) : p.bn * 128;
+    const int b_cols = p.pair ? p.bn / 2 : p.bn;                     // B columns staged per CTA
+    const int b_bytes = p.b_mn ? ((b_cols + slab_cols - 1) / slab_cols) * (slab_cols * 128) : b_cols * 128;
     const int stage_bytes = (p.passes == 1 ? 1 : 2) * (UM_A_BYTES + b_bytes);
     p.stages = (UM_MAX_SMEM - 1024 - UM_TAIL_BYTES) / stage_bytes;
     if (p.stages > 6) p.stages = 6;
     const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024 + UM_TAIL_BYTES;
     p.batch = (int)batch;
-    const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + UM_BM - 1) / UM_BM) * batch;
+    const int tile_rows = p.pair ? 2 * UM_BM : UM_BM;
+    const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + tile_rows - 1) / tile_rows) * batch;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
         return cuda_status(cudaGetLastError(), "cudaDeviceGetAttribute(multiprocessor count)");
     const long long bound = p.tile_tab ? p.tile_cap : n_tiles;      // grouped mode: the tile count is only known on the device
-    const dim3 grid((unsigned)(bound < sms ? bound : sms));         // persistent: one CTA per SM walks the tile list
+    if (bound >= (1LL << 31)) { set_error("tile kernel: %lld tiles exceed the 32-bit tile index", bound); return KGE_E_SHAPE; }
+    const int slots = p.pair ? sms / 2 : sms;                       // persistent: one CTA (or CTA pair) per SM (pair of SMs)
+    const unsigned ctas = (unsigned)(bound < slots ? bound : slots) * (p.pair ? 2u : 1u);
     const bool prof = g_prof_on && g_prof_n < 64;
     if (prof) {
         if (!g_prof_events_made) {
@@ -641,8 +890,13 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
         }
         cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
     }
-    umma_gemm_kernel<<<grid, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
-    KGE_LAUNCH_CHECK("umma_gemm_kernel");
+    if (p.pair) {
+        umma_pair_kernel<<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        KGE_LAUNCH_CHECK("umma_pair_kernel");
+    } else {
+        umma_gemm_kernel<<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        KGE_LAUNCH_CHECK("umma_gemm_kernel");
+    }
     if (prof) {
         cudaEventRecord(g_prof_ev[2 * g_prof_n + 1], s);
         ++g_prof_n; ++g_prof_launches;
@@ -650,6 +904,9 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     }
     return 0;
 }
+
+// CTA pairs pay off once a product has more than one 128-row tile per batch; narrow outputs stay on the one-CTA kernel.
+static bool want_pair(int m_rows, int n_cols) { return m_rows > UM_BM && n_cols >= 64; }
 
 // Forward scores of the chunk's negatives.  ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 0).
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s) {
@@ -675,14 +932,16 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     // n_neg rows need 16-byte row pitch in the output only for vector stores; tensor maps need dim % 4 == 0 (checked)
     CUtensorMap mah, mal, mbh, mbl;
     const uint64_t ld = static_cast<uint64_t>(a.dim) * 4;
-    const int bn = a.n_neg >= 128 ? 128 : pick_bn(a.n_neg);
+    const bool pair = want_pair(a.chunk, a.n_neg);
+    const int bn = pair ? pick_bn(a.n_neg) : (a.n_neg >= 128 ? 128 : pick_bn(a.n_neg));
+    const int b_box = pair ? bn / 2 : bn;           // a CTA of a pair stages half of the tile's columns
     if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
     if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bn, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bn, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
-    p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0;
+    p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0; p.pair = pair;
     p.ep = dist ? EP_DIST : EP_STORE;
     p.out = a.negs; p.out_ld = a.n_neg; p.out_batch_rows = a.chunk;
     p.sq_a = sq; p.sq_b = sq + n_a; p.fix_count = fixc; p.fix_list = fixl; p.fix_cap = L.fix_cap;
@@ -735,7 +994,9 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
         }
     }
     const uint64_t ld = static_cast<uint64_t>(a.dim) * 4, lw = static_cast<uint64_t>(a.n_neg) * 4;
-    const int bn = pick_bn(a.dim);
+    // pairs with an MN-major B: tiles are whole slabs per CTA (multiples of 64 columns), the last one narrowed by the kernel
+    const bool pair_ga = want_pair(a.chunk, a.dim), pair_gx = want_pair(a.n_neg, a.dim);
+    const int bn64 = a.dim >= 256 ? 256 : (a.dim + 63) / 64 * 64;
     CUtensorMap mah, mal, mbh, mbl;
     // GA = W . X : A = W K-major (rows i, K = j), B = X MN-major (N = dim, K rows = j)
     if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
@@ -744,7 +1005,7 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
     if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
-    p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = bn; p.a_mn = 0; p.b_mn = 1;
+    p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = pair_ga ? bn64 : pick_bn(a.dim); p.a_mn = 0; p.b_mn = 1; p.pair = pair_ga;
     p.ep = dist ? EP_RANK1 : EP_STORE;
     p.out = ga; p.out_ld = a.dim; p.out_batch_rows = a.chunk;
     p.scale = rowsum; p.y_hi = hi; p.y_lo = lo;
@@ -755,7 +1016,7 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
     if ((rc = make_tensor_map_3d(&mbh, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
     if ((rc = make_tensor_map_3d(&mbl, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
     memset(&p, 0, sizeof(p));
-    p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = bn; p.a_mn = 1; p.b_mn = 1;
+    p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = pair_gx ? bn64 : pick_bn(a.dim); p.a_mn = 1; p.b_mn = 1; p.pair = pair_gx;
     p.ep = dist ? EP_RANK1 : EP_STORE;
     p.out = a.g_neg; p.out_ld = a.dim; p.out_batch_rows = a.n_neg;
     p.scale = colsum; p.y_hi = hi + n_a * a.dim; p.y_lo = lo + n_a * a.dim;

@@ -87,7 +87,8 @@ def test_score_forward_chunk_shared(model, d, chunk, nchunks, nn, head):
 
 @pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx", "RESCAL"])
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (64, 128, 2, 256, 0), (400, 256, 2, 384, 0),
-                                                     (200, 130, 2, 150, 1), (36, 7, 3, 9, 0), (512, 1024, 1, 1024, 0)])
+                                                     (200, 130, 2, 150, 1), (36, 7, 3, 9, 0), (512, 1024, 1, 1024, 0),
+                                                     (100, 384, 2, 200, 0), (64, 520, 1, 1000, 1)])
 def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
     """3xTF32 tcgen05 path of the chunk-shared dot-product scorers: same 1e-4 tolerance as the fp32 CUDA-core path."""
     from cuke_b200 import scoring
@@ -144,7 +145,8 @@ def test_transe_tensor_cores_cancellation(frac, overflow):
 
 @pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx", "RESCAL"])
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
-                                                     (36, 7, 4, 12, 0), (512, 512, 1, 1024, 0)])
+                                                     (36, 7, 4, 12, 0), (512, 512, 1, 1024, 0), (100, 384, 2, 200, 0),
+                                                     (72, 520, 1, 1000, 1)])
 def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
     from cuke_b200 import scoring
     if model == "RESCAL":
