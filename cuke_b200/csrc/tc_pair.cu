@@ -59,6 +59,23 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, int elem_bytes, uint6
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return KGE_E_DEVICE; }
     return 0;
 }
+int make_tensor_map_slabs(CUtensorMap* out, const void* base, int elem_bytes, uint64_t batch, uint64_t krows, uint64_t cols_padded,
+                          uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_krows, uint32_t box_slabs) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return KGE_E_DEVICE; }
+    const uint32_t slab_cols = 128 / elem_bytes;
+    if (cols_padded % slab_cols != 0) { set_error("slab tensor map: %llu columns are not whole slabs", (unsigned long long)cols_padded); return KGE_E_SHAPE; }
+    cuuint64_t gdim[4] = {slab_cols, krows, cols_padded / slab_cols, batch};
+    cuuint64_t gstride[3] = {row_stride_bytes, 128, batch_stride_bytes};
+    cuuint32_t box[4] = {slab_cols, box_krows, box_slabs, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                    const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    elem_bytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (slabs) failed with CUresult %d", (int)r); return KGE_E_DEVICE; }
+    return 0;
+}
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
     return make_tensor_map_3d(out, base, elem_bytes, 1, rows, cols, row_stride_bytes, rows * row_stride_bytes, box_rows, box_cols);
@@ -72,9 +89,10 @@ __device__ __forceinline__ void split4(float4 v, float4& hi, float4& lo) {
 }
 
 // Rows [0, n_a): anchors of the triples; rows [n_a, n_a + n_x): the negative rows, in id-list order.
-// One warp per row; hi / lo are (n_a + n_x, dim) fp32, sq (n_a + n_x) the squared norms of the unsplit rows.
+// One warp per row; hi / lo are (n_a + n_x) rows of fp32 with a pitch of ldp floats (dim rounded up to whole 128-byte
+// slabs, the padding written as zero), sq (n_a + n_x) the squared norms of the unsplit rows.
 template <int MODEL, typename T, typename I, int NV>
-__global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, long long n_a, long long n_x,
+__global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, long long n_a, long long n_x, int ldp,
                                                       float* hi, float* lo, float* sq) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -104,42 +122,93 @@ __global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, lon
     Row<NV> h, l;
 #pragma unroll
     for (int q = 0; q < NV; ++q) { s = dot4(v.v[q], v.v[q], s); split4(v.v[q], h.v[q], l.v[q]); }
-    store_row<NV, true>(hi + row * dim, h, dim, lane);
-    store_row<NV, true>(lo + row * dim, l, dim, lane);
+    store_row<NV, true>(hi + row * ldp, h, dim, lane);
+    store_row<NV, true>(lo + row * ldp, l, dim, lane);
+    if (dim + 4 * lane < ldp) {                       // at most 7 quads of padding
+        *reinterpret_cast<float4*>(hi + row * ldp + dim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(lo + row * ldp + dim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     s = warp_sum(s);
     if (lane == 0 && sq) sq[row] = s;
 }
 
-// W = dS (DIST == false) or dS / S (DIST: S = -distance; 0 where S == 0), split into hi / lo; row sums for DIST.
-// One warp per row of the (batch, n_neg) matrix.
-template <bool DIST>
-__global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, const float* sc, long long rows, int n_neg,
-                                                        float* hi, float* lo, float* rowsum) {
+// W = dS split into hi / lo (dot-product scorers).  One warp per row of the (batch, n_neg) matrix; hi / lo have a pitch
+// of ldw floats (n_neg rounded up to whole slabs, padding zero).
+__global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, long long rows, int n_neg, int ldw, float* hi, float* lo) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const float* d = ds + row * n_neg;
-    const float* s = sc ? sc + row * n_neg : nullptr;
-    float sum = 0.f;
-    for (int j = lane; j < n_neg; j += 32) {
-        float w = d[j];
-        if (DIST) { const float sv = s[j]; w = sv != 0.f ? w / sv : 0.f; sum += w; }
+    for (int j = lane; j < ldw; j += 32) {
+        const float w = j < n_neg ? d[j] : 0.f;
         const float h = tf32_trunc(w);
-        hi[row * n_neg + j] = h;
-        lo[row * n_neg + j] = tf32_trunc(w - h);
+        hi[row * ldw + j] = h;
+        lo[row * ldw + j] = tf32_trunc(w - h);
     }
-    if (DIST) { sum = warp_sum(sum); if (lane == 0) rowsum[row] = sum; }
 }
-// Column sums of W per chunk: colsum[c][j] = sum_i W[c*chunk + i][j], added in ascending i.
-__global__ void __launch_bounds__(256) tc_colsum_kernel(const float* hi, const float* lo, int chunk, int n_neg, long long batch,
-                                                        float* colsum) {
+// TransE: W = dS / S (0 where S == 0) split into hi / lo, with its row sums and per-block column sums in the same pass.
+// A block takes TW_ROWS consecutive rows of one chunk; thread t owns columns t, t + 256, ...: for a fixed row the block
+// reads consecutive columns (coalesced), a thread's column sum stays in a register across the rows, and the row sums are
+// reduced once per block.  colpart[(chunk * blocks_per_chunk + block)][j] holds the block's column sums; all sums are
+// added in a fixed order, so the result does not depend on scheduling.
+constexpr int TW_ROWS = 32;
+__global__ void __launch_bounds__(256) tc_pack_w_sums_kernel(const float* __restrict__ ds, const float* __restrict__ sc, int chunk, int n_neg,
+                                                             int ldw, float* __restrict__ hi, float* __restrict__ lo,
+                                                             float* __restrict__ rowsum, float* __restrict__ colpart) {
+    __shared__ float row_part[8][TW_ROWS];
+    const int c = blockIdx.y, r0 = blockIdx.x * TW_ROWS;
+    const int rows = min(TW_ROWS, chunk - r0);
+    const long long row0 = (long long)c * chunk + r0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float rs[TW_ROWS];
+#pragma unroll
+    for (int i = 0; i < TW_ROWS; ++i) rs[i] = 0.f;
+    float* cp = colpart + ((long long)c * gridDim.x + blockIdx.x) * n_neg;
+    for (int j = threadIdx.x; j < ldw; j += 256) {
+        float cs = 0.f;
+        const bool in = j < n_neg;
+        float dv[TW_ROWS], sv[TW_ROWS];
+#pragma unroll
+        for (int i = 0; i < TW_ROWS; ++i) {          // all loads of the column strip first
+            const bool ok = in && i < rows;
+            const long long o = (row0 + i) * n_neg + j;
+            dv[i] = ok ? __ldg(ds + o) : 0.f;
+            sv[i] = ok ? __ldg(sc + o) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < TW_ROWS; ++i) {
+            if (i < rows) {
+                const float w = sv[i] != 0.f ? dv[i] / sv[i] : 0.f;
+                const float h = tf32_trunc(w);
+                hi[(row0 + i) * ldw + j] = h;
+                lo[(row0 + i) * ldw + j] = tf32_trunc(w - h);
+                cs += w;
+                rs[i] += w;
+            }
+        }
+        if (in) cp[j] = cs;
+    }
+#pragma unroll
+    for (int i = 0; i < TW_ROWS; ++i) {
+        const float v = warp_sum(rs[i]);
+        if (lane == 0) row_part[warp][i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += row_part[w][threadIdx.x];
+        rowsum[row0 + threadIdx.x] = v;
+    }
+}
+// Column sums of W per chunk from the per-block sums: colsum[c][j] = sum_b colpart[c][b][j], ascending b.
+__global__ void __launch_bounds__(256) tc_colsum_kernel(const float* colpart, int blocks_per_chunk, int n_neg, float* colsum) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     const int c = blockIdx.y;
     if (j >= n_neg) return;
-    const long long i0 = (long long)c * chunk;
-    const int rows = (int)min((long long)chunk, batch - i0);
+    const float* cp = colpart + (long long)c * blocks_per_chunk * n_neg + j;
     float s = 0.f;
-    for (int i = 0; i < rows; ++i) { const long long o = (i0 + i) * n_neg + j; s += hi[o] + lo[o]; }
+    for (int b = 0; b < blocks_per_chunk; ++b) s += cp[(long long)b * n_neg];
     colsum[(long long)c * n_neg + j] = s;
 }
 
@@ -177,6 +246,8 @@ struct GemmTc {
     // EP_GV: gv_out[row] = bf16(coef[row] * (acc + rel_vec[z]));  EP_SCATTER: rows go to neg_out (signed by side) / pos_out
     const float* coef; __nv_bfloat16* gv_out; int sc_n_neg; int sc_n_neg_head;
     int pair;                         // 1: CTA pairs (256-row tiles, umma_pair_kernel)
+    int a_slabs4d, b_slabs4d;         // MN-major operand read through a 4-D slab map: one copy per stage instead of one per slab
+    long long y_ld;                   // EP_RANK1: row pitch of y_hi / y_lo
     int32_t* err;
 };
 
@@ -287,8 +358,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 }
             }
         } else if (p.ep == EP_RANK1) {
-            const float* yh = p.y_hi + grow0 * p.out_ld + col;
-            const float* yl = p.y_lo + grow0 * p.out_ld + col;
+            const float* yh = p.y_hi + grow0 * p.y_ld + col;
+            const float* yl = p.y_lo + grow0 * p.y_ld + col;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
             // the y rows come from memory: all loads of a 16-row batch are issued before the first store
 #pragma unroll 1
@@ -297,7 +368,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const bool ok = col_ok && r0 + i < rows_here;
-                    const long long off = static_cast<long long>(r0 + i) * p.out_ld;
+                    const long long off = static_cast<long long>(r0 + i) * p.y_ld;
                     y[i] = ok ? __ldg(yh + off) + __ldg(yl + off) : 0.f;
                 }
 #pragma unroll
@@ -423,6 +494,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     if (!p.a_mn) {
                         umma::tma_load_3d(a_hi, &map_a_hi, k0, m0, za, &full[s]);
                         if (lo) umma::tma_load_3d(a_lo, &map_a_lo, k0, m0, za, &full[s]);
+                    } else if (p.a_slabs4d) {
+                        umma::tma_load_4d(a_hi, &map_a_hi, 0, k0, m0 / slab_cols, za, &full[s]);
+                        if (lo) umma::tma_load_4d(a_lo, &map_a_lo, 0, k0, m0 / slab_cols, za, &full[s]);
                     } else {
                         for (int sl = 0; sl < a_slabs; ++sl) {
                             umma::tma_load_3d(a_hi + sl * slab_bytes, &map_a_hi, m0 + slab_cols * sl, k0, za, &full[s]);
@@ -432,6 +506,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     if (!p.b_mn) {
                         umma::tma_load_3d(b_hi, &map_b_hi, k0, n0, b, &full[s]);
                         if (lo) umma::tma_load_3d(b_lo, &map_b_lo, k0, n0, b, &full[s]);
+                    } else if (p.b_slabs4d) {
+                        umma::tma_load_4d(b_hi, &map_b_hi, 0, k0, n0 / slab_cols, b, &full[s]);
+                        if (lo) umma::tma_load_4d(b_lo, &map_b_lo, 0, k0, n0 / slab_cols, b, &full[s]);
                     } else {
                         for (int sl = 0; sl < b_slabs; ++sl) {
                             umma::tma_load_3d(b_hi + sl * slab_bytes, &map_b_hi, n0 + slab_cols * sl, k0, b, &full[s]);
@@ -589,7 +666,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 const int hn = bnt / 2;
                 const int nb0 = n0 + static_cast<int>(rank) * hn;                                      // this CTA's columns
                 const int b_slabs = hn / slab_cols;
-                const uint32_t tx_pair = 2u * n_parts * (UM_A_BYTES + (p.b_mn ? b_slabs * slab_bytes : hn * 128));
+                const uint32_t tx_pair = 2u * n_parts * (UM_A_BYTES + (p.b_slabs4d ? b_bytes : p.b_mn ? b_slabs * slab_bytes : hn * 128));
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
@@ -600,6 +677,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     if (!p.a_mn) {
                         umma::tma_load_3d_pair(a_hi, &map_a_hi, k0, m0, b, lead_full);
                         if (lo) umma::tma_load_3d_pair(a_lo, &map_a_lo, k0, m0, b, lead_full);
+                    } else if (p.a_slabs4d) {
+                        umma::tma_load_4d_pair(a_hi, &map_a_hi, 0, k0, m0 / slab_cols, b, lead_full);
+                        if (lo) umma::tma_load_4d_pair(a_lo, &map_a_lo, 0, k0, m0 / slab_cols, b, lead_full);
                     } else {
                         for (int sl = 0; sl < a_slabs; ++sl) {
                             umma::tma_load_3d_pair(a_hi + sl * slab_bytes, &map_a_hi, m0 + slab_cols * sl, k0, b, lead_full);
@@ -609,6 +689,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     if (!p.b_mn) {
                         umma::tma_load_3d_pair(b_hi, &map_b_hi, k0, nb0, b, lead_full);
                         if (lo) umma::tma_load_3d_pair(b_lo, &map_b_lo, k0, nb0, b, lead_full);
+                    } else if (p.b_slabs4d) {         // the box is the full half-tile: slabs past the narrowed tile read as zero
+                        umma::tma_load_4d_pair(b_hi, &map_b_hi, 0, k0, nb0 / slab_cols, b, lead_full);
+                        if (lo) umma::tma_load_4d_pair(b_lo, &map_b_lo, 0, k0, nb0 / slab_cols, b, lead_full);
                     } else {
                         for (int sl = 0; sl < b_slabs; ++sl) {
                             umma::tma_load_3d_pair(b_hi + sl * slab_bytes, &map_b_hi, nb0 + slab_cols * sl, k0, b, lead_full);
@@ -742,16 +825,19 @@ static inline size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 struct TcLayout {        // carving of the tensor-core workspace
     size_t mat;          // bytes of one (n_a + n_x, dim) matrix
     size_t w;            // bytes of one (batch, n_neg) matrix (backward only)
-    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, total;
+    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, off_colpart, total;
     unsigned long long fix_cap;
+    int ldp, ldw;        // row pitches in floats: dim and n_neg rounded up to whole 128-byte slabs
 };
 static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool backward) {
     TcLayout L;
     const long long n_chunks = batch / chunk;
     const size_t rows = static_cast<size_t>(batch + n_chunks * n_neg);
     const size_t pairs = static_cast<size_t>(batch) * n_neg;
-    L.mat = al256(rows * dim * 4);
-    L.w = backward ? al256(pairs * 4) : 0;
+    L.ldp = (dim + 31) / 32 * 32;
+    L.ldw = (n_neg + 31) / 32 * 32;
+    L.mat = al256(rows * L.ldp * 4);
+    L.w = backward ? al256(static_cast<size_t>(batch) * L.ldw * 4) : 0;
     L.fix_cap = backward ? 0 : (pairs / 64 > 4096 ? pairs / 64 : 4096);
     size_t o = 0;
     L.off_hi = o; o += L.mat;
@@ -763,6 +849,7 @@ static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool b
     L.off_wlo = o; o += L.w;
     L.off_rowsum = o; o += backward ? al256(static_cast<size_t>(batch) * 4) : 0;
     L.off_colsum = o; o += backward ? al256(static_cast<size_t>(n_chunks) * n_neg * 4) : 0;
+    L.off_colpart = o; o += backward ? al256(static_cast<size_t>(n_chunks) * ((chunk + TW_ROWS - 1) / TW_ROWS) * n_neg * 4) : 0;
     L.total = o;
     return L;
 }
@@ -771,34 +858,34 @@ size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, i
 }
 
 template <int MODEL, typename T, typename I>
-static int tc_pack_go(const ScoreArgs& a, int head, long long n_a, long long n_x, float* hi, float* lo, float* sq, cudaStream_t s) {
+static int tc_pack_go(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
     const int nv = quads_per_lane(a.dim);
     const int wpb = 8;
     const unsigned blocks = (unsigned)((n_a + n_x + wpb - 1) / wpb);
     switch (nv) {
-        case 1: tc_pack_kernel<MODEL, T, I, 1><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, hi, lo, sq); break;
-        case 2: tc_pack_kernel<MODEL, T, I, 2><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, hi, lo, sq); break;
-        case 4: tc_pack_kernel<MODEL, T, I, 4><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, hi, lo, sq); break;
-        case 8: tc_pack_kernel<MODEL, T, I, 8><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, hi, lo, sq); break;
+        case 1: tc_pack_kernel<MODEL, T, I, 1><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
+        case 2: tc_pack_kernel<MODEL, T, I, 2><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
+        case 4: tc_pack_kernel<MODEL, T, I, 4><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
+        case 8: tc_pack_kernel<MODEL, T, I, 8><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
         default: set_error("dim %d > 1024 is not supported", a.dim); return KGE_E_UNSUPPORTED;
     }
     KGE_LAUNCH_CHECK("tc_pack_kernel");
     return 0;
 }
 template <int MODEL>
-static int tc_pack_types(const ScoreArgs& a, int head, long long n_a, long long n_x, float* hi, float* lo, float* sq, cudaStream_t s) {
+static int tc_pack_types(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
     if (a.dtype == KGE_F32)
-        return a.id_bits == 64 ? tc_pack_go<MODEL, float, int64_t>(a, head, n_a, n_x, hi, lo, sq, s)
-                               : tc_pack_go<MODEL, float, int32_t>(a, head, n_a, n_x, hi, lo, sq, s);
-    return a.id_bits == 64 ? tc_pack_go<MODEL, __nv_bfloat16, int64_t>(a, head, n_a, n_x, hi, lo, sq, s)
-                           : tc_pack_go<MODEL, __nv_bfloat16, int32_t>(a, head, n_a, n_x, hi, lo, sq, s);
+        return a.id_bits == 64 ? tc_pack_go<MODEL, float, int64_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s)
+                               : tc_pack_go<MODEL, float, int32_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+    return a.id_bits == 64 ? tc_pack_go<MODEL, __nv_bfloat16, int64_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s)
+                           : tc_pack_go<MODEL, __nv_bfloat16, int32_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
 }
-static int tc_pack(const ScoreArgs& a, int head, long long n_a, long long n_x, float* hi, float* lo, float* sq, cudaStream_t s) {
+static int tc_pack(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
     switch (a.model) {
-        case KGE_TRANSE: return tc_pack_types<KGE_TRANSE>(a, head, n_a, n_x, hi, lo, sq, s);
-        case KGE_DISTMULT: return tc_pack_types<KGE_DISTMULT>(a, head, n_a, n_x, hi, lo, sq, s);
-        case KGE_COMPLEX: return tc_pack_types<KGE_COMPLEX>(a, head, n_a, n_x, hi, lo, sq, s);
-        case KGE_RESCAL: return tc_pack_types<KGE_RESCAL>(a, head, n_a, n_x, hi, lo, sq, s);
+        case KGE_TRANSE: return tc_pack_types<KGE_TRANSE>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+        case KGE_DISTMULT: return tc_pack_types<KGE_DISTMULT>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+        case KGE_COMPLEX: return tc_pack_types<KGE_COMPLEX>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+        case KGE_RESCAL: return tc_pack_types<KGE_RESCAL>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
         default: break;
     }
     set_error("model %d is not supported with chunk-shared negatives", a.model);
@@ -922,7 +1009,7 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     float* sq = reinterpret_cast<float*>(w + L.off_sq);
     unsigned long long* fixc = reinterpret_cast<unsigned long long*>(w + L.off_fixc);
     unsigned long long* fixl = reinterpret_cast<unsigned long long*>(w + L.off_fixl);
-    int rc = tc_pack(a, head, n_a, n_x, hi, lo, sq, s);
+    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, sq, s);
     if (rc) return rc;
     const bool dist = a.model == KGE_TRANSE;
     if (dist) {
@@ -931,14 +1018,14 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     }
     // n_neg rows need 16-byte row pitch in the output only for vector stores; tensor maps need dim % 4 == 0 (checked)
     CUtensorMap mah, mal, mbh, mbl;
-    const uint64_t ld = static_cast<uint64_t>(a.dim) * 4;
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4;
     const bool pair = want_pair(a.chunk, a.n_neg);
     const int bn = pair ? pick_bn(a.n_neg) : (a.n_neg >= 128 ? 128 : pick_bn(a.n_neg));
     const int b_box = pair ? bn / 2 : bn;           // a CTA of a pair stages half of the tile's columns
     if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
     if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
     p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0; p.pair = pair;
@@ -978,48 +1065,66 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
     float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
     float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
     float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
+    float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
     const bool dist = a.model == KGE_TRANSE;
-    int rc = tc_pack(a, head, n_a, n_x, hi, lo, nullptr, s);
+    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, nullptr, s);
     if (rc) return rc;
-    {
+    if (dist) {
+        const int bpc = (a.chunk + TW_ROWS - 1) / TW_ROWS;
+        tc_pack_w_sums_kernel<<<dim3(bpc, (unsigned)n_chunks), 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
+        KGE_LAUNCH_CHECK("tc_pack_w_sums_kernel");
+        tc_colsum_kernel<<<dim3((a.n_neg + 255) / 256, (unsigned)n_chunks), 256, 0, s>>>(colpart, bpc, a.n_neg, colsum);
+        KGE_LAUNCH_CHECK("tc_colsum_kernel");
+    } else {
         const int wpb = 8;
         const unsigned blocks = (unsigned)((a.batch + wpb - 1) / wpb);
-        if (dist) tc_pack_w_kernel<true><<<blocks, wpb * 32, 0, s>>>(a.dneg, a.negs, a.batch, a.n_neg, whi, wlo, rowsum);
-        else tc_pack_w_kernel<false><<<blocks, wpb * 32, 0, s>>>(a.dneg, nullptr, a.batch, a.n_neg, whi, wlo, rowsum);
+        tc_pack_w_kernel<<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
         KGE_LAUNCH_CHECK("tc_pack_w_kernel");
-        if (dist) {
-            const dim3 g((a.n_neg + 255) / 256, (unsigned)n_chunks);
-            tc_colsum_kernel<<<g, 256, 0, s>>>(whi, wlo, a.chunk, a.n_neg, a.batch, colsum);
-            KGE_LAUNCH_CHECK("tc_colsum_kernel");
-        }
     }
-    const uint64_t ld = static_cast<uint64_t>(a.dim) * 4, lw = static_cast<uint64_t>(a.n_neg) * 4;
-    // pairs with an MN-major B: tiles are whole slabs per CTA (multiples of 64 columns), the last one narrowed by the kernel
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4, lw = static_cast<uint64_t>(L.ldw) * 4;
+    // Pairs with an MN-major B: tiles are whole slabs per CTA (multiples of 64 columns), the last one narrowed by the kernel.
+    // The packed matrices have whole-slab pitches, so MN-major operands are read through 4-D slab maps (one copy per stage);
+    // the one-CTA kernel keeps per-slab copies for B because its tile width need not be a whole number of slabs.
     const bool pair_ga = want_pair(a.chunk, a.dim), pair_gx = want_pair(a.n_neg, a.dim);
     const int bn64 = a.dim >= 256 ? 256 : (a.dim + 63) / 64 * 64;
+    const float* xhi = hi + n_a * L.ldp;
+    const float* xlo = lo + n_a * L.ldp;
     CUtensorMap mah, mal, mbh, mbl;
-    // GA = W . X : A = W K-major (rows i, K = j), B = X MN-major (N = dim, K rows = j)
-    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * a.dim, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
     GemmTc p;
+    // GA = W . X : A = W K-major (rows i, K = j), B = X MN-major (N = dim, K rows = j)
     memset(&p, 0, sizeof(p));
     p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = pair_ga ? bn64 : pick_bn(a.dim); p.a_mn = 0; p.b_mn = 1; p.pair = pair_ga;
+    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
+    if (pair_ga) {
+        p.b_slabs4d = 1;
+        if ((rc = make_tensor_map_slabs(&mbh, xhi, 4, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, UM_BK, bn64 / 64))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbl, xlo, 4, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, UM_BK, bn64 / 64))) return rc;
+    } else {
+        if ((rc = make_tensor_map_3d(&mbh, xhi, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
+        if ((rc = make_tensor_map_3d(&mbl, xlo, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
+    }
     p.ep = dist ? EP_RANK1 : EP_STORE;
     p.out = ga; p.out_ld = a.dim; p.out_batch_rows = a.chunk;
-    p.scale = rowsum; p.y_hi = hi; p.y_lo = lo;
+    p.scale = rowsum; p.y_hi = hi; p.y_lo = lo; p.y_ld = L.ldp;
     if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
     // GX = W^T . A : A-operand = W MN-major (M = j, K rows = i), B = anchors MN-major (N = dim, K rows = i)
-    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BK, 32, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BK, 32, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
     memset(&p, 0, sizeof(p));
     p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = pair_gx ? bn64 : pick_bn(a.dim); p.a_mn = 1; p.b_mn = 1; p.pair = pair_gx;
+    p.a_slabs4d = 1;
+    if ((rc = make_tensor_map_slabs(&mah, whi, 4, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, UM_BK, UM_BM / 32))) return rc;
+    if ((rc = make_tensor_map_slabs(&mal, wlo, 4, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, UM_BK, UM_BM / 32))) return rc;
+    if (pair_gx) {
+        p.b_slabs4d = 1;
+        if ((rc = make_tensor_map_slabs(&mbh, hi, 4, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, UM_BK, bn64 / 64))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbl, lo, 4, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, UM_BK, bn64 / 64))) return rc;
+    } else {
+        if ((rc = make_tensor_map_3d(&mbh, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
+        if ((rc = make_tensor_map_3d(&mbl, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
+    }
     p.ep = dist ? EP_RANK1 : EP_STORE;
     p.out = a.g_neg; p.out_ld = a.dim; p.out_batch_rows = a.n_neg;
-    p.scale = colsum; p.y_hi = hi + n_a * a.dim; p.y_lo = lo + n_a * a.dim;
+    p.scale = colsum; p.y_hi = xhi; p.y_lo = xlo; p.y_ld = L.ldp;
     return run_gemm(mah, mal, mbh, mbl, p, n_chunks, s);
 }
 

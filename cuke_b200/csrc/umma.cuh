@@ -56,6 +56,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
+// 4-D form for MN-major operands: coordinates (column within slab, k-row, slab, batch); one copy brings a whole
+// [slab][k-row][128 bytes] block, the layout the tensor core reads MN-major operands from.
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -137,6 +145,12 @@ __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(leader_bar)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(leader_bar)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {      // the same warp of both CTAs
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
 }
@@ -216,5 +230,10 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
 int make_tensor_map_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t batch, uint64_t rows, uint64_t cols,
                        uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_rows, uint32_t box_cols,
                        bool atom32 = false);
+
+// MN-major operand whose row pitch is a whole number of 128-byte slabs: 4-D view (column in slab, k-row, slab, batch)
+// with a (slab_cols, box_krows, box_slabs, 1) box, so one copy fills box_slabs consecutive slabs of a stage.
+int make_tensor_map_slabs(CUtensorMap* out, const void* base, int elem_bytes, uint64_t batch, uint64_t krows, uint64_t cols_padded,
+                          uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_krows, uint32_t box_slabs);
 
 }  // namespace kge
