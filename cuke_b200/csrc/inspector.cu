@@ -172,13 +172,21 @@ __global__ void __launch_bounds__(RS_THREADS) unique_apply_kernel(const unsigned
 // Window = 32 consecutive sorted positions, one warp per window.  A segment that lies inside one window is
 // finished there; a segment that crosses window boundaries leaves one partial row per window ("trail" in
 // its first window, "lead" in every later one), summed in window order by segred_span_kernel.
-__device__ __forceinline__ int seg_of_position(const int* seg, int U, int p) {   // largest u with seg[u] <= p
+// Largest u in [0, U) with seg[u] <= p, found by the whole warp: every round the 32 lanes probe 32 evenly spaced
+// entries at once, so the search is log32(U) dependent loads deep instead of log2(U).  seg[0] == 0 <= p always holds.
+__device__ __forceinline__ int seg_of_position(const int* seg, int U, int p, int lane) {
     int lo = 0, hi = U - 1;
-    while (lo < hi) {
-        int mid = (lo + hi + 1) >> 1;
-        if (seg[mid] <= p) lo = mid; else hi = mid - 1;
+    while (hi - lo >= 32) {
+        const int step = (hi - lo + 32) >> 5;                  // ceil((hi - lo + 1) / 32)
+        const int idx = lo + lane * step;
+        const bool ok = idx <= hi && seg[idx] <= p;            // true for lanes 0 .. k, false above
+        const int k = __popc(__ballot_sync(kFull, ok)) - 1;
+        lo += k * step;
+        hi = min(hi, lo + step - 1);
     }
-    return lo;
+    const int idx = lo + lane;
+    const bool ok = idx <= hi && seg[idx] <= p;
+    return lo + __popc(__ballot_sync(kFull, ok)) - 1;
 }
 
 template <int NV, bool VEC>
@@ -191,31 +199,38 @@ __global__ void __launch_bounds__(256) segred_window_kernel(const float* rows, i
     if (p0 >= n) return;
     const int p1 = (int)min(n, p0 + 32);
     const int U = (int)*n_unique;
-    int cur = seg_of_position(seg, U, (int)p0);
+    int cur = seg_of_position(seg, U, (int)p0, lane);
     int cur_end = seg[cur + 1];
     const int my = (p0 + lane < n) ? perm[p0 + lane] : 0;
     Row<NV> acc;
     row_zero<NV>(acc);
-    int piece_start = (int)p0;
-    for (int p = (int)p0; p < p1; ++p) {
-        const int src = __shfl_sync(kFull, my, p - (int)p0);
-        Row<NV> x;
-        load_row_f32<NV, VEC>(x, rows + (long long)src * dim, dim, lane);
+    // four rows are requested before the first of them is added: the adds (and the stores at segment ends) stay in
+    // position order, the memory latency of the gathered rows overlaps
+    for (int pb = (int)p0; pb < p1; pb += 4) {
+        Row<NV> x[4];
 #pragma unroll
-        for (int q = 0; q < NV; ++q) acc.v[q] = acc.v[q] + x.v[q];
-        if (p + 1 == cur_end || p + 1 == p1) {
-            const int s = seg[cur];
-            float* dst;
-            if (s >= (int)p0 && cur_end <= p1) dst = out + (long long)cur * dim;       // whole segment in this window
-            else if (s < (int)p0) dst = lead + wi * dim;                              // continues from the left
-            else dst = trail + wi * dim;                                              // continues to the right
-            store_row<NV, VEC>(dst, acc, dim, lane);
-            row_zero<NV>(acc);
-            piece_start = p + 1;
-            if (p + 1 == cur_end && p + 1 < p1) { ++cur; cur_end = seg[cur + 1]; }
+        for (int u = 0; u < 4; ++u) {
+            const int src = __shfl_sync(kFull, my, min(pb + u, p1 - 1) - (int)p0);
+            if (pb + u < p1) load_row_f32<NV, VEC>(x[u], rows + (long long)src * dim, dim, lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int p = pb + u;
+            if (p >= p1) break;
+#pragma unroll
+            for (int q = 0; q < NV; ++q) acc.v[q] = acc.v[q] + x[u].v[q];
+            if (p + 1 == cur_end || p + 1 == p1) {
+                const int s = seg[cur];
+                float* dst;
+                if (s >= (int)p0 && cur_end <= p1) dst = out + (long long)cur * dim;       // whole segment in this window
+                else if (s < (int)p0) dst = lead + wi * dim;                              // continues from the left
+                else dst = trail + wi * dim;                                              // continues to the right
+                store_row<NV, VEC>(dst, acc, dim, lane);
+                row_zero<NV>(acc);
+                if (p + 1 == cur_end && p + 1 < p1) { ++cur; cur_end = seg[cur + 1]; }
+            }
         }
     }
-    (void)piece_start;
 }
 
 // One CTA per window boundary b (between windows b and b+1): if a segment crosses it and starts in window b, the
@@ -231,7 +246,7 @@ __global__ void __launch_bounds__(256) segred_span_kernel(int dim, long long n, 
     const long long edge = (b + 1) * 32;            // first position of window b+1
     if (edge >= n) return;
     const int U = (int)*n_unique;
-    const int u = seg_of_position(seg, U, (int)edge - 1);
+    const int u = seg_of_position(seg, U, (int)edge - 1, lane);
     const int s = seg[u], e = seg[u + 1];
     if (e <= edge || s < b * 32) return;            // does not cross here, or started in an earlier window (block-uniform)
     const long long parts = (e - 1) / 32 - b + 1;   // part 0 = trail[b], part k = lead[b + k]
