@@ -68,7 +68,7 @@ size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, i
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
 void gemm_profile_enable(int on);
 int gemm_profile_read(double* ms, long long* launches, double* flops);
-int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -363,8 +363,9 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     }
     if (p->neg_mode == KGE_NEG_CHUNK_SHARED) {
         const bool head = p->n_neg_head > 0;
+        const float* ga_scale = nullptr;
         if (tc_backward(p)) {
-            rc = launch_pair_backward_tc(a, head ? 1 : 0, ws1, static_cast<char*>(workspace) + 3 * rb, tc_bytes(p, 1), s);
+            rc = launch_pair_backward_tc(a, head ? 1 : 0, ws1, &ga_scale, static_cast<char*>(workspace) + 3 * rb, tc_bytes(p, 1), s);
         } else {
             if (p->model != KGE_RESCAL) {
                 rc = launch_anchor(a, head ? nullptr : ws0, head ? ws0 : nullptr, s);
@@ -376,6 +377,7 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
         ScoreArgs b = a;
         b.n_neg = 0; b.n_neg_head = 0;
         if (head) b.ga_head_init = ws1; else b.ga_tail_init = ws1;
+        b.ga_init_scale = ga_scale;
         rc = launch_triple_backward(b, s);
     } else {
         rc = launch_triple_backward(a, s);

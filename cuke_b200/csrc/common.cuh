@@ -118,6 +118,7 @@ struct ScoreArgs {
     float* g_head; float* g_tail; float* g_neg; float* g_rel; float* g_rel2;
     const float* ga_tail_init;               // (batch, dim) anchor gradients accumulated elsewhere (chunk-shared)
     const float* ga_head_init;
+    const float* ga_init_scale;              // optional (batch): the initial anchor gradient is scale[i] * anchor_i - init_i
     const float* anchors;                    // (batch, dim) precomputed anchors (RESCAL), or NULL
     const unsigned long long* guard;         // if set, pair_fwd_kernel only runs when *guard > guard_cap (tensor-core overflow path)
     unsigned long long guard_cap;

@@ -325,6 +325,11 @@ __global__ void __launch_bounds__(128) triple_bwd_kernel(ScoreArgs a) {
         }
         if (FORM == FORM_DIST_H) { cw = row_dot<NV>(c, w); ww = row_dot<NV>(w, w); }
         if (init) load_row_f32<NV, VEC>(gc, init + i * dim, dim, lane); else row_zero<NV>(gc);
+        if (init && a.ga_init_scale) {         // distance scorers on the tensor cores: init holds sum_j W_ij x_j only
+            const float sc = a.ga_init_scale[i];
+#pragma unroll
+            for (int q = 0; q < NV; ++q) gc.v[q] = sc * c.v[q] - gc.v[q];
+        }
 
         for (int j = p_lo; j < p_hi; ++j) {
             Row<NV> x, gx;

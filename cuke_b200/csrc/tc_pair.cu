@@ -326,16 +326,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     }
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
-        float v[32];
-        umma::tmem_ld32(t_row + c * 32, v);         // warp-collective
         const int nbase = n0 + c * 32;
         const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
+        const bool col_ok = lane < lim;
+        const int col = nbase + lane;
+        float y[32];
+        if (p.ep == EP_RANK1) {          // the y rows come from memory: requested before the accumulator is read
+            const float* yh = p.y_hi + grow0 * p.y_ld + col;
+            const float* yl = p.y_lo + grow0 * p.y_ld + col;
+#pragma unroll
+            for (int r = 0; r < 32; ++r) {
+                const long long off = static_cast<long long>(r) * p.y_ld;
+                y[r] = (col_ok && r < rows_here) ? __ldg(yh + off) + __ldg(yl + off) : 0.f;
+            }
+        }
+        float v[32];
+        umma::tmem_ld32(t_row + c * 32, v);         // warp-collective
         if (rows_here <= 0 || lim <= 0) continue;    // warp-uniform
 #pragma unroll
         for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
         __syncwarp();
-        const bool col_ok = lane < lim;
-        const int col = nbase + lane;
         if (p.ep == EP_DIST) {
             const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
@@ -358,26 +368,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 }
             }
         } else if (p.ep == EP_RANK1) {
-            const float* yh = p.y_hi + grow0 * p.y_ld + col;
-            const float* yl = p.y_lo + grow0 * p.y_ld + col;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
-            // the y rows come from memory: all loads of a 16-row batch are issued before the first store
-#pragma unroll 1
-            for (int r0 = 0; r0 < rows_here; r0 += 16) {
-                float y[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const bool ok = col_ok && r0 + i < rows_here;
-                    const long long off = static_cast<long long>(r0 + i) * p.y_ld;
-                    y[i] = ok ? __ldg(yh + off) + __ldg(yl + off) : 0.f;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int r = r0 + i;
-                    const float x = stg[r * 32 + (lane ^ r)];
-                    const float rs = __shfl_sync(0xffffffffu, row_op, r);
-                    if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[i], -x);
-                }
+            for (int r = 0; r < 32; ++r) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                const float rs = __shfl_sync(0xffffffffu, row_op, r);
+                if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[r], -x);
             }
         } else if (p.ep == EP_GV) {          // dL/dv rows for the backward products, stored as bf16
             float rv = 0.f;
@@ -1046,9 +1042,12 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     return rc;
 }
 
-// Backward contractions.  anchors_out: (batch, dim) fp32 anchor-gradient rows GA; g_neg rows are written to a.g_neg.
+// Backward contractions.  ga: (batch, dim) fp32 anchor-gradient rows; g_neg rows are written to a.g_neg.  For the distance
+// scorer ga holds only sum_j W_ij x_j and *ga_scale the row sums of W: the anchor gradient is ga_scale[i] * anchor_i - ga_i,
+// applied by the per-triple backward kernel, which has the anchor row in registers anyway (else *ga_scale is NULL).
 // ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 1).
-int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, size_t ws_bytes, cudaStream_t s) {
+int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s) {
+    *ga_scale = nullptr;
     if (a.batch <= 0 || a.n_neg <= 0) return 0;
     if (a.dim % 4 != 0 || a.n_neg % 4 != 0) {
         set_error("the tensor-core backward needs dim %% 4 == 0 and n_neg %% 4 == 0, got %d and %d", a.dim, a.n_neg);
@@ -1104,9 +1103,9 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, void* ws, s
         if ((rc = make_tensor_map_3d(&mbh, xhi, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
         if ((rc = make_tensor_map_3d(&mbl, xlo, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
     }
-    p.ep = dist ? EP_RANK1 : EP_STORE;
+    p.ep = EP_STORE;
     p.out = ga; p.out_ld = a.dim; p.out_batch_rows = a.chunk;
-    p.scale = rowsum; p.y_hi = hi; p.y_lo = lo; p.y_ld = L.ldp;
+    if (dist) *ga_scale = rowsum;
     if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
     // GX = W^T . A : A-operand = W MN-major (M = j, K rows = i), B = anchors MN-major (N = dim, K rows = i)
     memset(&p, 0, sizeof(p));
