@@ -71,6 +71,8 @@ SIGNATURES = {
     "kge_score_workspace_bytes": (_sz, [_PP, _i32]),
     "kge_score_forward": (C.c_int, [_PP, _PT, _vp, _vp, _vp, _sz, _vp]),
     "kge_score_backward": (C.c_int, [_PP, _PT, _vp, _vp, _vp, _vp, _PG, _vp, _sz, _vp]),
+    "kge_score_loss_backward_workspace_bytes": (_sz, [_PP]),
+    "kge_score_loss_backward": (C.c_int, [_PP, _PT, _f32, _vp, _vp, _PG, _vp, _sz, _vp]),
     "kge_logistic_loss": (C.c_int, [_vp, _i64, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _sz, _vp]),
     "kge_owner_counts": (C.c_int, [_vp, _vp, _i64, _i64, _i32, _vp, _vp]),
 }

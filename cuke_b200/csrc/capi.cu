@@ -69,6 +69,8 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
 void gemm_profile_enable(int on);
 int gemm_profile_read(double* ms, long long* launches, double* flops);
 int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
+                                 void* ws, size_t ws_bytes, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -162,6 +164,8 @@ static size_t tc_bytes(const kge_problem* p, int backward) {
     if (backward ? !tc_backward(p) : !tc_forward(p)) return 0;
     return tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, backward);
 }
+// Fused forward + loss + backward: the chunk-shared tensor-core scorers whose anchors are built from table rows alone.
+static bool tc_fused(const kge_problem* p) { return tc_backward(p) && p->model != KGE_RESCAL; }
 
 }  // namespace kge
 
@@ -385,6 +389,60 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     if (rc) return rc;
     if (p->model == KGE_RESCAL) rc = launch_rescal_backward(p, t, ws2, g->g_head, g->g_rel2, s);
     return rc;
+}
+
+size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p) {
+    if (!p || p->batch <= 0 || !tc_fused(p)) return 256;
+    const size_t dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
+    return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2) + 256;
+}
+
+int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float neg_weight, float* pos_score, float* loss_out,
+                            const kge_grads* g, void* workspace, size_t workspace_bytes, kge_stream_t stream) {
+    const char* fn = "kge_score_loss_backward";
+    int rc = check_problem(fn, p, t, true);
+    if (rc) return rc;
+    if (!tc_fused(p)) {
+        set_error("%s: needs precision KGE_PREC_TENSOR, chunk-shared negatives with n_neg %% 4 == 0, dim %% 4 == 0 and "
+                  "TransE, DistMult or ComplEx; use kge_score_forward / kge_logistic_loss / kge_score_backward otherwise", fn);
+        return KGE_E_UNSUPPORTED;
+    }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    KGE_REQUIRE_PTR(loss_out, "loss_out");
+    if (p->batch == 0) return cuda_status(cudaMemsetAsync(loss_out, 0, 4, s), "kge_score_loss_backward(batch=0)");
+    if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }
+    KGE_REQUIRE_PTR(pos_score, "pos_score");
+    KGE_REQUIRE_PTR(g->g_head, "g_head"); KGE_REQUIRE_PTR(g->g_tail, "g_tail"); KGE_REQUIRE_PTR(g->g_rel, "g_rel");
+    KGE_REQUIRE_PTR(g->g_neg, "g_neg");
+    const size_t need = kge_score_loss_backward_workspace_bytes(p);
+    KGE_REQUIRE_PTR(workspace, "workspace");
+    if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    const size_t rb = rows_bytes(p), dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
+    char* wsb = static_cast<char*>(workspace);
+    float* ga = reinterpret_cast<float*>(wsb);                       // anchor gradients summed over the chunk's negatives
+    float* dpos = reinterpret_cast<float*>(wsb + rb);
+    void* loss_ws = wsb + rb + dpos_bytes;
+    char* tcw = wsb + rb + dpos_bytes + 4096;
+
+    ScoreArgs a = score_args(p, t);
+    a.pos = pos_score;
+    ScoreArgs apos = a;
+    apos.n_neg = 0; apos.n_neg_head = 0;
+    rc = launch_triple_forward(apos, s);                             // positive scores
+    if (rc) return rc;
+    rc = launch_logistic_loss(pos_score, p->batch, nullptr, 0, neg_weight, dpos, nullptr, loss_out, loss_ws, 4096, s);
+    if (rc) return rc;
+    a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel; a.g_rel2 = g->g_rel2;
+    const bool head = p->n_neg_head > 0;
+    const float* ga_scale = nullptr;
+    rc = launch_pair_loss_backward_tc(a, head ? 1 : 0, neg_weight, loss_out, ga, &ga_scale, tcw,
+                                      tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2), s);
+    if (rc) return rc;
+    ScoreArgs b = a;
+    b.dpos = dpos; b.n_neg = 0; b.n_neg_head = 0;
+    if (head) b.ga_head_init = ga; else b.ga_tail_init = ga;
+    b.ga_init_scale = ga_scale;
+    return launch_triple_backward(b, s);
 }
 
 int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg, int64_t n_neg_total, float neg_weight,

@@ -85,7 +85,8 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
 __device__ __forceinline__ float tf32_trunc(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
 __device__ __forceinline__ void split4(float4 v, float4& hi, float4& lo) {
     hi = make_float4(tf32_trunc(v.x), tf32_trunc(v.y), tf32_trunc(v.z), tf32_trunc(v.w));
-    lo = make_float4(tf32_trunc(v.x - hi.x), tf32_trunc(v.y - hi.y), tf32_trunc(v.z - hi.z), tf32_trunc(v.w - hi.w));
+    // v - hi is exact (the low mantissa bits of v); the tensor core reads only its top 19 bits, and hi + lo == v
+    lo = make_float4(v.x - hi.x, v.y - hi.y, v.z - hi.z, v.w - hi.w);
 }
 
 // Rows [0, n_a): anchors of the triples; rows [n_a, n_a + n_x): the negative rows, in id-list order.
@@ -220,7 +221,7 @@ constexpr int UM_EPI_BYTES = 8 * 32 * 32 * 4;                // epilogue staging
 constexpr int UM_TAIL_BYTES = 256 + UM_EPI_BYTES;            // barriers and tensor-memory slot, then the staging squares
 constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
-enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3, EP_GV = 4, EP_SCATTER = 5 };
+enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3, EP_GV = 4, EP_SCATTER = 5, EP_LOSS = 6 };
 
 struct GemmTc {
     int m_rows, n_cols, k_len;        // extents per batch
@@ -245,6 +246,14 @@ struct GemmTc {
     int group_k;
     // EP_GV: gv_out[row] = bf16(coef[row] * (acc + rel_vec[z]));  EP_SCATTER: rows go to neg_out (signed by side) / pos_out
     const float* coef; __nv_bfloat16* gv_out; int sc_n_neg; int sc_n_neg_head;
+    // EP_LOSS: the score never leaves the tile.  loss += neg_w * softplus(S), dS = neg_w * sigmoid(S), and
+    // W = dS (dot-product scorers) or dS / S (loss_dist: S = -sqrt(sq_a + sq_b - 2 acc), exact where that cancels) is
+    // stored split into w_hi / w_lo (pitch ldw) for the backward products, with partial row sums
+    // rowpart[(n_tile * 2 + half)][row], partial column sums colpart[(batch * ceil(m_rows / 32) + row block)][col]
+    // and one loss partial per epilogue warp and tile, loss_part[slot].
+    float* w_hi; float* w_lo; long long ldw; float neg_w; int loss_dist;
+    float* rowpart; float* colpart; float* loss_part;
+    const float* ex_a_hi; const float* ex_a_lo; const float* ex_x_hi; const float* ex_x_lo; long long ex_ld;   // exact rows
     int pair;                         // 1: CTA pairs (256-row tiles, umma_pair_kernel)
     int a_slabs4d, b_slabs4d;         // MN-major operand read through a 4-D slab map: one copy per stage instead of one per slab
     long long y_ld;                   // EP_RANK1: row pitch of y_hi / y_lo
@@ -271,7 +280,7 @@ constexpr int UM_EPI_WARPS = 8;
 // lane = COLUMN: global loads and stores are then 128-byte row segments, per-column operands are one register per lane,
 // per-row operands one shuffle per row, and the fix-up test is a mask bit instead of a branch per element.
 __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
-                                              int bn_tile, int buf, uint32_t drained, float* epi_smem) {
+                                              int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot) {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = q * 32 + lane;                 // row of the tile held by this thread after tcgen05.ld
@@ -320,10 +329,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     // per-row operands live in the lane that owns the row and are broadcast by shuffle
     float row_op = 0.f;
     if (row_ok) {
-        if (p.ep == EP_DIST) row_op = p.sq_a[grow0 + lane];
+        if (p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist)) row_op = p.sq_a[grow0 + lane];
         else if (p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
         else if (p.ep == EP_GV) row_op = p.coef[m];
     }
+    float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; lane r holds row r's sum of W
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
         const int nbase = n0 + c * 32;
@@ -346,7 +356,56 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 #pragma unroll
         for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
         __syncwarp();
-        if (p.ep == EP_DIST) {
+        if (p.ep == EP_LOSS) {
+            const float sb = (p.loss_dist && col_ok) ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
+            float* wh = p.w_hi + grow0 * p.ldw + col;
+            float* wl = p.w_lo + grow0 * p.ldw + col;
+            const bool pad_ok = col < p.ldw;         // pitch padding past the last column is written as zero
+            float col_acc = 0.f;
+#pragma unroll 4
+            for (int r = 0; r < rows_here; ++r, wh += p.ldw, wl += p.ldw) {
+                const float x = stg[r * 32 + (lane ^ r)];
+                float sc = x;
+                if (p.loss_dist) {
+                    const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
+                    float d2 = fmaf(-2.f, x, nn);
+                    unsigned flagged = __ballot_sync(0xffffffffu, col_ok && d2 < 0.015625f * nn);
+                    while (flagged) {                // cancellation: the squared distance again, from the rows themselves
+                        const int cl = __ffs(flagged) - 1;
+                        flagged &= flagged - 1;
+                        const long long ao = (grow0 + r) * p.ex_ld, xo = (static_cast<long long>(b) * p.n_cols + nbase + cl) * p.ex_ld;
+                        float e2 = 0.f;
+                        for (int k = lane; k < p.k_len; k += 32) {
+                            const float df = (p.ex_a_hi[ao + k] + p.ex_a_lo[ao + k]) - (p.ex_x_hi[xo + k] + p.ex_x_lo[xo + k]);
+                            e2 = fmaf(df, df, e2);
+                        }
+                        e2 = warp_sum(e2);
+                        if (lane == cl) d2 = e2;
+                    }
+                    sc = -sqrtf(fmaxf(d2, 0.f));
+                }
+                // softplus(sc) and sigmoid(sc) from one exponential: e = exp(-|sc|) in (0, 1]
+                const float e = __expf(-fabsf(sc));
+                const float l1p = e < 0.00024414062f ? e * fmaf(-0.5f, e, 1.f) : __logf(1.f + e);
+                const float inv = __fdividef(1.f, 1.f + e);
+                const float sig = sc >= 0.f ? inv : e * inv;
+                float w = p.neg_w * sig;
+                if (p.loss_dist) w = sc != 0.f ? __fdividef(w, sc) : 0.f;
+                if (!col_ok) w = 0.f;
+                if (col_ok) loss_acc = fmaf(p.neg_w, fmaxf(sc, 0.f) + l1p, loss_acc);
+                col_acc += w;
+                float rsum = w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+                if (lane == r) row_acc += rsum;
+                if (pad_ok) {
+                    const float h = __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
+                    *wh = h;
+                    *wl = w - h;
+                }
+            }
+            if (col_ok) p.colpart[(static_cast<long long>(b) * ((p.m_rows + 31) / 32) + (mq >> 5)) * p.n_cols + col] = col_acc;
+        } else if (p.ep == EP_DIST) {
             const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
             uint32_t bad = 0;
@@ -412,6 +471,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     umma::tc_fence_before();
     __syncwarp();
     if (lane == 0) umma::mbar_arrive_cluster(drained);
+    if (p.ep == EP_LOSS) {
+        const long long total_rows = static_cast<long long>(p.batch) * p.m_rows;
+        if (row_ok) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
+        const float l = warp_sum(loss_acc);
+        if (lane == 0) p.loss_part[slot * UM_EPI_WARPS + (warp - 2)] = l;
+    }
 }
 
 // Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
@@ -587,7 +652,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }   // warp-uniform result
             umma::tc_fence_after();
-            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem);
+            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
     umma::tc_fence_before();
@@ -774,7 +839,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }
             umma::tc_fence_after();
             epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
-                          umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem);
+                          umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank);
         }
     }
     umma::tc_fence_before();
@@ -821,11 +886,19 @@ static inline size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 struct TcLayout {        // carving of the tensor-core workspace
     size_t mat;          // bytes of one (n_a + n_x, dim) matrix
     size_t w;            // bytes of one (batch, n_neg) matrix (backward only)
-    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, off_colpart, total;
+    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, off_colpart, off_rowpart, off_losspart, total;
+    long long loss_parts;    // fused mode: loss partials (one per epilogue warp and 128-row tile)
+    int fwd_bn, fwd_pair;    // tiling of the forward product
     unsigned long long fix_cap;
     int ldp, ldw;        // row pitches in floats: dim and n_neg rounded up to whole 128-byte slabs
 };
-static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool backward) {
+// CTA pairs pay off once a product has more than one 128-row tile per batch; narrow outputs stay on the one-CTA kernel.
+static bool want_pair(int m_rows, int n_cols) { return m_rows > UM_BM && n_cols >= 64; }
+static int pick_bn(int n);
+
+// mode 0: forward, 1: backward, 2: fused forward + loss + backward
+static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, int mode) {
+    const bool backward = mode != 0;
     TcLayout L;
     const long long n_chunks = batch / chunk;
     const size_t rows = static_cast<size_t>(batch + n_chunks * n_neg);
@@ -835,6 +908,10 @@ static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool b
     L.mat = al256(rows * L.ldp * 4);
     L.w = backward ? al256(static_cast<size_t>(batch) * L.ldw * 4) : 0;
     L.fix_cap = backward ? 0 : (pairs / 64 > 4096 ? pairs / 64 : 4096);
+    L.fwd_pair = want_pair(chunk, n_neg) ? 1 : 0;
+    L.fwd_bn = L.fwd_pair ? pick_bn(n_neg) : (n_neg >= 128 ? 128 : pick_bn(n_neg));
+    const long long tiles_n = (n_neg + L.fwd_bn - 1) / L.fwd_bn;
+    L.loss_parts = tiles_n * ((chunk + UM_BM - 1) / UM_BM + 1) * n_chunks * UM_EPI_WARPS;
     size_t o = 0;
     L.off_hi = o; o += L.mat;
     L.off_lo = o; o += L.mat;
@@ -846,11 +923,13 @@ static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, bool b
     L.off_rowsum = o; o += backward ? al256(static_cast<size_t>(batch) * 4) : 0;
     L.off_colsum = o; o += backward ? al256(static_cast<size_t>(n_chunks) * n_neg * 4) : 0;
     L.off_colpart = o; o += backward ? al256(static_cast<size_t>(n_chunks) * ((chunk + TW_ROWS - 1) / TW_ROWS) * n_neg * 4) : 0;
+    L.off_rowpart = o; o += mode == 2 ? al256(static_cast<size_t>(2 * tiles_n) * batch * 4) : 0;
+    L.off_losspart = o; o += mode == 2 ? al256(static_cast<size_t>(L.loss_parts) * 4) : 0;
     L.total = o;
     return L;
 }
-size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int backward) {
-    return tc_layout(batch, chunk, n_neg, dim, backward != 0).total;
+size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode) {
+    return tc_layout(batch, chunk, n_neg, dim, mode).total;
 }
 
 template <int MODEL, typename T, typename I>
@@ -988,16 +1067,13 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     return 0;
 }
 
-// CTA pairs pay off once a product has more than one 128-row tile per batch; narrow outputs stay on the one-CTA kernel.
-static bool want_pair(int m_rows, int n_cols) { return m_rows > UM_BM && n_cols >= 64; }
-
 // Forward scores of the chunk's negatives.  ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 0).
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s) {
     if (a.batch <= 0 || a.n_neg <= 0) return 0;
     if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, false);
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 0);
     if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
     float* hi = reinterpret_cast<float*>(w + L.off_hi);
@@ -1015,8 +1091,8 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     // n_neg rows need 16-byte row pitch in the output only for vector stores; tensor maps need dim % 4 == 0 (checked)
     CUtensorMap mah, mal, mbh, mbl;
     const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4;
-    const bool pair = want_pair(a.chunk, a.n_neg);
-    const int bn = pair ? pick_bn(a.n_neg) : (a.n_neg >= 128 ? 128 : pick_bn(a.n_neg));
+    const bool pair = L.fwd_pair != 0;
+    const int bn = L.fwd_bn;
     const int b_box = pair ? bn / 2 : bn;           // a CTA of a pair stages half of the tile's columns
     if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
     if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
@@ -1042,44 +1118,19 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     return rc;
 }
 
-// Backward contractions.  ga: (batch, dim) fp32 anchor-gradient rows; g_neg rows are written to a.g_neg.  For the distance
-// scorer ga holds only sum_j W_ij x_j and *ga_scale the row sums of W: the anchor gradient is ga_scale[i] * anchor_i - ga_i,
-// applied by the per-triple backward kernel, which has the anchor row in registers anyway (else *ga_scale is NULL).
-// ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 1).
-int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s) {
-    *ga_scale = nullptr;
-    if (a.batch <= 0 || a.n_neg <= 0) return 0;
-    if (a.dim % 4 != 0 || a.n_neg % 4 != 0) {
-        set_error("the tensor-core backward needs dim %% 4 == 0 and n_neg %% 4 == 0, got %d and %d", a.dim, a.n_neg);
-        return KGE_E_UNSUPPORTED;
-    }
+// The two backward products from W (split, in the workspace) and the packed operands: GA = W . X and GX = W^T . A, with
+// the rank-1 terms of the distance scorer (row / column sums of W).
+static int tc_backward_products(const ScoreArgs& a, const TcLayout& L, char* w, bool dist, float* ga, const float** ga_scale,
+                                cudaStream_t s) {
     const long long n_chunks = a.batch / a.chunk;
-    const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, true);
-    if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
-    char* w = static_cast<char*>(ws);
+    const long long n_a = a.batch;
     float* hi = reinterpret_cast<float*>(w + L.off_hi);
     float* lo = reinterpret_cast<float*>(w + L.off_lo);
     float* whi = reinterpret_cast<float*>(w + L.off_whi);
     float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
     float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
     float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
-    float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
-    const bool dist = a.model == KGE_TRANSE;
-    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, nullptr, s);
-    if (rc) return rc;
-    if (dist) {
-        const int bpc = (a.chunk + TW_ROWS - 1) / TW_ROWS;
-        tc_pack_w_sums_kernel<<<dim3(bpc, (unsigned)n_chunks), 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
-        KGE_LAUNCH_CHECK("tc_pack_w_sums_kernel");
-        tc_colsum_kernel<<<dim3((a.n_neg + 255) / 256, (unsigned)n_chunks), 256, 0, s>>>(colpart, bpc, a.n_neg, colsum);
-        KGE_LAUNCH_CHECK("tc_colsum_kernel");
-    } else {
-        const int wpb = 8;
-        const unsigned blocks = (unsigned)((a.batch + wpb - 1) / wpb);
-        tc_pack_w_kernel<<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
-        KGE_LAUNCH_CHECK("tc_pack_w_kernel");
-    }
+    int rc = 0;
     const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4, lw = static_cast<uint64_t>(L.ldw) * 4;
     // Pairs with an MN-major B: tiles are whole slabs per CTA (multiples of 64 columns), the last one narrowed by the kernel.
     // The packed matrices have whole-slab pitches, so MN-major operands are read through 4-D slab maps (one copy per stage);
@@ -1127,6 +1178,124 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float
     return run_gemm(mah, mal, mbh, mbl, p, n_chunks, s);
 }
 
+// Backward contractions.  ga: (batch, dim) fp32 anchor-gradient rows; g_neg rows are written to a.g_neg.  For the distance
+// scorer ga holds only sum_j W_ij x_j and *ga_scale the row sums of W: the anchor gradient is ga_scale[i] * anchor_i - ga_i,
+// applied by the per-triple backward kernel, which has the anchor row in registers anyway (else *ga_scale is NULL).
+// ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 1).
+int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s) {
+    *ga_scale = nullptr;
+    if (a.batch <= 0 || a.n_neg <= 0) return 0;
+    if (a.dim % 4 != 0 || a.n_neg % 4 != 0) {
+        set_error("the tensor-core backward needs dim %% 4 == 0 and n_neg %% 4 == 0, got %d and %d", a.dim, a.n_neg);
+        return KGE_E_UNSUPPORTED;
+    }
+    const long long n_chunks = a.batch / a.chunk;
+    const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 1);
+    if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = static_cast<char*>(ws);
+    float* hi = reinterpret_cast<float*>(w + L.off_hi);
+    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    float* whi = reinterpret_cast<float*>(w + L.off_whi);
+    float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
+    float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
+    float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
+    float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
+    const bool dist = a.model == KGE_TRANSE;
+    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, nullptr, s);
+    if (rc) return rc;
+    if (dist) {
+        const int bpc = (a.chunk + TW_ROWS - 1) / TW_ROWS;
+        tc_pack_w_sums_kernel<<<dim3(bpc, (unsigned)n_chunks), 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
+        KGE_LAUNCH_CHECK("tc_pack_w_sums_kernel");
+        tc_colsum_kernel<<<dim3((a.n_neg + 255) / 256, (unsigned)n_chunks), 256, 0, s>>>(colpart, bpc, a.n_neg, colsum);
+        KGE_LAUNCH_CHECK("tc_colsum_kernel");
+    } else {
+        const int wpb = 8;
+        const unsigned blocks = (unsigned)((a.batch + wpb - 1) / wpb);
+        tc_pack_w_kernel<<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
+        KGE_LAUNCH_CHECK("tc_pack_w_kernel");
+    }
+    return tc_backward_products(a, L, w, dist, ga, ga_scale, s);
+}
+
+
+// ---- fused forward + logistic loss + backward (chunk-shared negatives) -----------------------------------------------
+// rowsum[i] = sum_t rowpart[t][i], t ascending.
+__global__ void __launch_bounds__(256) tc_rowsum_kernel(const float* rowpart, int parts, long long rows, float* rowsum) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows) return;
+    float s = 0.f;
+    for (int t = 0; t < parts; ++t) s += rowpart[(long long)t * rows + i];
+    rowsum[i] = s;
+}
+// loss[0] += sum of the partials, in a fixed order (thread-strided, then a tree).
+__global__ void __launch_bounds__(1024) tc_loss_add_kernel(const float* part, long long n, float* loss) {
+    __shared__ float red[1024];
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < n; i += 1024) s += part[i];
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 512; o > 0; o >>= 1) { if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    if (threadIdx.x == 0) *loss += red[0];
+}
+
+// Scores of the negatives, their logistic loss and the backward products in one pass: the forward tile kernel turns each
+// score into its loss term and its W entry in the epilogue (EP_LOSS), so the (batch x n_neg) score matrix, its gradient
+// and a second operand pack are never written or read.  loss[0] must already hold the positives' part; the negatives'
+// part is added.  ga / *ga_scale as in launch_pair_backward_tc; g_neg rows go to a.g_neg.
+// ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 2).
+int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
+                                 void* ws, size_t ws_bytes, cudaStream_t s) {
+    *ga_scale = nullptr;
+    if (a.batch <= 0 || a.n_neg <= 0) return 0;
+    if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
+    const long long n_chunks = a.batch / a.chunk;
+    const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 2);
+    if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = static_cast<char*>(ws);
+    float* hi = reinterpret_cast<float*>(w + L.off_hi);
+    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    float* sq = reinterpret_cast<float*>(w + L.off_sq);
+    float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
+    float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
+    float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
+    float* rowpart = reinterpret_cast<float*>(w + L.off_rowpart);
+    float* losspart = reinterpret_cast<float*>(w + L.off_losspart);
+    const bool dist = a.model == KGE_TRANSE;
+    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, sq, s);
+    if (rc) return rc;
+    CUtensorMap mah, mal, mbh, mbl;
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4;
+    const bool pair = L.fwd_pair != 0;
+    const int bn = L.fwd_bn;
+    const int b_box = pair ? bn / 2 : bn;
+    if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    GemmTc p;
+    memset(&p, 0, sizeof(p));
+    p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0; p.pair = pair;
+    p.ep = EP_LOSS;
+    p.sq_a = sq; p.sq_b = sq + n_a; p.loss_dist = dist ? 1 : 0; p.neg_w = neg_w;
+    p.w_hi = reinterpret_cast<float*>(w + L.off_whi); p.w_lo = reinterpret_cast<float*>(w + L.off_wlo); p.ldw = L.ldw;
+    p.rowpart = rowpart; p.colpart = colpart; p.loss_part = losspart;
+    p.ex_a_hi = hi; p.ex_a_lo = lo; p.ex_x_hi = hi + n_a * L.ldp; p.ex_x_lo = lo + n_a * L.ldp; p.ex_ld = L.ldp;
+    if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
+    const long long tiles_n = (a.n_neg + bn - 1) / bn;
+    const long long tiles = tiles_n * ((a.chunk + (pair ? 2 : 1) * UM_BM - 1) / ((pair ? 2 : 1) * UM_BM)) * n_chunks;
+    tc_loss_add_kernel<<<1, 1024, 0, s>>>(losspart, tiles * (pair ? 2 : 1) * UM_EPI_WARPS, loss);
+    KGE_LAUNCH_CHECK("tc_loss_add_kernel");
+    if (dist) {
+        tc_rowsum_kernel<<<(unsigned)((a.batch + 255) / 256), 256, 0, s>>>(rowpart, (int)(2 * tiles_n), a.batch, rowsum);
+        KGE_LAUNCH_CHECK("tc_rowsum_kernel");
+        tc_colsum_kernel<<<dim3((a.n_neg + 255) / 256, (unsigned)n_chunks), 256, 0, s>>>(colpart, (a.chunk + 31) / 32, a.n_neg, colsum);
+        KGE_LAUNCH_CHECK("tc_colsum_kernel");
+    }
+    return tc_backward_products(a, L, w, dist, ga, ga_scale, s);
+}
 
 // ---- TransR forward on the tensor cores (bf16 tables) ---------------------------------------------------------------
 // score(i, j) = -|| (a - b) . P[r_i] + R[r_i] ||.  The inspector has grouped the triples by relation; every group's

@@ -99,8 +99,9 @@ class KgeStep:
 
     def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
                  neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None,
-                 precision: str = "fp32"):
+                 precision: str = "fp32", fused: bool = True):
         self.models, self.ent_local, self.rel = list(models), ent_local, rel
+        self.fused = fused                    # use the fused forward+loss+backward call where the scorer supports it
         self.n_ent, self.rank, self.world, self.group = int(n_ent), int(rank), int(world), group
         self.neg_mode, self.n_neg_head, self.chunk, self.precision = neg_mode, n_neg_head, chunk, precision
         self.dim = ent_local.shape[1]
@@ -128,12 +129,17 @@ class KgeStep:
         rinsp = None
         for m in self.models:
             sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk, self.precision)
-            pos, negs, _ = sc.forward(sh, r32, st, sneg)
-            loss, dpos, dneg = scoring.logistic_loss(pos, negs)
-            out.loss[m], out.pos[m] = loss, pos
-            if not backward:
-                continue
-            sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
+            if backward and self.fused and sc.supports_fused_step(sneg.shape[-1]):
+                # one call: the scores of the negatives become loss terms and gradient weights inside the tile kernel
+                pos, loss, sg = sc.loss_backward(sh, r32, st, sneg)
+                out.loss[m], out.pos[m] = loss, pos
+            else:
+                pos, negs, _ = sc.forward(sh, r32, st, sneg)
+                loss, dpos, dneg = scoring.logistic_loss(pos, negs)
+                out.loss[m], out.pos[m] = loss, pos
+                if not backward:
+                    continue
+                sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
             grad_rows = scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)     # aligned with insp.uniq
             if rinsp is None:
                 rinsp = scoring.inspect(r32, self.n_rel[m])

@@ -337,6 +337,37 @@ class Scorer:
         return SlotGrads(ent_slots, rel_slots, rel2_slots, rel2_groups, rel_insp)
 
 
+    def supports_fused_step(self, n_neg: int) -> bool:
+        """True where loss_backward applies: tensor precision, chunk-shared negatives, TransE / DistMult / ComplEx."""
+        return (self.precision == PRECISIONS["tensor"] and self.neg_mode == "chunk_shared" and self.dim % 4 == 0
+                and n_neg % 4 == 0 and n_neg > 0 and self.model in ("TransE", "DistMult", "ComplEx"))
+
+    def loss_backward(self, h, r, t, neg, neg_weight: Optional[float] = None,
+                      ent_slots: Optional[torch.Tensor] = None):
+        """forward -> logistic_loss -> backward in one call (kge_score_loss_backward): returns (pos, loss, SlotGrads).
+        The scores of the negatives are consumed inside the tile kernel and are not returned."""
+        self._check_ids(h, r, t, neg)
+        B, d, dev = h.numel(), self.dim, self.ent.device
+        p = self._problem(h, neg)
+        kt = self._tensors(h, r, t, neg, None)
+        if neg_weight is None:
+            neg_weight = 1.0 / max(p.n_neg, 1)
+        n_slots = 2 * B + neg.numel()
+        if ent_slots is None:
+            ent_slots = torch.empty((n_slots, d), dtype=torch.float32, device=dev)
+        elif ent_slots.shape != (n_slots, d):
+            raise ValueError("ent_slots has the wrong shape")
+        rel_slots = torch.empty((B, d), dtype=torch.float32, device=dev)
+        pos = torch.empty(B, dtype=torch.float32, device=dev)
+        loss = torch.empty(1, dtype=torch.float32, device=dev)
+        g = KgeGrads(_ptr(ent_slots[:B]), _ptr(ent_slots[B:2 * B]), _ptr(ent_slots[2 * B:]), _ptr(rel_slots), None)
+        L = _lib.lib()
+        ws = workspace(L.kge_score_loss_backward_workspace_bytes(C.byref(p)), dev, "score")
+        check(L.kge_score_loss_backward(C.byref(p), C.byref(kt), float(neg_weight), _ptr(pos), _ptr(loss), C.byref(g),
+                                        _ptr(ws), ws.numel(), _stream()))
+        return pos, loss, SlotGrads(ent_slots, rel_slots, None, None, None)
+
+
 def entity_id_list(h, t, neg) -> torch.Tensor:
     """The id list [h | t | neg] whose slots SlotGrads.ent_slots follows."""
     parts = [h.reshape(-1), t.reshape(-1)]

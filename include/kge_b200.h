@@ -234,6 +234,19 @@ KGE_API int kge_score_backward(const kge_problem* p, const kge_tensors* t,
                        const float* dpos, const float* dneg, const kge_grads* g,
                        void* workspace, size_t workspace_bytes, kge_stream_t stream);
 
+/* Forward, logistic ranking loss and backward of the chunk-shared scorers in one call, on the tensor-core path:
+ * the same numbers as kge_score_forward -> kge_logistic_loss(neg_weight) -> kge_score_backward, but each score of a
+ * negative is turned into its loss term and its gradient weight inside the tile that produced it, so the
+ * (batch, n_neg) score matrix, its gradient and a second operand pack never reach memory.  Writes pos_score (batch,),
+ * loss_out (1,) and the gradient rows of `g`; scores of the negatives are not returned.  Needs precision
+ * KGE_PREC_TENSOR, neg_mode KGE_NEG_CHUNK_SHARED, dim % 4 == 0, n_neg % 4 == 0 and TransE, DistMult or ComplEx
+ * (KGE_E_UNSUPPORTED otherwise).  No reference counterpart: the reference stops at per-triple outputs
+ * (apps/kge/kge.py:273-390) and leaves loss and gradients to the caller's framework. */
+KGE_API size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p);
+KGE_API int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float neg_weight,
+                            float* pos_score, float* loss_out, const kge_grads* g,
+                            void* workspace, size_t workspace_bytes, kge_stream_t stream);
+
 /* Logistic ranking loss over the scores and its derivative, for driving fwd+bwd without a host round trip:
  * loss = sum softplus(-pos) + (1/n_neg_per_pos) sum softplus(neg);  dpos = -sigmoid(-pos),
  * dneg = sigmoid(neg)/n_neg_per_pos.  loss_out (1,) fp32 device, reduced in a fixed order.

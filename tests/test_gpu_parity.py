@@ -157,6 +157,66 @@ def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
     assert scoring.device_flags() == 0
 
 
+def _softplus(x):
+    return np.maximum(x, 0.0) + np.log1p(np.exp(-np.abs(x)))
+
+
+@pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx"])
+@pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
+                                                     (36, 7, 4, 12, 0), (100, 384, 2, 200, 0), (72, 520, 1, 1000, 1)])
+def test_fused_loss_backward(model, d, chunk, nchunks, nn, head):
+    """kge_score_loss_backward = forward -> logistic loss -> backward without the score matrix: the loss against the
+    oracle's scores (float64 softplus), positives and gradient rows against the unfused calls, all at the fp32 tolerance."""
+    from cuke_b200 import scoring
+    p = make_problem(model, seed=13 * d + chunk, ne=600, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    nnh = nn if head else 0
+    sc = gpu_scorer(p, nnh, precision="tensor")
+    assert sc.supports_fused_step(nn)
+    h, r, t, neg = gpu_ids(p)
+    pos, loss, sg = sc.loss_backward(h, r, t, neg)
+    assert scoring.device_flags() == 0
+    rpos, rneg = oracle.scores(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], p["neg"], "chunk_shared", nnh, chunk)
+    ref_loss = _softplus(-rpos.astype(np.float64)).sum() + _softplus(rneg.astype(np.float64)).sum() / nn
+    assert rel_err(pos.cpu().numpy(), rpos) < FP32_TOL
+    assert abs(float(loss.item()) - ref_loss) < FP32_TOL * abs(ref_loss)
+    pos_u, negs_u, _ = sc.forward(h, r, t, neg)
+    loss_u, dpos, dneg = scoring.logistic_loss(pos_u, negs_u)
+    sg_u = sc.backward(h, r, t, neg, pos_u, negs_u, dpos, dneg)
+    assert abs(float(loss.item()) - float(loss_u.item())) < FP32_TOL * abs(float(loss_u.item()))
+    assert rel_err(sg.ent_slots.cpu().numpy(), sg_u.ent_slots.cpu().numpy()) < FP32_TOL
+    assert rel_err(sg.rel_slots.cpu().numpy(), sg_u.rel_slots.cpu().numpy()) < FP32_TOL
+    pos2, loss2, sg2 = sc.loss_backward(h, r, t, neg)      # fixed summation orders: bit-identical on a second call
+    assert torch.equal(loss, loss2) and torch.equal(sg.ent_slots, sg2.ent_slots) and torch.equal(sg.rel_slots, sg2.rel_slots)
+
+
+def test_fused_loss_backward_cancellation():
+    """TransE negatives that (nearly) coincide with their anchor: the fused epilogue recomputes those distances from the
+    rows themselves, so loss and gradients still match the unfused exact path."""
+    from cuke_b200 import scoring
+    d, chunk, nchunks, nn = 128, 256, 2, 512
+    p = make_problem("TransE", seed=5, ne=4000, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk)
+    g = p["g"]
+    E, R = p["E"], p["R"]
+    for c in range(nchunks):
+        for k in range(24):
+            i = c * chunk + int(g.integers(0, chunk))
+            anchor = E[p["h"][i]] + R[p["r"][i]]
+            row = 3000 + c * 24 + k
+            E[row] = anchor * (1.0 + (1e-3 * g.standard_normal(d)).astype(np.float32) * (k % 2))
+            p["neg"][c, k] = row
+    sc = gpu_scorer(p, 0, precision="tensor")
+    sc_exact = gpu_scorer(p, 0)                      # CUDA-core fp32 path
+    h, r, t, neg = gpu_ids(p)
+    pos, loss, sg = sc.loss_backward(h, r, t, neg)
+    assert scoring.device_flags() == 0
+    pos_u, negs_u, _ = sc_exact.forward(h, r, t, neg)
+    loss_u, dpos, dneg = scoring.logistic_loss(pos_u, negs_u)
+    sg_u = sc_exact.backward(h, r, t, neg, pos_u, negs_u, dpos, dneg)
+    assert abs(float(loss.item()) - float(loss_u.item())) < FP32_TOL * abs(float(loss_u.item()))
+    assert rel_err(sg.ent_slots.cpu().numpy(), sg_u.ent_slots.cpu().numpy()) < FP32_TOL
+    assert rel_err(sg.rel_slots.cpu().numpy(), sg_u.rel_slots.cpu().numpy()) < FP32_TOL
+
+
 @pytest.mark.parametrize("d,B,nn,nnh,nr", [(200, 64, 16, 8, 11), (64, 300, 5, 0, 3), (256, 40, 33, 33, 40), (200, 500, 0, 0, 1),
                                            (200, 1024, 128, 64, 50)])
 def test_transr_tensor_cores_bf16(d, B, nn, nnh, nr):
