@@ -260,10 +260,15 @@ struct GemmTc {
     int32_t* err;
 };
 
-__device__ __forceinline__ float sqrt_approx(float x) {       // MUFU square root, relative error ~2^-23
-    float r;
-    asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
-    return r;
+// One special-function instruction each (flush-to-zero forms: no denormal fix-up code around them); relative error ~2^-22.
+__device__ __forceinline__ float sqrt_approx(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float ex2_approx(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float lg2_approx(float x) { float r; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float rcp_approx(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+// log1p(e) for e in [0, 1]: lg2(1 + e) ln 2, or e - e^2/2 where 1 + e would round the small term away
+__device__ __forceinline__ float log1p_unit(float e) {
+    const float big = lg2_approx(1.f + e) * 0.69314718f;
+    return e < 0.00024414062f ? e * fmaf(-0.5f, e, 1.f) : big;
 }
 
 constexpr int UM_THREADS = 320;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2..9: epilogue
@@ -333,7 +338,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         else if (p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
         else if (p.ep == EP_GV) row_op = p.coef[m];
     }
-    float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; lane r holds row r's sum of W
+    float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; this thread's (= row's) sum of W
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
         const int nbase = n0 + c * 32;
@@ -357,54 +362,122 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
         __syncwarp();
         if (p.ep == EP_LOSS) {
-            const float sb = (p.loss_dist && col_ok) ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
             float* wh = p.w_hi + grow0 * p.ldw + col;
             float* wl = p.w_lo + grow0 * p.ldw + col;
             const bool pad_ok = col < p.ldw;         // pitch padding past the last column is written as zero
-            float col_acc = 0.f;
-#pragma unroll 4
-            for (int r = 0; r < rows_here; ++r, wh += p.ldw, wl += p.ldw) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                float sc = x;
-                if (p.loss_dist) {
-                    const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
-                    float d2 = fmaf(-2.f, x, nn);
-                    unsigned flagged = __ballot_sync(0xffffffffu, col_ok && d2 < 0.015625f * nn);
-                    while (flagged) {                // cancellation: the squared distance again, from the rows themselves
-                        const int cl = __ffs(flagged) - 1;
-                        flagged &= flagged - 1;
-                        const long long ao = (grow0 + r) * p.ex_ld, xo = (static_cast<long long>(b) * p.n_cols + nbase + cl) * p.ex_ld;
-                        float e2 = 0.f;
-                        for (int k = lane; k < p.k_len; k += 32) {
-                            const float df = (p.ex_a_hi[ao + k] + p.ex_a_lo[ao + k]) - (p.ex_x_hi[xo + k] + p.ex_x_lo[xo + k]);
-                            e2 = fmaf(df, df, e2);
-                        }
-                        e2 = warp_sum(e2);
-                        if (lane == cl) d2 = e2;
-                    }
-                    sc = -sqrtf(fmaxf(d2, 0.f));
-                }
-                // softplus(sc) and sigmoid(sc) from one exponential: e = exp(-|sc|) in (0, 1]
-                const float e = __expf(-fabsf(sc));
-                const float l1p = e < 0.00024414062f ? e * fmaf(-0.5f, e, 1.f) : __logf(1.f + e);
-                const float inv = __fdividef(1.f, 1.f + e);
-                const float sig = sc >= 0.f ? inv : e * inv;
-                float w = p.neg_w * sig;
-                if (p.loss_dist) w = sc != 0.f ? __fdividef(w, sc) : 0.f;
-                if (!col_ok) w = 0.f;
-                if (col_ok) loss_acc = fmaf(p.neg_w, fmaxf(sc, 0.f) + l1p, loss_acc);
-                col_acc += w;
-                float rsum = w;
+            const float nw = p.neg_w;
+            float lsum = 0.f;                        // loss terms of this chunk, scaled by neg_w once at the end
+            if (p.loss_dist) {
+                // S = -dd, dd = sqrt(d2) >= 0: softplus(S) = log1p(e), sigmoid(S) = e / (1 + e) with e = exp(-dd), and
+                // W = dS / S = -neg_w e / ((1 + e) dd).  The loop body has no branches, so rows overlap in the pipeline:
+                // columns past the end carry sq_b = +inf and entries whose d2 cancels are set to +inf too - both then
+                // contribute exact zeros - and the cancelling entries are redone from the rows themselves after the loop.
+                const float inf = __int_as_float(0x7f800000);
+                const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : inf;
+                float col_acc = 0.f;
+                uint32_t bad = 0;
+                // rows in batches of eight: all staging reads first, then eight independent chains, then the stores
+                // (a store between two reads would serialise the rows: the compiler cannot rule out aliasing)
+#pragma unroll 1
+                for (int r0 = 0; r0 < rows_here; r0 += 8) {
+                    float d2v[8], wv[8];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
-                if (lane == r) row_acc += rsum;
-                if (pad_ok) {
-                    const float h = __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
-                    *wh = h;
-                    *wl = w - h;
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = r0 + i;
+                        const float x = stg[r * 32 + (lane ^ r)];
+                        const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
+                        const float d2 = fmaf(-2.f, x, nn);
+                        const bool flag = d2 < 0.015625f * nn;
+                        bad |= (flag ? 1u : 0u) << r;
+                        d2v[i] = (flag || r >= rows_here) ? inf : fmaxf(d2, 0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float dd = sqrt_approx(d2v[i]);
+                        const float e = ex2_approx(dd * -1.44269504f);
+                        const float q = rcp_approx((1.f + e) * dd);          // dd = inf: q = 0 and e = 0; dd = 0: masked below
+                        wv[i] = dd > 0.f ? (-nw * e) * q : 0.f;
+                        lsum += log1p_unit(e);
+                        col_acc += wv[i];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = r0 + i;
+                        if (r < rows_here) {
+                            stg[r * 32 + (lane ^ r)] = wv[i];                     // kept for the row sums below
+                            if (pad_ok) {
+                                const float h = __uint_as_float(__float_as_uint(wv[i]) & 0xFFFFE000u);
+                                wh[static_cast<long long>(r) * p.ldw] = h;
+                                wl[static_cast<long long>(r) * p.ldw] = wv[i] - h;
+                            }
+                        }
+                    }
+                }
+                bad &= rows_here >= 32 ? 0xffffffffu : ((1u << rows_here) - 1u);
+                if (__any_sync(0xffffffffu, bad != 0)) {
+                    for (int r = 0; r < rows_here; ++r) {
+                        unsigned todo = __ballot_sync(0xffffffffu, (bad >> r) & 1u);
+                        while (todo) {
+                            const int cl = __ffs(todo) - 1;
+                            todo &= todo - 1;
+                            const long long ao = (grow0 + r) * p.ex_ld, xo = (static_cast<long long>(b) * p.n_cols + nbase + cl) * p.ex_ld;
+                            float e2 = 0.f;
+                            for (int k = lane; k < p.k_len; k += 32) {
+                                const float df = (p.ex_a_hi[ao + k] + p.ex_a_lo[ao + k]) - (p.ex_x_hi[xo + k] + p.ex_x_lo[xo + k]);
+                                e2 = fmaf(df, df, e2);
+                            }
+                            e2 = warp_sum(e2);
+                            if (lane == cl) {
+                                const float dd = sqrtf(e2);
+                                const float e = __expf(-dd);
+                                const float w = dd > 0.f ? -nw * e / ((1.f + e) * dd) : 0.f;
+                                lsum += log1pf(e);
+                                col_acc += w;
+                                stg[r * 32 + (lane ^ r)] = w;
+                                const float h = __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
+                                wh[static_cast<long long>(r) * p.ldw] = h;
+                                wl[static_cast<long long>(r) * p.ldw] = w - h;
+                            }
+                        }
+                    }
+                }
+                if (col_ok) p.colpart[(static_cast<long long>(b) * ((p.m_rows + 31) / 32) + (mq >> 5)) * p.n_cols + col] = col_acc;
+                __syncwarp();
+                if (lane < rows_here) {              // back to thread = row: this chunk's part of the row sum of W
+                    float rs = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) rs += stg[lane * 32 + (j ^ lane)];
+                    row_acc += rs;
+                }
+            } else {
+#pragma unroll 1
+                for (int r0 = 0; r0 < rows_here; r0 += 8) {
+                    float sv[8], wv[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { const int r = r0 + i; sv[i] = stg[r * 32 + (lane ^ r)]; }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        // softplus(sc) and sigmoid(sc) from one exponential: e = exp(-|sc|) in (0, 1]
+                        const float sc = sv[i];
+                        const float e = ex2_approx(fabsf(sc) * -1.44269504f);
+                        const float l1p = log1p_unit(e);
+                        const float inv = rcp_approx(1.f + e);
+                        const bool ok = col_ok && r0 + i < rows_here;
+                        wv[i] = ok ? nw * (sc >= 0.f ? inv : e * inv) : 0.f;
+                        lsum += ok ? fmaxf(sc, 0.f) + l1p : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = r0 + i;
+                        if (pad_ok && r < rows_here) {
+                            const float h = __uint_as_float(__float_as_uint(wv[i]) & 0xFFFFE000u);
+                            wh[static_cast<long long>(r) * p.ldw] = h;
+                            wl[static_cast<long long>(r) * p.ldw] = wv[i] - h;
+                        }
+                    }
                 }
             }
-            if (col_ok) p.colpart[(static_cast<long long>(b) * ((p.m_rows + 31) / 32) + (mq >> 5)) * p.n_cols + col] = col_acc;
+            loss_acc = fmaf(nw, lsum, loss_acc);
         } else if (p.ep == EP_DIST) {
             const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
@@ -473,7 +546,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     if (lane == 0) umma::mbar_arrive_cluster(drained);
     if (p.ep == EP_LOSS) {
         const long long total_rows = static_cast<long long>(p.batch) * p.m_rows;
-        if (row_ok) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
+        if (row_ok && p.loss_dist) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
         const float l = warp_sum(loss_acc);
         if (lane == 0) p.loss_part[slot * UM_EPI_WARPS + (warp - 2)] = l;
     }
