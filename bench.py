@@ -403,13 +403,17 @@ def main():
         U_r = int(torch.unique(r).numel())
         L = _lib.lib()
         if args.precision == "tensor":
-            # the six contractions of a step (forward S, backward GA and GX, for both scorers) are launches of ONE kernel
+            # the six contractions of a step (forward S with the loss epilogue, backward GA and GX, for both scorers) are
+            # launches of ONE kernel; the same calls as KgeStep.step makes
             def fwd_bwd():
                 for m in models:
                     sc = scoring.Scorer(m, staged, rel[m], None, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, "tensor")
-                    pos, negs, _ = sc.forward(sh, r32, st, sneg)
-                    loss, dpos, dneg = scoring.logistic_loss(pos, negs)
-                    sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
+                    if sc.supports_fused_step(sneg.shape[-1]):
+                        sc.loss_backward(sh, r32, st, sneg)
+                    else:
+                        pos, negs, _ = sc.forward(sh, r32, st, sneg)
+                        loss, dpos, dneg = scoring.logistic_loss(pos, negs)
+                        sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
             for _ in range(2):
                 fwd_bwd()
             torch.cuda.synchronize()
@@ -425,7 +429,8 @@ def main():
             ach = flops / t_k / 1e12
             # operands (hi and lo of both matrices) read once, result written once
             bytes_alg = 2 * 4 * (B + neg.numel()) * d + 4 * pairs
-            roof = {"kernel": "umma_gemm_kernel (tcgen05 3xTF32; average over the step's six contraction launches)",
+            roof = {"kernel": "umma_pair_kernel (tcgen05 cta_group::2, 3xTF32; average over the step's six contraction launches: "
+                              "two forward products with the fused loss epilogue, four backward products)",
                     "bound": "tensor", "achieved": ach, "peak": bf16_peak, "unit": "TFLOP/s", "frac": ach / bf16_peak,
                     "peak_source": f"MEASURED_PEAKS.json bf16 dense, burst ({peak_kind})",
                     "note": "achieved counts useful fp32 flops (2MNK); each is 3 tf32 MMAs at half the bf16 rate, so the "
