@@ -427,8 +427,8 @@ def main():
             t_k = ms.value * 1e-3 / max(n.value, 1)
             flops = fl.value / max(n.value, 1)
             ach = flops / t_k / 1e12
-            # operands (hi and lo of both matrices) read once, result written once
-            bytes_alg = 2 * 4 * (B + neg.numel()) * d + 4 * pairs
+            # forward launch: operands (hi and lo of both matrices) read once, W written once as hi and lo
+            bytes_alg = 2 * 4 * (B + neg.numel()) * d + 2 * 4 * pairs
             roof = {"kernel": "umma_pair_kernel (tcgen05 cta_group::2, 3xTF32; average over the step's six contraction launches: "
                               "two forward products with the fused loss epilogue, four backward products)",
                     "bound": "tensor", "achieved": ach, "peak": bf16_peak, "unit": "TFLOP/s", "frac": ach / bf16_peak,
@@ -436,8 +436,8 @@ def main():
                     "note": "achieved counts useful fp32 flops (2MNK); each is 3 tf32 MMAs at half the bf16 rate, so the "
                             "tensor pipe does 6x this many bf16-equivalent flops",
                     "tensor_pipe_equiv_frac": 6 * ach / bf16_peak, "launches_timed": n.value, "ms": t_k * 1e3,
-                    "traffic": 624e6, "traffic_note": "dram read+write of the forward launch, ncu capture at 32 chunks x 2 "
-                                                      "(profiles/umma_gemm_c5_32chunks_ncu_full.txt)",
+                    "traffic": 885.6e6, "traffic_note": "dram read+write of the TransE forward+loss launch, ncu capture at 32 chunks x 2 "
+                                                        "(profiles/umma_pair_c5_32chunks_ncu_full.txt)",
                     "hbm": {"bound": "hbm", "achieved": bytes_alg / t_k / 1e9, "peak": hbm_gbs, "unit": "GB/s",
                             "frac": bytes_alg / t_k / 1e9 / hbm_gbs, "bytes_alg": bytes_alg,
                             "peak_source": f"MEASURED_PEAKS.json ({peak_kind})"}}
