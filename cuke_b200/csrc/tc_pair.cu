@@ -221,6 +221,7 @@ constexpr int UM_EPI_BYTES = 8 * 32 * 32 * 4;                // epilogue staging
 constexpr int UM_TAIL_BYTES = 256 + UM_EPI_BYTES;            // barriers and tensor-memory slot, then the staging squares
 constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
+constexpr long long kTailSide = 1LL << 40;      // added to a slot number in row_dst: the row's gradient enters with a minus sign
 enum { EP_STORE = 0, EP_DIST = 1, EP_RANK1 = 2, EP_NORM = 3, EP_GV = 4, EP_SCATTER = 5, EP_LOSS = 6 };
 
 struct GemmTc {
@@ -527,7 +528,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 const float x = stg[r * 32 + (lane ^ r)];
                 const long long dst = p.row_dst[mq + r];          // same address in every lane: one broadcast load
                 if (dst == -1 || !col_ok) continue;
-                if (dst >= 0) p.neg_out[dst * p.n_cols + col] = ((int)(dst % p.sc_n_neg) >= p.sc_n_neg_head) ? -x : x;
+                if (dst >= kTailSide) p.neg_out[(dst - kTailSide) * p.n_cols + col] = -x;
+                else if (dst >= 0) p.neg_out[dst * p.n_cols + col] = x;
                 else p.pos_out[(-2 - dst) * p.n_cols + col] = x;
             }
         } else {                             // EP_STORE
@@ -1468,7 +1470,10 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
             }
         }
         if (lane == 0) {
-            row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1);
+            // backward: a tail-replaced negative receives minus the row gradient; the side is folded into the slot number
+            // here (+ kTailSide) so that the scatter epilogue needs no division per row
+            const bool tail_side = coef != nullptr && j > 0 && j - 1 >= a.n_neg_head;
+            row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1) + (tail_side ? kTailSide : 0);
             if (coef) {      // dL/dv = (dS / S) v
                 const float sc = j == 0 ? a.pos[i] : a.negs[(long long)i * a.n_neg + (j - 1)];
                 const float ds = j == 0 ? a.dpos[i] : a.dneg[(long long)i * a.n_neg + (j - 1)];
