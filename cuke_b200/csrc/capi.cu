@@ -159,7 +159,7 @@ static bool tc_transr(const kge_problem* p) {
     return p->precision == KGE_PREC_TENSOR && p->model == KGE_TRANSR && p->dtype == KGE_BF16 && p->dim % 8 == 0 && p->dim <= 256 &&
            p->neg_mode != KGE_NEG_CHUNK_SHARED;
 }
-static bool tc_backward(const kge_problem* p) { return tc_forward(p) && p->n_neg % 4 == 0; }
+static bool tc_backward(const kge_problem* p) { return tc_forward(p); }
 static size_t tc_bytes(const kge_problem* p, int backward) {
     if (backward ? !tc_backward(p) : !tc_forward(p)) return 0;
     return tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, backward);
@@ -403,7 +403,7 @@ int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float ne
     int rc = check_problem(fn, p, t, true);
     if (rc) return rc;
     if (!tc_fused(p)) {
-        set_error("%s: needs precision KGE_PREC_TENSOR, chunk-shared negatives with n_neg %% 4 == 0, dim %% 4 == 0 and "
+        set_error("%s: needs precision KGE_PREC_TENSOR, chunk-shared negatives, dim %% 4 == 0 and "
                   "TransE, DistMult or ComplEx; use kge_score_forward / kge_logistic_loss / kge_score_backward otherwise", fn);
         return KGE_E_UNSUPPORTED;
     }

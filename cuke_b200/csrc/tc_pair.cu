@@ -1260,10 +1260,7 @@ static int tc_backward_products(const ScoreArgs& a, const TcLayout& L, char* w, 
 int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s) {
     *ga_scale = nullptr;
     if (a.batch <= 0 || a.n_neg <= 0) return 0;
-    if (a.dim % 4 != 0 || a.n_neg % 4 != 0) {
-        set_error("the tensor-core backward needs dim %% 4 == 0 and n_neg %% 4 == 0, got %d and %d", a.dim, a.n_neg);
-        return KGE_E_UNSUPPORTED;
-    }
+    if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
     const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 1);

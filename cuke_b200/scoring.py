@@ -340,7 +340,7 @@ class Scorer:
     def supports_fused_step(self, n_neg: int) -> bool:
         """True where loss_backward applies: tensor precision, chunk-shared negatives, TransE / DistMult / ComplEx."""
         return (self.precision == PRECISIONS["tensor"] and self.neg_mode == "chunk_shared" and self.dim % 4 == 0
-                and n_neg % 4 == 0 and n_neg > 0 and self.model in ("TransE", "DistMult", "ComplEx"))
+                and n_neg > 0 and self.model in ("TransE", "DistMult", "ComplEx"))
 
     def loss_backward(self, h, r, t, neg, neg_weight: Optional[float] = None,
                       ent_slots: Optional[torch.Tensor] = None):

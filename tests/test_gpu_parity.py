@@ -146,7 +146,7 @@ def test_transe_tensor_cores_cancellation(frac, overflow):
 @pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx", "RESCAL"])
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
                                                      (36, 7, 4, 12, 0), (512, 512, 1, 1024, 0), (100, 384, 2, 200, 0),
-                                                     (72, 520, 1, 1000, 1)])
+                                                     (72, 520, 1, 1000, 1), (40, 260, 2, 129, 0), (36, 7, 3, 9, 0)])
 def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
     from cuke_b200 import scoring
     if model == "RESCAL":
@@ -163,7 +163,8 @@ def _softplus(x):
 
 @pytest.mark.parametrize("model", ["TransE", "DistMult", "ComplEx"])
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
-                                                     (36, 7, 4, 12, 0), (100, 384, 2, 200, 0), (72, 520, 1, 1000, 1)])
+                                                     (36, 7, 4, 12, 0), (100, 384, 2, 200, 0), (72, 520, 1, 1000, 1),
+                                                     (40, 260, 2, 129, 0), (36, 7, 3, 9, 0)])
 def test_fused_loss_backward(model, d, chunk, nchunks, nn, head):
     """kge_score_loss_backward = forward -> logistic loss -> backward without the score matrix: the loss against the
     oracle's scores (float64 softplus), positives and gradient rows against the unfused calls, all at the fp32 tolerance."""
