@@ -196,7 +196,8 @@ def workload_config(cfg, models, n_gpus):
                         f"per {cfg.chunk}-triple chunk, Zipf(1.1) entity ids",
             "scorers": models, "triples_per_gpu": cfg.batch, "neg_mode": cfg.neg_mode, "n_neg": cfg.n_neg, "chunk": cfg.chunk,
             "dim": cfg.dim, "n_ent": cfg.n_ent, "n_rel": cfg.n_rel, "parallelism": f"dp{n_gpus}+row-sharded-entities",
-            "l2": "inputs larger than L2 (6.4 GB table, 76 MB staged rows, 269 MB scores per scorer); no flush"}
+            "l2": "inputs larger than L2 (6.4 GB table, 76 MB staged rows, 2 x 268 MB of split gradient weights per scorer; "
+                  "the 268 MB score matrix is consumed inside the tile kernel); no flush"}
 
 
 # ---------------------------------------------------------------------------------------------------------
