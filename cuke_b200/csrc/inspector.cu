@@ -250,12 +250,24 @@ __global__ void __launch_bounds__(256) segred_span_kernel(int dim, long long n, 
     const int s = seg[u], e = seg[u + 1];
     if (e <= edge || s < b * 32) return;            // does not cross here, or started in an earlier window (block-uniform)
     const long long parts = (e - 1) / 32 - b + 1;   // part 0 = trail[b], part k = lead[b + k]
-    Row<NV> acc, x;
+    Row<NV> acc;
     row_zero<NV>(acc);
-    for (long long k = w; k < parts; k += 8) {
-        load_row_f32<NV, VEC>(x, (k == 0 ? trail + b * dim : lead + (b + k) * dim), dim, lane);
+    // four parts are requested before the first is added (same order of additions): the hottest row of a Zipf batch has
+    // hundreds of parts, and its chain of dependent loads would otherwise set the duration of the whole launch
+    for (long long k = w; k < parts; k += 32) {
+        Row<NV> x[4];
 #pragma unroll
-        for (int q = 0; q < NV; ++q) acc.v[q] = acc.v[q] + x.v[q];
+        for (int u = 0; u < 4; ++u) {
+            const long long kk = k + 8 * u;
+            if (kk < parts) load_row_f32<NV, VEC>(x[u], (kk == 0 ? trail + b * dim : lead + (b + kk) * dim), dim, lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (k + 8 * u < parts) {
+#pragma unroll
+                for (int q = 0; q < NV; ++q) acc.v[q] = acc.v[q] + x[u].v[q];
+            }
+        }
     }
     store_row<NV, VEC>(part + w * dim, acc, dim, lane);
     __syncthreads();
