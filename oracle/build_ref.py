@@ -23,7 +23,7 @@ with torch.utils.cpp_extension.  Two variants per scorer:
 Outputs go only to oracle/_ref/ (git-ignored; it travels to the GPU box as built files).
 No reference source is copied: the .cpp files are outputs of running the reference.
 
-Usage:  python oracle/build_ref.py [--ref /root/reference] [--only transE,...] [--threads T]
+Usage:  python oracle/build_ref.py [--ref <cuke checkout>] [--only transE,...] [--threads T]
 """
 from __future__ import annotations
 
