@@ -76,18 +76,52 @@ __global__ void __launch_bounds__(RS_THREADS) radix_hist_kernel(const unsigned* 
     hist[(long long)threadIdx.x * nblocks + blockIdx.x] = h[threadIdx.x];
 }
 
-// Exclusive scan of `total` unsigned counters by ONE block of 1024 threads (total <= 256 * 2048).
+// Exclusive scan of `total` unsigned counters by ONE block of 1024 threads (total <= 256 * 2048).  Each warp owns a
+// contiguous span (a multiple of 32 counters) and reads it 32 counters at a time, lane = consecutive counter: pass 1 sums
+// the spans, the 32 span totals are scanned, pass 2 rewrites each span with its running prefix.  Four groups are
+// requested before the first is used, so a span costs a few memory round trips instead of one per counter.
 __global__ void __launch_bounds__(1024) scan_exclusive_kernel(unsigned* data, int total, long long* total_out) {
-    __shared__ int warp_tot[33];
-    const int per = (total + 1023) / 1024;
-    const int lo = min(total, (int)threadIdx.x * per), hi = min(total, lo + per);
+    __shared__ int span_tot[32];
+    __shared__ int span_off[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int groups = (total + 31) / 32;                         // groups of 32 counters
+    const int gpw = (groups + 31) / 32;                           // groups per warp
+    const int g0 = w * gpw, g1 = min(groups, g0 + gpw);
     int s = 0;
-    for (int i = lo; i < hi; ++i) s += (int)data[i];
-    int block_total;
-    int incl = block_inclusive_scan(s, warp_tot, block_total);
-    int run = incl - s;
-    for (int i = lo; i < hi; ++i) { int v = (int)data[i]; data[i] = (unsigned)run; run += v; }
-    if (total_out && threadIdx.x == 0) *total_out = block_total;
+    for (int g = g0; g < g1; g += 4) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const int i = (g + u) * 32 + lane; v[u] = (g + u < g1 && i < total) ? (int)data[i] : 0; }
+        s += (v[0] + v[1]) + (v[2] + v[3]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
+    if (lane == 0) span_tot[w] = s;
+    __syncthreads();
+    if (w == 0) {
+        const int t = span_tot[lane];
+        int incl = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += y; }
+        span_off[lane] = incl - t;
+        if (lane == 31 && total_out) *total_out = incl;
+    }
+    __syncthreads();
+    int run = span_off[w];
+    for (int g = g0; g < g1; g += 4) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const int i = (g + u) * 32 + lane; v[u] = (g + u < g1 && i < total) ? (int)data[i] : 0; }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            int incl = v[u];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += y; }
+            const int i = (g + u) * 32 + lane;
+            if (g + u < g1 && i < total) data[i] = (unsigned)(run + incl - v[u]);
+            run += __shfl_sync(kFull, incl, 31);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(RS_THREADS) radix_scatter_kernel(const unsigned* keys_in, const int* vals_in,
