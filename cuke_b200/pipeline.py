@@ -119,14 +119,25 @@ class KgeStep:
         B = h.numel()
         insp = scoring.inspect(scoring.entity_id_list(h, t, neg), self.n_ent)
         out.n_staged = insp.n_unique
+        r32 = r.to(torch.int32)
+        rinsp = None
         if self.exchange is None:
             staged = scoring.gather_rows(self.ent_local, insp.uniq, n_dev=insp.n_unique)
         else:
-            staged = self.exchange.stage(insp)
+            # the staging exchange (three collectives and one host read of the split sizes) runs on the side stream;
+            # the relation-side inspector needs no entity row and is queued on the main stream first, so it runs meanwhile
+            main = torch.cuda.current_stream()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            if backward:
+                rinsp = scoring.inspect(r32, self.n_rel[self.models[0]])
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                staged = self.exchange.stage(insp)
+            main.wait_stream(self.comm_stream)
+            staged.record_stream(main)
         sh, st = insp.inverse[:B], insp.inverse[B:2 * B]
         sneg = insp.inverse[2 * B:].view(neg.shape)
-        r32 = r.to(torch.int32)
-        rinsp = None
         for m in self.models:
             sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk, self.precision)
             if backward and self.fused and sc.supports_fused_step(sneg.shape[-1]):
@@ -141,22 +152,28 @@ class KgeStep:
                     continue
                 sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
             grad_rows = scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)     # aligned with insp.uniq
-            if rinsp is None:
-                rinsp = scoring.inspect(r32, self.n_rel[m])
-            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp, zero_tail=False)
-            dense_rel = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
-            scoring.scatter_rows(rel_rows, rinsp.uniq, dense_rel, n_dev=rinsp.n_unique)
             if self.exchange is None:
                 out.ent_ids, out.n_ent_rows, out.ent_grad[m] = insp.uniq, insp.n_unique, grad_rows
             else:
+                # the entity rows start their way home before the relation-side reduction is queued
                 main = torch.cuda.current_stream()
                 ready = torch.cuda.Event()
                 ready.record(main)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ready)
                     grad_rows.record_stream(self.comm_stream)
-                    dense_rel.record_stream(self.comm_stream)
                     out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
+            if rinsp is None:
+                rinsp = scoring.inspect(r32, self.n_rel[m])
+            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp, zero_tail=False)
+            dense_rel = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
+            scoring.scatter_rows(rel_rows, rinsp.uniq, dense_rel, n_dev=rinsp.n_unique)
+            if self.exchange is not None:
+                ready2 = torch.cuda.Event()
+                ready2.record(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ready2)
+                    dense_rel.record_stream(self.comm_stream)
                     dist.all_reduce(dense_rel, group=self.group)
             out.rel_grad[m] = dense_rel
         if self.exchange is not None and backward:
