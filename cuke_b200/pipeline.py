@@ -89,6 +89,12 @@ class StepOutput:
     ent_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n, dim) fp32 rows aligned with ent_ids
     rel_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n_rel, dim) dense fp32
     n_staged: Optional[torch.Tensor] = None      # (1,) distinct entity rows this rank touched
+    done: Optional[torch.cuda.Event] = None      # N GPUs, step(..., wait=False): recorded after the last gradient return
+
+    def wait(self) -> None:
+        """Make the current stream wait until the entity / relation gradients of this step have arrived."""
+        if self.done is not None:
+            torch.cuda.current_stream().wait_event(self.done)
 
 
 class KgeStep:
@@ -113,7 +119,11 @@ class KgeStep:
         # gradient rows travel home on a side stream while the next scorer computes
         self.comm_stream = torch.cuda.Stream(device=ent_local.device) if world > 1 else None
 
-    def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True) -> StepOutput:
+    def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True,
+             wait: bool = True) -> StepOutput:
+        """One step.  With several GPUs and wait=False the call returns while the last scorer's gradient rows are still
+        travelling to their owners (side stream); `StepOutput.wait()` orders a consumer after them.  The next step's
+        inspector then overlaps that return; its staging exchange runs on the same side stream, i.e. after it."""
         import torch.distributed as dist
         out = StepOutput()
         B = h.numel()
@@ -177,5 +187,8 @@ class KgeStep:
                     dist.all_reduce(dense_rel, group=self.group)
             out.rel_grad[m] = dense_rel
         if self.exchange is not None and backward:
-            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            out.done = torch.cuda.Event()
+            out.done.record(self.comm_stream)
+            if wait:
+                out.wait()
         return out
