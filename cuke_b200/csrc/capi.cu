@@ -71,6 +71,7 @@ int gemm_profile_read(double* ms, long long* launches, double* flops);
 int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float** ga_scale, void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
                                  void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_loss_add(const float* part, long long n, float* loss, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -420,29 +421,27 @@ int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float ne
     const size_t rb = rows_bytes(p), dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
     char* wsb = static_cast<char*>(workspace);
     float* ga = reinterpret_cast<float*>(wsb);                       // anchor gradients summed over the chunk's negatives
-    float* dpos = reinterpret_cast<float*>(wsb + rb);
-    void* loss_ws = wsb + rb + dpos_bytes;
+    float* pos_loss = reinterpret_cast<float*>(wsb + rb);            // loss term of every positive
     char* tcw = wsb + rb + dpos_bytes + 4096;
 
+    cudaError_t ce = cudaMemsetAsync(loss_out, 0, 4, s);
+    if (ce != cudaSuccess) return cuda_status(ce, "kge_score_loss_backward(loss)");
     ScoreArgs a = score_args(p, t);
     a.pos = pos_score;
-    ScoreArgs apos = a;
-    apos.n_neg = 0; apos.n_neg_head = 0;
-    rc = launch_triple_forward(apos, s);                             // positive scores
-    if (rc) return rc;
-    rc = launch_logistic_loss(pos_score, p->batch, nullptr, 0, neg_weight, dpos, nullptr, loss_out, loss_ws, 4096, s);
-    if (rc) return rc;
     a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel; a.g_rel2 = g->g_rel2;
     const bool head = p->n_neg_head > 0;
     const float* ga_scale = nullptr;
     rc = launch_pair_loss_backward_tc(a, head ? 1 : 0, neg_weight, loss_out, ga, &ga_scale, tcw,
                                       tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2), s);
     if (rc) return rc;
+    // positives: score, loss term, dS and their gradient rows in the per-triple kernel, on top of the anchor gradients
     ScoreArgs b = a;
-    b.dpos = dpos; b.n_neg = 0; b.n_neg_head = 0;
+    b.pos_loss = pos_loss; b.n_neg = 0; b.n_neg_head = 0;
     if (head) b.ga_head_init = ga; else b.ga_tail_init = ga;
     b.ga_init_scale = ga_scale;
-    return launch_triple_backward(b, s);
+    rc = launch_triple_backward(b, s);
+    if (rc) return rc;
+    return launch_loss_add(pos_loss, p->batch, loss_out, s);
 }
 
 int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg, int64_t n_neg_total, float neg_weight,

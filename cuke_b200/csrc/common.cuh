@@ -115,6 +115,8 @@ struct ScoreArgs {
     const void* h; const void* r; const void* t; const void* neg;
     float* pos; float* negs;                 // forward outputs / backward inputs (saved scores)
     const float* dpos; const float* dneg;    // backward
+    float* pos_loss;                         // optional (batch): the per-triple backward kernel forms the positive's score
+                                             // (-> pos), its logistic loss term (-> pos_loss) and dS itself; dpos is unused
     float* g_head; float* g_tail; float* g_neg; float* g_rel; float* g_rel2;
     const float* ga_tail_init;               // (batch, dim) anchor gradients accumulated elsewhere (chunk-shared)
     const float* ga_head_init;

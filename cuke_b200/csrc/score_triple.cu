@@ -227,7 +227,15 @@ __global__ void __launch_bounds__(128) triple_bwd_kernel(ScoreArgs a) {
         load_row<T, NV, VEC>(h, E + hid * dim, dim, lane);
         load_row<T, NV, VEC>(t, E + tid * dim, dim, lane);
         if (MODEL != KGE_RESCAL) load_row<T, NV, VEC>(r, R + rid * dim, dim, lane);
-        const float ds = a.dpos ? a.dpos[i] : 0.f;
+        float ds = a.dpos ? a.dpos[i] : 0.f;
+        if (a.pos_loss != nullptr) {          // fused step: same formulas as the logistic loss kernel
+            const float ps = positive_score<MODEL, NV>(h, t, r, w, h);
+            ds = -1.f / (1.f + __expf(ps));                                         // -sigmoid(-ps)
+            if (lane == 0) {
+                a.pos[i] = ps;
+                a.pos_loss[i] = fmaxf(-ps, 0.f) + log1pf(__expf(-fabsf(ps)));      // softplus(-ps)
+            }
+        }
         if (MODEL == KGE_TRANSE) {
             float s = 0.f;
 #pragma unroll

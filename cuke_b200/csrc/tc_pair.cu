@@ -1312,10 +1312,17 @@ __global__ void __launch_bounds__(1024) tc_loss_add_kernel(const float* part, lo
     if (threadIdx.x == 0) *loss += red[0];
 }
 
+// loss[0] += sum of part[0..n), in the fixed order of tc_loss_add_kernel.
+int launch_loss_add(const float* part, long long n, float* loss, cudaStream_t s) {
+    tc_loss_add_kernel<<<1, 1024, 0, s>>>(part, n, loss);
+    KGE_LAUNCH_CHECK("tc_loss_add_kernel");
+    return 0;
+}
+
 // Scores of the negatives, their logistic loss and the backward products in one pass: the forward tile kernel turns each
 // score into its loss term and its W entry in the epilogue (EP_LOSS), so the (batch x n_neg) score matrix, its gradient
-// and a second operand pack are never written or read.  loss[0] must already hold the positives' part; the negatives'
-// part is added.  ga / *ga_scale as in launch_pair_backward_tc; g_neg rows go to a.g_neg.
+// and a second operand pack are never written or read.  loss[0] must be initialised by the caller; the
+// negatives' part is added to it.  ga / *ga_scale as in launch_pair_backward_tc; g_neg rows go to a.g_neg.
 // ws: tc_pair_workspace_bytes(batch, chunk, n_neg, dim, 2).
 int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
                                  void* ws, size_t ws_bytes, cudaStream_t s) {
