@@ -85,6 +85,13 @@ int launch_loss_add(const float* part, long long n, float* loss, cudaStream_t s)
         if ((ptr) == nullptr) { set_error("%s: %s is NULL", fn, name); return KGE_E_NULL; } \
         if (reinterpret_cast<uintptr_t>(ptr) & ((bits) / 8 - 1)) { set_error("%s: %s is not aligned to its element size", fn, name); return KGE_E_ALIGN; } \
     } while (0)
+// gradient rows: vector (16-byte) stores only when dim % 4 == 0, element stores otherwise
+#define KGE_REQUIRE_ROWS(ptr, name, dim)                                               \
+    do {                                                                               \
+        if ((ptr) == nullptr) { set_error("%s: %s is NULL", fn, name); return KGE_E_NULL; } \
+        if (reinterpret_cast<uintptr_t>(ptr) & (((dim) % 4 == 0) ? 15u : 3u)) {        \
+            set_error("%s: %s is not aligned (16 bytes when dim %% 4 == 0, else 4)", fn, name); return KGE_E_ALIGN; } \
+    } while (0)
 #define KGE_OPTIONAL_PTR(ptr, name)                                                    \
     do {                                                                               \
         if ((ptr) != nullptr && !aligned16(ptr)) { set_error("%s: %s is not 16-byte aligned", fn, name); return KGE_E_ALIGN; } \
@@ -331,12 +338,12 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }
     KGE_REQUIRE_PTR(dpos, "dpos");
-    KGE_REQUIRE_PTR(g->g_head, "g_head"); KGE_REQUIRE_PTR(g->g_tail, "g_tail");
-    if (p->model != KGE_RESCAL) KGE_REQUIRE_PTR(g->g_rel, "g_rel");
-    if (p->model == KGE_TRANSH || p->model == KGE_RESCAL || p->model == KGE_TRANSR) KGE_REQUIRE_PTR(g->g_rel2, "g_rel2");
+    KGE_REQUIRE_ROWS(g->g_head, "g_head", p->dim); KGE_REQUIRE_ROWS(g->g_tail, "g_tail", p->dim);
+    if (p->model != KGE_RESCAL) KGE_REQUIRE_ROWS(g->g_rel, "g_rel", p->dim);
+    if (p->model == KGE_TRANSH || p->model == KGE_RESCAL || p->model == KGE_TRANSR) KGE_REQUIRE_ROWS(g->g_rel2, "g_rel2", p->dim);
     if (p->model == KGE_TRANSR) { KGE_REQUIRE_PTR(pos_score, "pos_score"); if (p->neg_mode != KGE_NEG_NONE) KGE_REQUIRE_PTR(neg_score, "neg_score"); }
     if (p->neg_mode != KGE_NEG_NONE) {
-        KGE_REQUIRE_PTR(dneg, "dneg"); KGE_REQUIRE_PTR(g->g_neg, "g_neg");
+        KGE_REQUIRE_PTR(dneg, "dneg"); KGE_REQUIRE_ROWS(g->g_neg, "g_neg", p->dim);
         if (p->neg_mode == KGE_NEG_CHUNK_SHARED && p->model == KGE_TRANSE) KGE_REQUIRE_PTR(neg_score, "neg_score");
     }
     (void)pos_score;

@@ -697,7 +697,8 @@ extern "C" int kge_segment_reduce_static(const float* rows, int32_t dim, int64_t
                   fn, nwin * dim, kStaticHalfFloats, (long long)n, dim);
         return KGE_E_RANGE;
     }
-    const void* ptrs[] = {n_out > 0 ? out : (float*)16, n > 0 ? (const void*)rows : (const void*)16,
+    // `out` receives rows whenever there is anything to reduce (n > 0) or to zero-fill (n_out > 0)
+    const void* ptrs[] = {(n_out > 0 || n > 0) ? out : (float*)16, n > 0 ? (const void*)rows : (const void*)16,
                           n > 0 ? (const void*)perm : (const void*)16, n > 0 ? (const void*)seg : (const void*)16,
                           n > 0 ? (const void*)n_unique : (const void*)16};
     const char* names[] = {"out", "rows", "perm", "seg", "n_unique"};

@@ -21,6 +21,7 @@
 // Replaces the scalar-FMA inner loops that cuke generates for bvv over gathered rows
 // (apps/kge/kge.py:13-15, pycuke1/codegen/gpu.py:43-51).
 #include <string.h>
+#include <atomic>
 #include "rows.cuh"
 #include "umma.cuh"
 
@@ -577,6 +578,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     uint64_t* acc_full = empty + p.stages;          // [2] accumulator written  (MMA -> epilogue)
     uint64_t* acc_empty = acc_full + 2;             // [2] accumulator drained  (epilogue -> MMA)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* epi_fail = tmem_slot + 1;    // set by an epilogue warp whose wait ran out (EP_NORM)
     float* epi_smem = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + 256);      // staging squares (EP_NORM: partial sums)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -593,6 +595,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
         for (int s = 0; s < 2; ++s) { umma::mbar_init(&acc_full[s], 1); umma::mbar_init(&acc_empty[s], UM_EPI_WARPS); }
+        *epi_fail = 0u;
         umma::fence_barrier_init();
     }
     if (warp == 1) { umma::tmem_alloc(tmem_slot, tmem_cols); umma::tmem_relinquish(); }
@@ -725,7 +728,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }   // warp-uniform result
+            bool ok = umma::mbar_wait(&acc_full[buf], aph);                                           // warp-uniform result
+            if (p.ep == EP_NORM) {
+                // the eight epilogue warps meet at a named barrier inside this epilogue: they give up together or not at all
+                if (!ok && lane == 0) *epi_fail = 1u;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                ok = *epi_fail == 0u;
+            }
+            if (!ok) { if (lane == 0) atomicOr(p.err, 2); break; }
             umma::tc_fence_after();
             epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
@@ -1094,12 +1104,16 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     if (p.passes == 0) p.passes = 3;
     p.err = device_error_word();
     if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
-    static bool attr_set = false;
-    if (!attr_set) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return cuda_status(cudaGetLastError(), "cudaDeviceGetAttribute(multiprocessor count)");
+    // the shared-memory opt-in is a per-device attribute of the kernel: remembered per device ordinal
+    static std::atomic<bool> attr_set[128];
+    if (dev < 0 || dev >= 128 || !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
         if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(tile kernels)");
-        attr_set = true;
+        if (dev >= 0 && dev < 128) attr_set[dev].store(true, std::memory_order_release);
     }
     const int slab_cols = 128 / p.elem_bytes;
     const int b_cols = p.pair ? p.bn / 2 : p.bn;                     // B columns staged per CTA
@@ -1111,9 +1125,6 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     p.batch = (int)batch;
     const int tile_rows = p.pair ? 2 * UM_BM : UM_BM;
     const long long n_tiles = (long long)((p.n_cols + p.bn - 1) / p.bn) * ((p.m_rows + tile_rows - 1) / tile_rows) * batch;
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        return cuda_status(cudaGetLastError(), "cudaDeviceGetAttribute(multiprocessor count)");
     const long long bound = p.tile_tab ? p.tile_cap : n_tiles;      // grouped mode: the tile count is only known on the device
     if (bound >= (1LL << 31)) { set_error("tile kernel: %lld tiles exceed the 32-bit tile index", bound); return KGE_E_SHAPE; }
     const int slots = p.pair ? sms / 2 : sms;                       // persistent: one CTA (or CTA pair) per SM (pair of SMs)

@@ -54,6 +54,9 @@ CONFIGS = {
     "c3": Config("c3", 3, "TransR", 40000, 1350, 200, 8192, 128, "per_triple", 64, dtype="bf16", ent_dist="zipf"),
     "c4": Config("c4", 4, "RESCAL", 100000, 500, 256, 16384, 256, "chunk_shared", 0, 256, ent_dist="zipf",
                  extra_models=("ComplEx",)),
+    # c4 over bf16 tables (same ids and values, tables rounded to bf16; accumulation stays fp32)
+    "c4_bf16": Config("c4_bf16", 4, "RESCAL", 100000, 500, 256, 16384, 256, "chunk_shared", 0, 256, dtype="bf16", ent_dist="zipf",
+                      extra_models=("ComplEx",)),
     "c5": Config("c5", 5, "TransE", 4000000, 1000, 400, 65536, 1024, "chunk_shared", 0, 1024, ent_dist="zipf",
                  extra_models=("DistMult",)),
 }

@@ -81,11 +81,18 @@ def ref_forward(model: str, E, R, P2, h, r, t) -> np.ndarray:
 
 def flat_scores(model: str, E, R, P2, h, r, t) -> np.ndarray:
     """Scalar score of every (h, r, t): reference output, plus -||.||_2 for the vector-valued scorers."""
-    out = ref_forward(model, E, R, P2, h, r, t)
     if model not in VECTOR_MODELS:
-        return out
-    sc = np.empty(out.shape[0], dtype=np.float32)
-    lib().ko_norm_scores(out.shape[0], out.shape[1], _p(out, C.c_float), _p(sc, C.c_float))
+        return ref_forward(model, E, R, P2, h, r, t)
+    # the (B, d) vectors are an intermediate here: long flattened batches go through in blocks (per-triple arithmetic,
+    # so the result does not depend on the blocking)
+    h, r, t = np.asarray(h), np.asarray(r), np.asarray(t)
+    B, blk = h.shape[0], 1 << 15
+    sc = np.empty(B, dtype=np.float32)
+    for lo in range(0, B, blk):
+        out = ref_forward(model, E, R, P2, h[lo:lo + blk], r[lo:lo + blk], t[lo:lo + blk])
+        part = np.empty(out.shape[0], dtype=np.float32)
+        lib().ko_norm_scores(out.shape[0], out.shape[1], _p(out, C.c_float), _p(part, C.c_float))
+        sc[lo:lo + blk] = part
     return sc
 
 

@@ -17,6 +17,45 @@ def rel_err(a, b):
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
 
 
+def elem_err(a, b):
+    """Element-wise companion of rel_err: max |a - b| / (|b| + 1e-3 max |b|).  Small entries are judged (almost) on
+    their own scale, so an error that the tensor-wide norm would hide behind one large entry shows up here."""
+    a = np.asarray(a, dtype=np.float64); b = np.asarray(b, dtype=np.float64)
+    if b.size == 0:
+        return 0.0
+    floor = 1e-3 * max(np.abs(b).max(), 1e-30)
+    return float((np.abs(a - b) / (np.abs(b) + floor)).max())
+
+
+def par_map(fn, items, workers=8):
+    """The oracle is single-threaded C called through ctypes (the GIL is released): independent pieces run side by side."""
+    from concurrent.futures import ThreadPoolExecutor
+    oracle.lib()
+    with ThreadPoolExecutor(max_workers=workers) as ex:
+        return list(ex.map(fn, items))
+
+
+def occurrence_problem(E, R, P2, h, r, t, neg):
+    """The same triples over tables in which every entity-id OCCURRENCE has a row of its own (copies of the original rows,
+    in the slot order [h | t | neg]) and relations are renumbered by first appearance in sorted order.  The oracle's dense
+    entity gradient over these tables IS the per-slot gradient the backward kernels write, so a sample of triples out of
+    a large batch can be checked without reducing the whole batch on the CPU.
+    Returns (E', R', P2', h', r', t', neg', rel_uniq)."""
+    h, r, t = (np.asarray(x, dtype=np.int64) for x in (h, r, t))
+    B = h.shape[0]
+    parts = [E[h], E[t]]
+    neg2 = None
+    if neg is not None:
+        neg = np.asarray(neg, dtype=np.int64)
+        parts.append(E[neg.reshape(-1)])
+        neg2 = (2 * B + np.arange(neg.size, dtype=np.int64)).reshape(neg.shape)
+    E2 = np.ascontiguousarray(np.concatenate(parts))
+    ru, r2 = np.unique(r, return_inverse=True)
+    R2 = None if R is None else np.ascontiguousarray(R[ru])
+    P22 = None if P2 is None else np.ascontiguousarray(P2[ru])
+    return E2, R2, P22, np.arange(B, dtype=np.int64), r2.astype(np.int64), B + np.arange(B, dtype=np.int64), neg2, ru
+
+
 def make_problem(model, seed=0, ne=300, nr=11, d=40, B=64, nn=8, neg_mode="per_triple", chunk=0, zipf=False):
     g = np.random.Generator(np.random.PCG64(1234 + seed))
     sig = 1.0 / np.sqrt(d)

@@ -180,3 +180,25 @@ def test_legacy_inspect_random_invariants():
         if c:
             vals, counts = np.unique(rel2[b], return_counts=True)
             assert counts.max() == np.sum(rel2[b] == uniq[b, 0])   # slot 0 = the most frequent id
+
+
+@pytest.mark.parametrize("model", ["TransE", "TransH", "TransR", "DistMult", "RESCAL", "ComplEx"])
+def test_occurrence_problem_gives_per_slot_gradients(model):
+    """kge_testlib.occurrence_problem: the oracle's dense gradient over one-row-per-occurrence tables, summed back by id,
+    is the dense gradient of the original problem (this is what lets the config tests check a sample of a large batch)."""
+    from tests.kge_testlib import make_problem, occurrence_problem
+    p = make_problem(model, seed=21, ne=40, nr=5, d=12, B=24, nn=6, zipf=True)
+    nnh = 0 if model == "RESCAL" else 3
+    g = p["g"]
+    dpos, dneg = g.standard_normal(24).astype(np.float32), g.standard_normal((24, 6)).astype(np.float32)
+    gE, gR, gP = oracle.grads(model, p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], dpos, p["neg"], dneg, "per_triple", nnh)
+    E2, R2, P2, h2, r2, t2, neg2, ru = occurrence_problem(p["E"], p["R"], p["P2"], p["h"], p["r"], p["t"], p["neg"])
+    oE, oR, oP = oracle.grads(model, E2, R2, P2, h2, r2, t2, dpos, neg2, dneg, "per_triple", nnh)
+    ids = np.concatenate([p["h"], p["t"], p["neg"].reshape(-1)])
+    back = np.zeros_like(gE)
+    np.add.at(back, ids, oE)
+    np.testing.assert_allclose(back, gE, rtol=1e-9, atol=1e-12)
+    if gR is not None:
+        np.testing.assert_allclose(oR, gR[ru], rtol=1e-9, atol=1e-12)
+    if gP is not None:
+        np.testing.assert_allclose(oP, gP[ru], rtol=1e-9, atol=1e-12)
