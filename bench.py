@@ -15,6 +15,15 @@ the owners) for BOTH scorers.  Scored triples per step per GPU = 2 scorers x (65
 One JSON line is printed by rank 0.  `value` is measured with the step's ids already on the device; `e2e` includes
 the pinned-host -> device copy of the ids and the device -> host read of the losses every step.  `--impl reference`
 times the reference's own CPU path (cuke's generated OpenMP C++, oracle/_ref) on a bounded sample.
+Beside the contract's keys the line carries
+  spread    the same K-step region repeated (median, min, max of ms per step);
+  roofline  the dominant kernel timed live (useful TFLOP/s against the measured bf16 peak), the ncu DRAM traffic of
+            its launches read from profiles/, and under "hbm" the compulsory bytes of the WHOLE step over the step time;
+  parity    computed outside the timed regions: at N = 1 one whole chunk of the timed batch through the timed KgeStep
+            object against the CPU oracle (loss, entity and relation gradients); at N > 1 the row-partitioned step
+            against the same step on one GPU (losses bit-equal, gradients 1e-5);
+  side      (N = 1) configurations c1-c4 and c4 over bf16 tables, one record per scorer, each with its roofline view
+            and the reference's OpenMP C++ on a bounded sample (`--no-side` skips them).
 """
 from __future__ import annotations
 
@@ -51,6 +60,7 @@ def parse():
     ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor"],
                     help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
+    ap.add_argument("--no-side", action="store_true", help="skip the c1-c4 side measurements appended to the c5 line")
     return ap.parse_args()
 
 
@@ -114,8 +124,10 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------
 def cpu_reference_rate(cfg, models, seconds: float, steps: int = 1, warmup: int = 0):
     """Scored triples/s of cuke's generated OpenMP C++ (forward: the reference's only complete path) on a bounded
-    sample of the workload: the first m triples of chunk 0 against that chunk's shared negatives, flattened the
-    way the reference flattens negatives, over a compact copy of exactly the rows the sample touches."""
+    sample of the workload, flattened the way the reference flattens negatives (apps/kge/data/data_init.py:55-61):
+    chunk-shared configurations take the first m triples of each of the first nc chunks against their chunk's shared
+    negatives, per-triple configurations the first m triples with their own negatives.  Tables are compact copies
+    holding exactly the rows the sample touches (fp32: the reference has no bf16 path)."""
     import torch
     from cuke_b200 import synth
     from oracle import oracle
@@ -124,55 +136,80 @@ def cpu_reference_rate(cfg, models, seconds: float, steps: int = 1, warmup: int 
     torch.set_num_threads(cores)
     h, r, t, neg = synth.make_batch(cfg, 0, 0)
     n_neg = neg.shape[1]
-    d = cfg.dim
+    shared = cfg.neg_mode == "chunk_shared"
     g = np.random.Generator(np.random.PCG64(synth.BASE_SEED + 5))
 
     def sample(m, nc=1):
-        """first m triples of each of the first nc chunks against their chunk's shared negatives, flattened"""
         hs, rs, ts = [], [], []
-        for c in range(nc):
-            lo = c * cfg.chunk
-            hh, rr, tt = h[lo:lo + m], r[lo:lo + m], t[lo:lo + m]
-            fh, fr, ft = oracle.flatten(hh, rr, tt, neg[c:c + 1], "chunk_shared", 0, m)
+        if shared:
+            for c in range(nc):
+                lo = c * cfg.chunk
+                hh, rr, tt = h[lo:lo + m], r[lo:lo + m], t[lo:lo + m]
+                fh, fr, ft = oracle.flatten(hh, rr, tt, neg[c:c + 1], "chunk_shared", 0, m)
+                hs += [hh, fh]; rs += [rr, fr]; ts += [tt, ft]
+        else:
+            hh, rr, tt = h[:m], r[:m], t[:m]
+            fh, fr, ft = oracle.flatten(hh, rr, tt, neg[:m], "per_triple", cfg.n_neg_head)
             hs += [hh, fh]; rs += [rr, fr]; ts += [tt, ft]
         fh, fr, ft = np.concatenate(hs), np.concatenate(rs), np.concatenate(ts)
         ue, inv = np.unique(np.concatenate([fh, ft]), return_inverse=True)
-        E = (g.standard_normal((len(ue), d)) / np.sqrt(d)).astype(np.float32)
-        R = (g.standard_normal((cfg.n_rel, d)) / np.sqrt(d)).astype(np.float32)
-        return E, R, inv[: len(fh)].astype(np.int32), fr.astype(np.int32), inv[len(fh):].astype(np.int32)
+        ur, rinv = np.unique(fr, return_inverse=True)
+        tabs = {}
+        for model in models:
+            d = synth.row_floats(cfg, model)
+            E = (g.standard_normal((len(ue), d)) / np.sqrt(d)).astype(np.float32)
+            R = None if model == "RESCAL" else (g.standard_normal((len(ur), d)) / np.sqrt(d)).astype(np.float32)
+            P2 = None
+            if model == "TransH":
+                w = g.standard_normal((len(ur), d))
+                P2 = (w / np.linalg.norm(w, axis=1, keepdims=True)).astype(np.float32)
+            if model in ("TransR", "RESCAL"):
+                P2 = (g.standard_normal((len(ur), d, d)) / np.sqrt(d)).astype(np.float32)
+            tabs[model] = (E, R, P2)
+        return tabs, inv[: len(fh)].astype(np.int32), rinv.astype(np.int32), inv[len(fh):].astype(np.int32)
 
-    def run(model, E, R, fh, fr, ft):
+    def run(model, tabs, fh, fr, ft):
+        E, R, P2 = tabs[model]
         if kind == "reference":
-            tt = torch.from_numpy
-            out = oracle.ref_run(model, tt(E), tt(R), None, tt(fh), tt(fr), tt(ft), omp=True)
+            tt = lambda a: None if a is None else torch.from_numpy(a)
+            out = oracle.ref_run(model, tt(E), tt(R), tt(P2), tt(fh), tt(fr), tt(ft), omp=True)
             if model in oracle.VECTOR_MODELS:
                 out = -torch.linalg.vector_norm(out, dim=1)      # the norm the reference leaves to its caller
             return out
-        return oracle.flat_scores(model, E, R, None, fh, fr, ft)
+        return oracle.flat_scores(model, E, R, P2, fh, fr, ft)
 
     # size the sample: probe with 8 triples x n_neg, then scale to the time budget
-    E, R, fh, fr, ft = sample(8)
-    t0 = time.perf_counter(); run(models[0], E, R, fh, fr, ft); probe = time.perf_counter() - t0
-    t0 = time.perf_counter(); run(models[0], E, R, fh, fr, ft); probe = min(probe, time.perf_counter() - t0)
-    per_triple = probe / len(fh)
-    want = seconds / max(steps + warmup, 1) / len(models) / max(per_triple, 1e-9) / (n_neg + 1)     # triples per step
-    m = int(max(8, min(cfg.chunk, want)))
-    nc = int(max(1, min(cfg.batch // cfg.chunk, 8, want // cfg.chunk)))
-    E, R, fh, fr, ft = sample(m, nc)
+    tabs, fh, fr, ft = sample(8)
+    probe = 1e9
+    for _ in range(2):
+        t0 = time.perf_counter()
+        for model in models:
+            run(model, tabs, fh, fr, ft)
+        probe = min(probe, time.perf_counter() - t0)
+    per_triple = probe / len(fh)                                                     # all scorers, per flattened triple
+    want = seconds / max(steps + warmup, 1) / max(per_triple, 1e-9) / (n_neg + 1)     # triples per step
+    if shared:
+        m = int(max(8, min(cfg.chunk, want)))
+        nc = int(max(1, min(cfg.batch // cfg.chunk, 8, want // cfg.chunk)))
+    else:
+        m, nc = int(max(8, min(cfg.batch, want))), 1
+    tabs, fh, fr, ft = sample(m, nc)
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
         for model in models:
-            run(model, E, R, fh, fr, ft)
+            run(model, tabs, fh, fr, ft)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
     scored = len(fh) * len(models)
     best = min(times)
+    what = (f"{m} triples of each of the first {nc} chunks x {n_neg} shared negatives + positives" if shared
+            else f"the first {m} triples x {n_neg} negatives + positives")
     return {"value": scored / best, "unit": "triples/s", "cores": cores if kind == "reference" else 1, "kind": kind,
-            "sample": f"forward only (the reference has no aggregated backward): {m} triples of each of the first {nc} chunks "
-                      f"x {n_neg} shared negatives + positives, flattened ({len(fh)} triples) x {len(models)} scorers, compact row table, "
-                      f"best of {len(times)}", "ms_per_step": statistics.mean(times) * 1e3, "scored_per_step": scored}
+            "sample": f"forward only (the reference has no aggregated backward): {what}, flattened ({len(fh)} triples) "
+                      f"x {len(models)} scorer(s), compact fp32 tables, best of {len(times)}",
+            "ms_per_step": statistics.mean(times) * 1e3, "scored_per_step": scored}
 
 
 def reference_arm(args, cfg, models):
@@ -204,23 +241,25 @@ def workload_config(cfg, models, n_gpus):
 # ---------------------------------------------------------------------------------------------------------
 # side measurements: the parity configurations c1-c4, one scorer at a time, single GPU
 # ---------------------------------------------------------------------------------------------------------
-def side_config(args):
-    """Times forward (and backward + gradient reduction where the scorer has one) of configs c1-c4 on one GPU and
-    prints one JSON line per scorer with the HBM view of the roofline.  Not the headline metric: the tables of
-    c1-c3 fit in L2, so a >256 MB buffer is written between timed iterations (cold-L2 figure) and the warm-L2
-    figure is reported beside it."""
+def side_measure(cname, steps, warmup, precision, cpu_seconds=0.0):
+    """Times forward (and backward + gradient reduction where the configuration has one) of a parity configuration on
+    one GPU, one scorer at a time; returns one record per scorer with the HBM view of the roofline and, if
+    cpu_seconds > 0, the reference's OpenMP C++ on a bounded sample.  Not the headline metric: the tables of c1-c3 fit
+    in L2, so a 384 MB buffer is written between timed iterations (cold-L2 figure) and the warm-L2 figure is reported
+    beside it."""
     import torch
     from cuke_b200 import scoring, synth
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    cfg = synth.CONFIGS[args.config]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = synth.CONFIGS[cname]
     hbm_gbs, _, peak_kind = peaks()
     flush = torch.empty(384 << 20, dtype=torch.uint8, device=dev)
+    out = []
     for model in (cfg.model,) + tuple(cfg.extra_models):
         ent, rel, rel2 = synth.make_tables(cfg, model)
         to = lambda a: None if a is None else torch.from_numpy(a).to(dev).to(torch.bfloat16 if cfg.dtype == "bf16" else torch.float32).contiguous()
         sc = scoring.Scorer(model, to(ent), to(rel), to(rel2), cfg.neg_mode, cfg.n_neg_head if model != "RESCAL" else 0, cfg.chunk,
-                            args.precision)
+                            precision)
+        del ent, rel, rel2
         h, r, t, neg = (torch.from_numpy(x).to(dev) for x in synth.make_batch(cfg, 0, 0))
         backward = cfg.backward
         d = synth.row_floats(cfg, model)
@@ -236,18 +275,18 @@ def side_config(args):
             return pos
 
         def timed(cold, bwd=True):
-            for _ in range(max(args.warmup, 3)):
+            for _ in range(max(warmup, 3)):
                 step(bwd)
             torch.cuda.synchronize()
             tot = 0.0
-            for _ in range(args.steps):
+            for _ in range(steps):
                 if cold:
                     flush.fill_(1)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(); step(bwd); e1.record()
                 torch.cuda.synchronize()
                 tot += e0.elapsed_time(e1)
-            return tot / args.steps
+            return tot / steps
 
         ms_cold, ms_warm, ms_fwd = timed(True), timed(False), timed(True, False)
         S = synth.scored_triples(cfg)
@@ -257,22 +296,103 @@ def side_config(args):
         bytes_fwd = U_e * d * es + U_r * relrow + 8 * (3 * cfg.batch + neg.numel()) + 4 * S
         bytes_bwd = (4 * S + U_e * d * 4 + U_r * relrow * 4 // es + U_e * d * es + U_r * relrow) if backward else 0
         bytes_alg = bytes_fwd + bytes_bwd
-        print(json.dumps({"metric": METRIC if backward else "scored_triples_per_sec_fwd", "side_measurement": True,
-                          "value": S / (ms_cold * 1e-3), "value_warm_l2": S / (ms_warm * 1e-3), "unit": "triples/s", "n_gpus": 1,
-                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm, "ms_fwd_only": ms_fwd,
-                          "dtype": cfg.dtype, "data": "synthetic", "precision": args.precision,
-                          "config": {"workload": f"{cfg.name}: {model} {'fwd+bwd' if backward else 'fwd'}, entities {cfg.n_ent}x{d}, "
-                                                 f"batch {cfg.batch}, {cfg.n_neg} negatives ({cfg.neg_mode})",
-                                     "l2": "384 MB written between timed iterations (cold L2); warm figure beside it"},
-                          "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms_cold * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
-                                       "frac": bytes_alg / (ms_cold * 1e-3) / 1e9 / hbm_gbs, "bytes_alg": bytes_alg,
-                                       "gathered_bytes": S * 2 * d * es, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
-                                       "traffic": None}}), flush=True)
+        rec = {"metric": METRIC if backward else "scored_triples_per_sec_fwd", "side_measurement": True,
+               "value": S / (ms_cold * 1e-3), "value_warm_l2": S / (ms_warm * 1e-3), "unit": "triples/s", "n_gpus": 1,
+               "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_cold, "ms_per_step_warm_l2": ms_warm, "ms_fwd_only": ms_fwd,
+               "dtype": cfg.dtype, "data": "synthetic", "precision": precision,
+               "config": {"workload": f"{cfg.name}: {model} {'fwd+bwd' if backward else 'fwd'}, entities {cfg.n_ent}x{d}, "
+                                      f"batch {cfg.batch}, {cfg.n_neg} negatives ({cfg.neg_mode})",
+                          "l2": "384 MB written between timed iterations (cold L2); warm figure beside it"},
+               "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms_cold * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                            "frac": bytes_alg / (ms_cold * 1e-3) / 1e9 / hbm_gbs, "bytes_alg": bytes_alg,
+                            "gathered_bytes": S * 2 * d * es, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
+                            "traffic": None}}
+        if model in ("TransR", "RESCAL"):
+            # contraction scorers: useful flops of the relation-matrix products beside the HBM view
+            # one d x d projection per scored triple (TransR, difference rows) or per positive (RESCAL); backward = 2 more
+            flops = 2.0 * d * d * (S if model == "TransR" else cfg.batch) * (3 if backward else 1)
+            _, bf16_peak, _ = peaks()
+            rec["roofline"]["tensor"] = {"useful_flops": flops, "achieved": flops / (ms_cold * 1e-3) / 1e12, "peak": bf16_peak,
+                                         "unit": "TFLOP/s", "frac": flops / (ms_cold * 1e-3) / 1e12 / bf16_peak}
+        if cpu_seconds > 0:
+            try:
+                res = cpu_reference_rate(cfg, [model], seconds=cpu_seconds, steps=2, warmup=1)
+                rec["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as e:
+                rec["cpu_baseline"] = {"value": None, "unit": "triples/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        out.append(rec)
+        del sc
+        torch.cuda.empty_cache()
+    return out
+
+
+def side_config(args):
+    import torch
+    torch.cuda.set_device(0)
+    for rec in side_measure(args.config, args.steps, args.warmup, args.precision, 0.0 if args.no_cpu_baseline else args.cpu_seconds):
+        print(json.dumps(rec), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------------------
+def profile_traffic():
+    """DRAM read + write of the tile kernel's launches as captured by ncu (profiles/umma_pair_c5_32chunks_ncu_full.txt:
+    one 'DRAM read' and one 'DRAM write' line per captured launch, in MB, at 32 of the bench's 64 chunks).  Returns
+    (bytes per launch averaged over the captured launches, launches captured, file) or None if the summary is absent."""
+    path = os.path.join(ROOT, "profiles", "umma_pair_c5_32chunks_ncu_full.txt")
+    if not os.path.exists(path):
+        return None
+    rd, wr = [], []
+    for ln in open(path):
+        f = ln.split()
+        if len(f) >= 4 and f[0] == "DRAM" and f[1] in ("read", "write") and f[-1] == "Mbyte":
+            (rd if f[1] == "read" else wr).append(float(f[2]) * 1e6)
+    if not rd or len(rd) != len(wr):
+        return None
+    return (sum(rd) + sum(wr)) / len(rd), len(rd), os.path.relpath(path, ROOT)
+
+
+def parity_single_gpu(cfg, models, stepper, ent_local, rel, devb, dev):
+    """One whole chunk of the bench's own batch (1,024 triples x 1,024 shared negatives x dim 400) through the same
+    KgeStep object the timed region uses, against the CPU oracle: loss, every entity gradient row, relation gradients.
+    Outside the timed region.  The oracle sees a compact copy of exactly the rows the chunk touches."""
+    import torch
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle
+    h, r, t, neg = devb[0]
+    c, nn = cfg.chunk, cfg.n_neg
+    hs, rs, ts, ns = h[:c].contiguous(), r[:c].contiguous(), t[:c].contiguous(), neg[:1].contiguous()
+    out = stepper.step(hs, rs, ts, ns)
+    U = int(out.n_ent_rows.item())
+    ids = out.ent_ids[:U]
+    E = ent_local[ids].cpu().numpy()                               # rows of the distinct ids, ascending
+    remap = lambda x: np.searchsorted(ids.cpu().numpy(), x.cpu().numpy())
+    hh, tt, ng, rr = remap(hs), remap(ts), remap(ns), rs.cpu().numpy()
+    sp = lambda x: np.maximum(x, 0.0) + np.log1p(np.exp(-np.abs(x)))
+    sg = lambda x: 1.0 / (1.0 + np.exp(-x))
+    oracle.lib()
+
+    def one(m):
+        R = rel[m].cpu().numpy()
+        pos, negs = oracle.scores(m, E, R, None, hh, rr, tt, ng, "chunk_shared", 0, c)
+        p64, n64 = pos.astype(np.float64), negs.astype(np.float64)
+        loss = sp(-p64).sum() + sp(n64).sum() / nn
+        gE, gR, _ = oracle.grads(m, E, R, None, hh, rr, tt, (-sg(-p64)).astype(np.float32), ng, (sg(n64) / nn).astype(np.float32),
+                                 "chunk_shared", 0, c)
+        rel_err = lambda a, b: float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+        return {"loss_rel_err": abs(out.loss[m].item() - loss) / abs(loss),
+                "pos_rel_err": rel_err(out.pos[m].double().cpu().numpy(), p64),
+                "entity_grad_rel_err": rel_err(out.ent_grad[m][:U].double().cpu().numpy(), gE),
+                "relation_grad_rel_err": rel_err(out.rel_grad[m].double().cpu().numpy(), gR)}
+    with ThreadPoolExecutor(max_workers=len(models)) as ex:
+        res = dict(zip(models, ex.map(one, models)))
+    worst = max(v for m in models for v in res[m].values())
+    return {"ok": bool(worst < 1e-4), "tolerance": 1e-4, "against": "CPU oracle (oracle/kge_oracle.c, pinned to the reference's generated C++)",
+            "case": f"chunk 0 of the timed batch: {c} triples x {nn} shared negatives, dim {cfg.dim}, {U} distinct rows, "
+                    f"through the timed KgeStep object", "scorers": res}
+
+
 def main():
     args = parse()
     from cuke_b200 import synth
@@ -290,7 +410,7 @@ def main():
     import torch
     import torch.distributed as dist
     from cuke_b200 import _lib, scoring
-    from cuke_b200.pipeline import KgeStep
+    from cuke_b200.pipeline import KgeStep, sharded_selfcheck
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -372,8 +492,13 @@ def main():
     w_main = max(args.warmup, 3)
     ms_step = timed(lambda i: stepper.step(*devb[i % nb], wait=(i == w_main + args.steps - 1)), args.steps, w_main)
     launches = (_lib.lib().kge_launch_count() - launches0) // (args.steps + max(args.warmup, 3))
-    clocks = sampler.stop() if rank == 0 else None
     value = scored_per_gpu * world / (ms_step * 1e-3)
+    # the same K-step region four more times: the spread of a 50-60 ms measurement
+    regions = [ms_step] + [timed(lambda i: stepper.step(*devb[i % nb], wait=(i == args.steps - 1)), args.steps, 0) for _ in range(4)]
+    clocks = sampler.stop() if rank == 0 else None
+    spread = {"regions": len(regions), "steps_each": args.steps, "ms_per_step_median": statistics.median(regions),
+              "ms_per_step_min": min(regions), "ms_per_step_max": max(regions),
+              "note": "`value` and `ms_per_step` are the first region (W warm-up steps, then exactly K timed steps)"}
 
     ms_fwd = timed(lambda i: stepper.step(*devb[i % nb], backward=False), max(3, args.steps // 2), 2)
 
@@ -388,7 +513,20 @@ def main():
 
     ms_e2e = timed(e2e_step, args.steps, 2)
     e2e = {"value": scored_per_gpu * world / (ms_e2e * 1e-3), "unit": "triples/s", "h2d_bytes_per_step": h2d_bytes,
-           "d2h_bytes_per_step": 4 * len(models), "ms_per_step": ms_e2e}
+           "d2h_bytes_per_step": 4 * len(models), "ms_per_step": ms_e2e,
+           "api": "cuke_b200.pipeline.KgeStep.step (pinned host ids -> device every step, losses read back every step)"}
+
+    # ---- parity, outside the timed regions -------------------------------------------------------------------------
+    parity = None
+    try:
+        if world == 1:
+            parity = parity_single_gpu(cfg, models, stepper, ent_local, rel, devb, dev)
+        else:
+            parity = sharded_selfcheck(rank, world, group, precision=args.precision)
+            if rank == 0:
+                parity["against"] = "the same step on one GPU with the whole table (GPU against GPU)"
+    except Exception as e:          # reported, never hidden
+        parity = {"ok": False, "error": f"{type(e).__name__}: {e}"}
 
     # ---- roofline of the dominant kernel, timed live (no collectives here: rank 0 only) ----------------------------
     hbm_gbs, bf16_peak, peak_kind = peaks()
@@ -406,6 +544,21 @@ def main():
         r32 = r.to(torch.int32)
         pairs = (B // cfg.chunk) * cfg.chunk * cfg.n_neg
         U_r = int(torch.unique(r).numel())
+        n_ids = 3 * B + neg.numel()
+        # compulsory HBM traffic of the WHOLE step: every distinct row once (the staging copy serves both scorers), ids
+        # once, one gradient row per distinct entity / relation row and scorer; the score matrix and its gradient are
+        # consumed inside the tile kernel (fused loss), so they contribute nothing.  Forward rows are read again by the
+        # backward only from the compact staging buffer, counted once more.
+        fused = args.precision == "tensor"
+        S1 = synth.scored_triples(cfg)
+        bytes_fwd = U * d * 4 + len(models) * U_r * d * 4 + 8 * n_ids + (0 if fused else len(models) * 4 * S1)
+        bytes_bwd = len(models) * (U * d * 4 + U_r * d * 4) + U * d * 4 + (0 if fused else len(models) * 4 * S1)
+        step_bytes = bytes_fwd + bytes_bwd
+        hbm_step = {"bound": "hbm", "scope": "whole step, compulsory bytes", "bytes_alg": step_bytes,
+                    "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                    "frac": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_gbs, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
+                    "distinct_entity_rows": U, "distinct_relation_rows": U_r,
+                    "note": "c5 with chunk-shared negatives is bound by the contraction, not by HBM: this fraction is small by construction"}
         L = _lib.lib()
         if args.precision == "tensor":
             # the six contractions of a step (forward S with the loss epilogue, backward GA and GX, for both scorers) are
@@ -432,20 +585,26 @@ def main():
             t_k = ms.value * 1e-3 / max(n.value, 1)
             flops = fl.value / max(n.value, 1)
             ach = flops / t_k / 1e12
-            # forward launch: operands (hi and lo of both matrices) read once, W written once as hi and lo
-            bytes_alg = 2 * 4 * (B + neg.numel()) * d + 2 * 4 * pairs
-            roof = {"kernel": "umma_pair_kernel (tcgen05 cta_group::2, 3xTF32; average over the step's six contraction launches: "
-                              "two forward products with the fused loss epilogue, four backward products)",
+            per_step = n.value // reps
+            traffic, traffic_note = None, "no ncu summary found under profiles/"
+            pt = profile_traffic()
+            if pt is not None:
+                scale = (B // cfg.chunk) / 32.0
+                traffic = pt[0] * scale
+                traffic_note = (f"dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of the {pt[1]} launches of one step captured by "
+                                f"ncu at 32 chunks ({pt[2]}), x {scale:g} for this run's {B // cfg.chunk} chunks (traffic grows with the chunk count)")
+            roof = {"kernel": "umma_pair_kernel (tcgen05 cta_group::2, 3xTF32; average over the step's contraction launches: "
+                              "per scorer the forward product with the fused loss epilogue and two backward products)",
                     "bound": "tensor", "achieved": ach, "peak": bf16_peak, "unit": "TFLOP/s", "frac": ach / bf16_peak,
                     "peak_source": f"MEASURED_PEAKS.json bf16 dense, burst ({peak_kind})",
                     "note": "achieved counts useful fp32 flops (2MNK); each is 3 tf32 MMAs at half the bf16 rate, so the "
                             "tensor pipe does 6x this many bf16-equivalent flops",
-                    "tensor_pipe_equiv_frac": 6 * ach / bf16_peak, "launches_timed": n.value, "ms": t_k * 1e3,
-                    "traffic": 885.6e6, "traffic_note": "dram read+write of the TransE forward+loss launch, ncu capture at 32 chunks x 2 "
-                                                        "(profiles/umma_pair_c5_32chunks_ncu_full.txt)",
-                    "hbm": {"bound": "hbm", "achieved": bytes_alg / t_k / 1e9, "peak": hbm_gbs, "unit": "GB/s",
-                            "frac": bytes_alg / t_k / 1e9 / hbm_gbs, "bytes_alg": bytes_alg,
-                            "peak_source": f"MEASURED_PEAKS.json ({peak_kind})"}}
+                    "tensor_pipe_equiv_frac": 6 * ach / bf16_peak, "launches_timed": n.value, "launches_per_step": per_step,
+                    "ms": t_k * 1e3, "share_of_step": per_step * t_k * 1e3 / ms_step,
+                    "traffic": traffic, "traffic_note": traffic_note,
+                    "traffic_per_step": None if traffic is None else traffic * per_step,
+                    "traffic_over_step_bytes_alg": None if traffic is None else traffic * per_step / step_bytes,
+                    "hbm": hbm_step}
         else:
             sc = scoring.Scorer(models[0], staged, rel[models[0]], None, cfg.neg_mode, cfg.n_neg_head, cfg.chunk)
             for _ in range(3):
@@ -462,23 +621,32 @@ def main():
             flop_per = 3 if models[0] == "TransE" else 2
             flops = flop_per * d * (pairs + B)
             fma_peak = scoring.fma_peak_tflops(dev)
-            bytes_alg = U * d * 4 + U_r * d * 4 + 4 * (3 * B + neg.numel()) + 4 * (pairs + B)
             roof = {"kernel": f"pair_fwd_kernel<{models[0]}> (+ positives kernel, <2% of the time)", "bound": "fp32_fma",
                     "achieved": flops / t_k / 1e12, "peak": fma_peak, "unit": "TFLOP/s", "frac": flops / t_k / 1e12 / fma_peak,
                     "peak_source": "kge_probe_fma microbenchmark on this GPU (2 flop per FMA)",
                     "pipe_slot_frac": (2 * d * (pairs + B) if models[0] == "TransE" else d * (pairs + B)) / t_k / (fma_peak * 1e12 / 2),
-                    "traffic": None, "ms": t_k * 1e3,
-                    "hbm": {"bound": "hbm", "achieved": bytes_alg / t_k / 1e9, "peak": hbm_gbs, "unit": "GB/s",
-                            "frac": bytes_alg / t_k / 1e9 / hbm_gbs, "peak_source": f"MEASURED_PEAKS.json ({peak_kind})",
-                            "bytes_alg": bytes_alg}}
+                    "traffic": None, "ms": t_k * 1e3, "hbm": hbm_step}
+        del staged
 
     cpu = None
+    side = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             res = cpu_reference_rate(cfg, models, seconds=args.cpu_seconds, steps=2, warmup=1)
             cpu = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
         except Exception as e:          # the baseline is reported, never required
             cpu = {"value": None, "unit": "triples/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    if rank == 0 and world == 1 and not args.no_side:
+        # the parity configurations c1-c4, after the timed c5 regions: one record per scorer (cold- and warm-L2 figures,
+        # HBM view of the roofline, the reference's OpenMP C++ on a bounded sample)
+        del stepper, devb
+        torch.cuda.empty_cache()
+        side = []
+        for cname in ("c1", "c2", "c3", "c4", "c4_bf16"):
+            try:
+                side += side_measure(cname, 5, 3, args.precision, 0.0 if args.no_cpu_baseline else min(args.cpu_seconds, 3.0))
+            except Exception as e:
+                side.append({"config": {"workload": cname}, "error": f"{type(e).__name__}: {e}"})
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
@@ -487,9 +655,10 @@ def main():
                     "fp32 storage and accumulation; contractions as 3xTF32 on the tensor cores (error-compensated, "
                     "max rel. error ~2e-6 vs fp64, inside the 1e-4 fp32 tolerance)" if args.precision == "tensor"
                     else "fp32 CUDA cores")),
+                "spread": spread,
                 "value_fwd_only": scored_per_gpu * world / (ms_fwd * 1e-3), "ms_per_step_fwd_only": ms_fwd,
                 "e2e": e2e, "gpu_launches": int(launches) * args.steps, "gpu_launches_per_step": int(launches),
-                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "parity": parity, "side": side}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier(group=group)

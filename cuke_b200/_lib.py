@@ -16,6 +16,8 @@ MODELS = {"TransE": 0, "TransH": 1, "TransR": 2, "TransF": 3, "DistMult": 4, "RE
 DTYPES = {"f32": 0, "bf16": 1}
 NEG_MODES = {"none": 0, "per_triple": 1, "chunk_shared": 2}
 PRECISIONS = {"fp32": 0, "tensor": 1}
+FLAG_CHECK_IDS = 1            # kge_problem.reserved
+ERR_WAIT_TIMEOUT, ERR_ID_RANGE = 2, 8     # values of the device error word (kge_check)
 VECTOR_MODELS = ("TransE", "TransH", "TransR")
 MATRIX_MODELS = ("TransR", "RESCAL")
 
@@ -56,6 +58,8 @@ SIGNATURES = {
     "kge_last_error": (C.c_char_p, []),
     "kge_launch_count": (C.c_longlong, []),
     "kge_check": (C.c_int, [_vp, C.POINTER(C.c_int32)]),
+    "kge_validate_ids": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _vp]),
+    "kge_selftest_wait_timeout": (C.c_int, [_i32, _vp]),
     "kge_ref_forward": (C.c_int, [_PP, _PT, _vp, _vp]),
     "kge_inspect_workspace_bytes": (_sz, [_i64]),
     "kge_inspect": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -72,6 +72,8 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float
 int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
                                  void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_loss_add(const float* part, long long n, float* loss, cudaStream_t s);
+int launch_validate_ids(const void* ids, int id_bits, long long n, long long limit, void* out, cudaStream_t s);
+int launch_wait_timeout_selftest(int polls, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
 #define KGE_REQUIRE_PTR(ptr, name)                                                     \
@@ -111,6 +113,8 @@ static int check_problem(const char* fn, const kge_problem* p, const kge_tensors
     if (p->dtype == KGE_BF16 && (p->dim & 7)) { set_error("%s: bf16 tables need dim %% 8 == 0 (16-byte rows), got %d", fn, p->dim); return KGE_E_UNSUPPORTED; }
     if (p->batch < 0) { set_error("%s: negative batch", fn); return KGE_E_SHAPE; }
     if (p->precision != KGE_PREC_FP32 && p->precision != KGE_PREC_TENSOR) { set_error("%s: unknown precision %d", fn, p->precision); return KGE_E_UNSUPPORTED; }
+    if (p->reserved & ~KGE_FLAG_CHECK_IDS) { set_error("%s: unknown flags 0x%x in reserved", fn, p->reserved); return KGE_E_UNSUPPORTED; }
+    if (!scored && p->reserved) { set_error("%s: KGE_FLAG_CHECK_IDS needs a workspace; check the ids with kge_validate_ids first", fn); return KGE_E_UNSUPPORTED; }
     if (p->batch == 0) return 0;
     KGE_REQUIRE_PTR(t->ent, "ent");
     if (uses_rel(p->model)) KGE_REQUIRE_PTR(t->rel, "rel");
@@ -175,6 +179,37 @@ static size_t tc_bytes(const kge_problem* p, int backward) {
 // Fused forward + loss + backward: the chunk-shared tensor-core scorers whose anchors are built from table rows alone.
 static bool tc_fused(const kge_problem* p) { return tc_backward(p) && p->model != KGE_RESCAL; }
 
+// ---- KGE_FLAG_CHECK_IDS: sanitised copies of h, r, t, neg in the tail of the workspace ------------------------------
+static long long neg_id_count(const kge_problem* p) {
+    if (p->neg_mode == KGE_NEG_PER_TRIPLE) return p->batch * p->n_neg;
+    if (p->neg_mode == KGE_NEG_CHUNK_SHARED && p->chunk > 0) return (p->batch / p->chunk) * p->n_neg;
+    return 0;
+}
+static inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+static size_t check_ids_bytes(const kge_problem* p) {
+    if (!p || !(p->reserved & KGE_FLAG_CHECK_IDS) || p->batch <= 0) return 0;
+    const size_t eb = p->id_bits == 64 ? 8 : 4;
+    return 3 * up256((size_t)p->batch * eb) + up256((size_t)neg_id_count(p) * eb) + 256;
+}
+// `at` = first byte of the id area (the call's own scratch ends there).  Fills *ts with the sanitised id pointers.
+static int sanitise_ids(const kge_problem* p, const kge_tensors* t, kge_tensors* ts, char* at, cudaStream_t s) {
+    *ts = *t;
+    const size_t eb = p->id_bits == 64 ? 8 : 4;
+    at = reinterpret_cast<char*>(up256(reinterpret_cast<uintptr_t>(at)));
+    const void* src[4] = {t->h, t->r, t->t, t->neg};
+    const void** dst[4] = {&ts->h, &ts->r, &ts->t, &ts->neg};
+    const long long cnt[4] = {p->batch, p->batch, p->batch, neg_id_count(p)};
+    const long long lim[4] = {p->n_ent, p->n_rel, p->n_ent, p->n_ent};
+    for (int k = 0; k < 4; ++k) {
+        if (cnt[k] <= 0 || src[k] == nullptr) continue;
+        int rc = launch_validate_ids(src[k], p->id_bits, cnt[k], lim[k], at, s);
+        if (rc) return rc;
+        *dst[k] = at;
+        at += up256((size_t)cnt[k] * eb);
+    }
+    return 0;
+}
+
 }  // namespace kge
 
 using namespace kge;
@@ -195,6 +230,22 @@ int kge_check(kge_stream_t stream, int32_t* flags_out) {
     if (e == cudaSuccess) e = cudaMemsetAsync(w, 0, sizeof(int32_t), s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return cuda_status(e, fn);
+}
+
+int kge_validate_ids(const void* ids, int32_t id_bits, int64_t n, int64_t id_space, void* sanitized, kge_stream_t stream) {
+    const char* fn = "kge_validate_ids";
+    if (id_bits != 32 && id_bits != 64) { set_error("%s: id_bits must be 32 or 64", fn); return KGE_E_UNSUPPORTED; }
+    if (n < 0 || id_space < 1) { set_error("%s: bad sizes", fn); return KGE_E_RANGE; }
+    if (n == 0) return 0;
+    KGE_REQUIRE_IDS(ids, "ids", id_bits);
+    if (sanitized) KGE_REQUIRE_IDS(sanitized, "sanitized", id_bits);
+    return launch_validate_ids(ids, id_bits, n, id_space, sanitized, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_selftest_wait_timeout(int32_t polls, kge_stream_t stream) {
+    const char* fn = "kge_selftest_wait_timeout";
+    if (polls < 1 || polls > 65536) { set_error("%s: polls %d outside [1, 65536]", fn, polls); return KGE_E_RANGE; }
+    return launch_wait_timeout_selftest(polls, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int kge_ref_forward(const kge_problem* p, const kge_tensors* t, float* out, kge_stream_t stream) {
@@ -279,7 +330,11 @@ int kge_segment_reduce(const float* rows, int32_t dim, int64_t n, const int32_t*
                                  workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
+static size_t score_scratch_bytes(const kge_problem* p, int32_t backward);
 size_t kge_score_workspace_bytes(const kge_problem* p, int32_t backward) {
+    return score_scratch_bytes(p, backward) + check_ids_bytes(p);
+}
+static size_t score_scratch_bytes(const kge_problem* p, int32_t backward) {
     if (!p || p->batch <= 0) return 256;
     const size_t rb = rows_bytes(p);
     if (backward && tc_transr(p))
@@ -300,9 +355,16 @@ int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_sco
     KGE_REQUIRE_PTR(pos_score, "pos_score");
     if (p->neg_mode != KGE_NEG_NONE) KGE_REQUIRE_PTR(neg_score, "neg_score");
     const size_t need = kge_score_workspace_bytes(p, 0);
-    if (need > 256) {
+    if (need > 256 || p->reserved) {
         KGE_REQUIRE_PTR(workspace, "workspace");
         if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    }
+    kge_tensors ts;
+    if (p->reserved & KGE_FLAG_CHECK_IDS) {
+        if (p->n_ent <= 0 || p->n_rel <= 0) { set_error("%s: KGE_FLAG_CHECK_IDS needs n_ent and n_rel", fn); return KGE_E_SHAPE; }
+        rc = sanitise_ids(p, t, &ts, static_cast<char*>(workspace) + score_scratch_bytes(p, 0), s);
+        if (rc) return rc;
+        t = &ts;
     }
     ScoreArgs a = score_args(p, t);
     a.pos = pos_score; a.negs = neg_score;
@@ -350,6 +412,13 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     const size_t need = kge_score_workspace_bytes(p, 1);
     KGE_REQUIRE_PTR(workspace, "workspace");
     if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+    kge_tensors ts;
+    if (p->reserved & KGE_FLAG_CHECK_IDS) {
+        if (p->n_ent <= 0 || p->n_rel <= 0) { set_error("%s: KGE_FLAG_CHECK_IDS needs n_ent and n_rel", fn); return KGE_E_SHAPE; }
+        rc = sanitise_ids(p, t, &ts, static_cast<char*>(workspace) + score_scratch_bytes(p, 1), s);
+        if (rc) return rc;
+        t = &ts;
+    }
     if (tc_transr(p)) {
         ScoreArgs a = score_args(p, t);
         a.pos = const_cast<float*>(pos_score); a.negs = const_cast<float*>(neg_score); a.dpos = dpos; a.dneg = dneg;
@@ -402,7 +471,7 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
 size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p) {
     if (!p || p->batch <= 0 || !tc_fused(p)) return 256;
     const size_t dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
-    return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2) + 256;
+    return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2) + 256 + check_ids_bytes(p);
 }
 
 int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float neg_weight, float* pos_score, float* loss_out,
@@ -433,6 +502,13 @@ int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float ne
 
     cudaError_t ce = cudaMemsetAsync(loss_out, 0, 4, s);
     if (ce != cudaSuccess) return cuda_status(ce, "kge_score_loss_backward(loss)");
+    kge_tensors ts;
+    if (p->reserved & KGE_FLAG_CHECK_IDS) {
+        if (p->n_ent <= 0 || p->n_rel <= 0) { set_error("%s: KGE_FLAG_CHECK_IDS needs n_ent and n_rel", fn); return KGE_E_SHAPE; }
+        rc = sanitise_ids(p, t, &ts, wsb + need - check_ids_bytes(p), s);
+        if (rc) return rc;
+        t = &ts;
+    }
     ScoreArgs a = score_args(p, t);
     a.pos = pos_score;
     a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel; a.g_rel2 = g->g_rel2;

@@ -62,6 +62,26 @@ __global__ void ids_to_keys_kernel(const void* ids, long long n, unsigned* keys)
     if (i < n) keys[i] = (unsigned)load_id<I>(ids, i);
 }
 
+// Range check with an optional sanitised copy (ids outside [0, limit) become 0).
+template <typename I>
+__global__ void validate_ids_kernel(const void* ids, long long n, long long limit, void* out, int32_t* err) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    long long v = static_cast<long long>(reinterpret_cast<const I*>(ids)[i]);
+    if (v < 0 || v >= limit) { atomicOr(err, KGE_ERR_ID_RANGE); v = 0; }
+    if (out) reinterpret_cast<I*>(out)[i] = static_cast<I>(v);
+}
+int launch_validate_ids(const void* ids, int id_bits, long long n, long long limit, void* out, cudaStream_t s) {
+    if (n <= 0) return 0;
+    int32_t* err = device_error_word();
+    if (!err) { set_error("no device error word"); return KGE_E_DEVICE; }
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (id_bits == 64) validate_ids_kernel<int64_t><<<blocks, 256, 0, s>>>(ids, n, limit, out, err);
+    else validate_ids_kernel<int32_t><<<blocks, 256, 0, s>>>(ids, n, limit, out, err);
+    KGE_LAUNCH_CHECK("validate_ids_kernel");
+    return 0;
+}
+
 __global__ void __launch_bounds__(RS_THREADS) radix_hist_kernel(const unsigned* keys, long long n, int shift, int ipt,
                                                                 unsigned* hist, int nblocks) {
     __shared__ unsigned h[256];

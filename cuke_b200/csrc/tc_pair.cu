@@ -624,7 +624,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     if (p.group_k) { kbase = tt.x; nkb = tt.y / bk; m0 = tt.z; b = 0; } else { m0 = tt.x; b = tt.y; }
                 }
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
                     umma::mbar_expect_tx(&full[s], tx_bytes);
@@ -679,12 +679,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
                 const int buf = lt & 1;
                 const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }   // drained?
+                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }   // drained?
                 umma::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * acc_cols;
                 const int nkb = (p.tile_tab && p.group_k) ? p.tile_tab[tile].y / bk : num_kb;
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
+                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }
                     umma::tc_fence_after();
                     const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;     // start address field
                     uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
@@ -735,7 +735,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 ok = *epi_fail == 0u;
             }
-            if (!ok) { if (lane == 0) atomicOr(p.err, 2); break; }
+            if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
             epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
@@ -814,7 +814,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 const int b_slabs = hn / slab_cols;
                 const uint32_t tx_pair = 2u * n_parts * (UM_A_BYTES + (p.b_slabs4d ? b_bytes : p.b_mn ? b_slabs * slab_bytes : hn * 128));
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }
                     uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st, *a_lo = st + UM_A_BYTES, *b_hi = st + n_parts * UM_A_BYTES, *b_lo = b_hi + b_bytes;
                     const uint32_t lead_full = umma::map_to_cta(umma::smem_u32(&full[s]), 0);
@@ -849,7 +849,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             // tail: every commit aimed at this CTA's `empty` barriers has landed before the CTA may exit
             for (int i = 0; i < p.stages && ok; ++i) {
-                if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, 2); ok = false; }
+                if (!umma::mbar_wait(&empty[s], ph ^ 1)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; }
                 if (++s == p.stages) { s = 0; ph ^= 1; }
             }
         }
@@ -873,11 +873,11 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                 const uint32_t idesc = umma::instr_desc(f16 ? 1u : 2u, 2 * UM_BM, (uint32_t)bnt, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
                 const int buf = lt & 1;
                 const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, 2); ok = false; break; }
+                if (!umma::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }
                 umma::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * acc_cols;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, 2); ok = false; break; }
+                    if (!umma::mbar_wait(&full[s], ph)) { atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); ok = false; break; }
                     umma::tc_fence_after();
                     const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;
                     uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
@@ -921,7 +921,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const int bnt = p.b_mn ? min(p.bn, (p.n_cols - n0 + unit - 1) / unit * unit) : p.bn;
             const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, 2); break; }
+            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
             epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
                           umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank);
@@ -1617,6 +1617,21 @@ static int transr_tc(const ScoreArgs& a, bool backward, float* dproj, const int*
     const int wpb = 8;
     transr_reduce_tc_kernel<<<(unsigned)((a.batch + wpb - 1) / wpb), wpb * 32, 0, s>>>(a, gv, gd0, trow0);
     KGE_LAUNCH_CHECK("transr_reduce_tc_kernel");
+    return 0;
+}
+
+// One warp, one barrier that nobody completes: the bounded wait runs out after `polls` polls and the kernel leaves normally.
+__global__ void wait_timeout_selftest_kernel(int polls, int32_t* err) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { umma::mbar_init(&bar, 1); umma::fence_barrier_init(); }
+    __syncwarp();
+    if (threadIdx.x == 0 && !umma::mbar_wait(&bar, 0, (uint32_t)polls)) atomicOr(err, KGE_ERR_WAIT_TIMEOUT);
+}
+int launch_wait_timeout_selftest(int polls, cudaStream_t s) {
+    int32_t* err = device_error_word();
+    if (!err) { set_error("no device error word"); return KGE_E_DEVICE; }
+    wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(polls, err);
+    KGE_LAUNCH_CHECK("wait_timeout_selftest_kernel");
     return 0;
 }
 

@@ -36,8 +36,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait; false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -192,3 +192,69 @@ class KgeStep:
             if wait:
                 out.wait()
         return out
+
+
+def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d: int = 64, chunk: int = 256, n_neg: int = 160,
+                      n_chunks: int = 2, n_ent: int = 5003, n_rel: int = 13) -> dict:
+    """Row-partitioned step against the same step on one GPU, on a small seeded problem (GPU against GPU; no CPU code).
+
+    Every rank scores its own batch against its shard of the table; rank 0 then recomputes all ranks' batches with the
+    whole table and compares: each rank's losses must be bit-equal (same kernels, same operand values, same order), the
+    summed entity / relation gradients must agree to 1e-5 (the owner-side sum adds the ranks' contributions in another
+    order than a single GPU would) and every rank must return gradients of rows it owns only.  Collective: call it on
+    every rank of `group`.  Returns {"ok", "world", "precision", "loss_bit_equal", "max_entity_err", "max_relation_err"}
+    on rank 0 and {"ok": None} elsewhere."""
+    import numpy as np
+    import torch.distributed as dist
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = np.random.Generator(np.random.PCG64(77))
+    E = (g.standard_normal((n_ent, d)) / np.sqrt(d)).astype(np.float32)
+    models = ["TransE", "DistMult"]
+    rel = {m: torch.from_numpy((g.standard_normal((n_rel, d)) / np.sqrt(d)).astype(np.float32)).to(dev) for m in models}
+    w = np.arange(1, n_ent + 1, dtype=np.float64) ** -1.1
+    B = chunk * n_chunks
+
+    def batch(rk):
+        gi = np.random.Generator(np.random.PCG64(1000 + rk))
+        ids = lambda size: torch.from_numpy(gi.choice(n_ent, size=size, p=w / w.sum()).astype(np.int64)).to(dev)
+        return ids(B), torch.from_numpy(gi.integers(0, n_rel, B)).to(dev), ids(B), ids((n_chunks, n_neg))
+
+    rpr = (n_ent + world - 1) // world
+    local = torch.from_numpy(E[rank * rpr: min(n_ent, (rank + 1) * rpr)]).to(dev).contiguous()
+    step = KgeStep(models, local, rel, n_ent, "chunk_shared", 0, chunk, rank, world, group, precision=precision)
+    out = step.step(*batch(rank))
+    k = int(out.n_ent_rows.item())
+    mine = {m: (out.ent_ids[:k].cpu(), out.ent_grad[m][:k].cpu(), out.rel_grad[m].cpu(), out.loss[m].cpu()) for m in models}
+    gathered = [None] * world
+    if world > 1:
+        dist.all_gather_object(gathered, mine, group=group)
+    else:
+        gathered = [mine]
+    res = {"ok": None}
+    if rank == 0:
+        full = KgeStep(models, torch.from_numpy(E).to(dev), rel, n_ent, "chunk_shared", 0, chunk, precision=precision)
+        dense = {m: torch.zeros((n_ent, d), dtype=torch.float64) for m in models}
+        drel = {m: torch.zeros((n_rel, d), dtype=torch.float64) for m in models}
+        loss_equal, owned = True, True
+        for rk in range(world):
+            o = full.step(*batch(rk))
+            u = int(o.n_ent_rows.item())
+            for m in models:
+                dense[m][o.ent_ids[:u].cpu()] += o.ent_grad[m][:u].double().cpu()
+                drel[m] += o.rel_grad[m].double().cpu()
+                loss_equal = loss_equal and bool(torch.equal(o.loss[m].cpu(), gathered[rk][m][3]))
+        err = rerr = 0.0
+        for m in models:
+            got = torch.zeros((n_ent, d), dtype=torch.float64)
+            for rk in range(world):
+                ids, rows, _, _ = gathered[rk][m]
+                owned = owned and bool(torch.all((ids >= rk * rpr) & (ids < (rk + 1) * rpr)))
+                got[ids] += rows.double()
+            err = max(err, float((got - dense[m]).abs().max() / dense[m].abs().max()))
+            rerr = max(rerr, float((gathered[0][m][2].double() - drel[m]).abs().max() / drel[m].abs().max()))
+        res = {"ok": bool(loss_equal and owned and err < 1e-5 and rerr < 1e-5), "world": world, "precision": precision,
+               "loss_bit_equal": loss_equal, "rows_owned_only": owned, "max_entity_err": err, "max_relation_err": rerr,
+               "case": f"TransE+DistMult, {B} triples/rank, {n_neg} shared negatives per {chunk}-chunk, dim {d}, {n_ent} rows"}
+    if world > 1:
+        dist.barrier(group=group)
+    return res

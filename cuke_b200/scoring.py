@@ -187,9 +187,25 @@ def owner_counts(insp: Inspection, rows_per_rank: int, world: int) -> torch.Tens
     return counts
 
 
+def validate_ids(ids: torch.Tensor, id_space: int, sanitized: Optional[torch.Tensor] = None) -> None:
+    """Range check of an id tensor (kge_validate_ids): ids outside [0, id_space) set ERR_ID_RANGE in the device error
+    word (read it with device_flags()); `sanitized` (same shape and dtype, may be `ids`) receives the ids with 0 in
+    place of the bad ones."""
+    _need_cuda(ids, sanitized)
+    if sanitized is not None and (sanitized.dtype != ids.dtype or sanitized.numel() != ids.numel()):
+        raise ValueError("sanitized must match ids in dtype and size")
+    check(_lib.lib().kge_validate_ids(_ptr(ids), _id_bits(ids), ids.numel(), int(id_space), _ptr(sanitized), _stream()))
+
+
+def selftest_wait_timeout(polls: int = 2048) -> None:
+    """Launches the library's wait self-test: a bounded wait that nothing completes runs out and reports ERR_WAIT_TIMEOUT."""
+    check(_lib.lib().kge_selftest_wait_timeout(int(polls), _stream()))
+
+
 def device_flags() -> int:
-    """Reads and clears the device error word (synchronises the current stream); 0 = clean, bit 2 = a bounded wait
-    inside a tensor-core kernel ran out and its outputs are invalid."""
+    """Reads and clears the device error word (synchronises the current stream); 0 = clean, else an OR of
+    _lib.ERR_WAIT_TIMEOUT (a bounded wait inside a tensor-core kernel ran out: its outputs are invalid) and
+    _lib.ERR_ID_RANGE (an id outside its table was met by a checked call)."""
     flags = C.c_int32(0)
     check(_lib.lib().kge_check(_stream(), C.byref(flags)))
     return int(flags.value)
@@ -233,10 +249,11 @@ class Scorer:
 
     def __init__(self, model: str, ent: torch.Tensor, rel: Optional[torch.Tensor] = None,
                  rel2: Optional[torch.Tensor] = None, neg_mode: str = "none", n_neg_head: int = 0, chunk: int = 0,
-                 precision: str = "fp32"):
+                 precision: str = "fp32", check_ids: bool = False):
         if model not in MODELS:
             raise KeyError(model)
         self.precision = PRECISIONS[precision]
+        self.flags = _lib.FLAG_CHECK_IDS if check_ids else 0     # ids are range-checked inside every scoring call
         _need_cuda(ent, rel, rel2)
         self.model, self.ent, self.rel, self.rel2 = model, ent, rel, rel2
         self.neg_mode, self.n_neg_head, self.chunk = neg_mode, int(n_neg_head), int(chunk)
@@ -246,7 +263,7 @@ class Scorer:
     def with_entities(self, ent: torch.Tensor) -> "Scorer":
         """Same scorer over another entity buffer (e.g. the compact staging buffer of distinct rows)."""
         sc = Scorer(self.model, ent, self.rel, self.rel2, self.neg_mode, self.n_neg_head, self.chunk)
-        sc.precision = self.precision
+        sc.precision, sc.flags = self.precision, self.flags
         return sc
 
     # -- struct plumbing
@@ -255,7 +272,7 @@ class Scorer:
         return KgeProblem(MODELS[self.model], DTYPES[_dtype_of(self.ent)], NEG_MODES[self.neg_mode if n_neg else "none"],
                           _id_bits(h), self.dim, n_neg, self.n_neg_head if n_neg else 0,
                           self.chunk if self.neg_mode == "chunk_shared" else 0, h.numel(), self.ent.shape[0], self.n_rel,
-                          self.precision, 0)
+                          self.precision, self.flags)
 
     def _tensors(self, h, r, t, neg, rel_insp: Optional[Inspection]) -> KgeTensors:
         kt = KgeTensors(_ptr(self.ent), _ptr(self.rel), _ptr(self.rel2), _ptr(h), _ptr(r), _ptr(t), _ptr(neg),
@@ -276,12 +293,22 @@ class Scorer:
         if neg is not None and self.neg_mode == "chunk_shared" and neg.shape[0] * self.chunk != h.shape[0]:
             raise ValueError("chunk_shared negatives must be (batch / chunk, n_neg)")
 
+    def _group_by_relation(self, r) -> Inspection:
+        """Inspector over the relation ids; with check_ids the grouping is built from the range-checked ids, because the
+        relation-matrix kernels address P[rel_uniq[g]] through it."""
+        if self.flags:
+            checked = torch.empty_like(r)
+            validate_ids(r, self.n_rel, checked)
+            r = checked
+        return inspect(r, self.n_rel)
+
     # -- reference-compatible output (what cuke's module.run returns)
     def ref_forward(self, h, r, t) -> torch.Tensor:
         self._check_ids(h, r, t, None)
         B = h.numel()
         out = torch.empty((B, self.dim) if self.model in VECTOR_MODELS else (B,), dtype=torch.float32, device=self.ent.device)
         p = self._problem(h, None)
+        p.reserved = 0
         kt = self._tensors(h, r, t, None, None)
         check(_lib.lib().kge_ref_forward(C.byref(p), C.byref(kt), _ptr(out), _stream()))
         return out
@@ -294,7 +321,7 @@ class Scorer:
         dev = self.ent.device
         p = self._problem(h, neg)
         if self.model in MATRIX_MODELS and rel_insp is None:
-            rel_insp = inspect(r, self.n_rel)
+            rel_insp = self._group_by_relation(r)
         kt = self._tensors(h, r, t, neg, rel_insp)
         pos = torch.empty(B, dtype=torch.float32, device=dev)
         negs = None
@@ -313,7 +340,7 @@ class Scorer:
         B, d, dev = h.numel(), self.dim, self.ent.device
         p = self._problem(h, neg)
         if self.model in MATRIX_MODELS and rel_insp is None:
-            rel_insp = inspect(r, self.n_rel)
+            rel_insp = self._group_by_relation(r)
         kt = self._tensors(h, r, t, neg, rel_insp)
         n_neg_ids = neg.numel() if p.n_neg else 0
         n_slots = 2 * B + n_neg_ids

@@ -19,7 +19,7 @@
  *     returns a thread-local, human-readable description of the last non-zero return.
  *   - Entity / relation ids are int64 (the reference's GPU convention, pycuke1/codegen/gpu.py:200-201)
  *     or int32 (`id_bits`).  Ids are trusted to lie inside the tables, exactly as in the reference
- *     (its generated kernels do no bounds checks either).
+ *     (its generated kernels do no bounds checks either), unless KGE_FLAG_CHECK_IDS / kge_validate_ids is used.
  *   - Relation matrices use the orientation of the reference's CPU path: for `'i,ij->j'`
  *     (apps/kge/kge.py:21-23) out[j] = sum_i x[i] * Proj[r][i][j].
  */
@@ -97,8 +97,16 @@ typedef struct kge_problem {
     int64_t n_ent;       /* rows of `ent` */
     int64_t n_rel;       /* rows of `rel` / `rel2` */
     int32_t precision;   /* enum kge_precision */
-    int32_t reserved;    /* must be 0 */
+    int32_t reserved;    /* flags: 0 or KGE_FLAG_CHECK_IDS */
 } kge_problem;
+
+/* kge_problem.reserved flag for kge_score_forward / kge_score_backward / kge_score_loss_backward: h, t, neg are checked
+ * against n_ent and r against n_rel before anything is gathered; an id outside sets KGE_ERR_ID_RANGE and row 0 is used
+ * in its place (that triple's outputs are meaningless, nothing outside the tables is touched).  Costs one pass over the
+ * ids and a copy of them in the workspace (kge_score_workspace_bytes accounts for it).  The rel_* grouping of the
+ * relation-matrix models is not re-checked: build it with kge_inspect over relation ids that went through
+ * kge_validate_ids. */
+#define KGE_FLAG_CHECK_IDS 1
 
 typedef struct kge_tensors {
     const void* ent;   /* (n_ent, dim) entity table, or a compact staging buffer addressed by slot ids */
@@ -134,9 +142,26 @@ KGE_API int kge_version(void);                 /* KGE_ABI_VERSION of the loaded 
 KGE_API const char* kge_last_error(void);      /* thread-local message for the last non-zero return */
 KGE_API long long kge_launch_count(void);      /* kernels launched by this library in this process so far */
 
-/* Reads (and clears) the device error word of the current device: 0 = clean.  Synchronises `stream`.
- * Bit 2: a bounded wait inside a kernel ran out and the kernel gave up (its outputs are then invalid). */
+/* Values OR-ed into the device error word by kernels of this library. */
+#define KGE_ERR_WAIT_TIMEOUT 2  /* a bounded wait inside a kernel ran out and the kernel gave up: its outputs are invalid */
+#define KGE_ERR_ID_RANGE 8      /* an id outside its table was met by kge_validate_ids / a call with KGE_FLAG_CHECK_IDS */
+
+/* Reads (and clears) the device error word of the current device: 0 = clean, else an OR of KGE_ERR_*.
+ * Synchronises `stream`. */
 KGE_API int kge_check(kge_stream_t stream, int32_t* flags_out);
+
+/* Range check of an id array: every ids[i] outside [0, id_space) sets KGE_ERR_ID_RANGE in the device error word, and,
+ * if `sanitized` is not NULL, sanitized[i] (same width; may be `ids` itself) receives the id or 0 in its place, so
+ * that a later gather never touches memory outside the table.  The reference's generated kernels trust their ids
+ * (pycuke1/codegen/gpu.py:9-123 emits no bounds checks); this is the opt-in check for ids that come from outside. */
+KGE_API int kge_validate_ids(const void* ids, int32_t id_bits, int64_t n, int64_t id_space, void* sanitized,
+                             kge_stream_t stream);
+
+/* Self-test of the bounded waits used inside the tensor-core kernels: one warp waits on a shared-memory barrier that
+ * nothing ever completes, with a limit of `polls` polls (1..65536), gives up, sets KGE_ERR_WAIT_TIMEOUT and returns.
+ * Shows that a wait that runs out ends the kernel normally and is reported through kge_check.  No reference
+ * counterpart. */
+KGE_API int kge_selftest_wait_timeout(int32_t polls, kge_stream_t stream);
 
 /* ---- reference-compatible forward ---------------------------------------------------------------
  * Replaces `module.run(*args)` of the code the reference generates for apps/kge/kge.py:273-390

@@ -163,7 +163,8 @@ def compile_all(made):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CUKE_REFERENCE", os.path.join(HERE, "..", "..", "reference")),
+                    help="the cuke checkout (default: $CUKE_REFERENCE, else a directory `reference` beside this repository)")
     ap.add_argument("--only", default=",".join(SCORERS))
     ap.add_argument("--threads", type=int, default=256,
                     help="num_threads() written into the OpenMP pragma; OMP_NUM_THREADS / "

@@ -446,3 +446,76 @@ def test_argument_errors():
     sc = gpu_scorer(p, 0)
     with pytest.raises((KgeError, ValueError)):
         sc.forward(*gpu_ids(p))
+
+
+# ---- opt-in safety checks -----------------------------------------------------------------------------------------------
+def test_validate_ids_reports_and_sanitises():
+    from cuke_b200 import _lib, scoring
+    assert scoring.device_flags() == 0
+    ids = torch.tensor([0, 5, 9, 10, -1, 3, 1 << 40], dtype=torch.int64, device="cuda")
+    out = torch.full_like(ids, 77)
+    scoring.validate_ids(ids, 10, out)
+    assert scoring.device_flags() == _lib.ERR_ID_RANGE
+    assert out.tolist() == [0, 5, 9, 0, 0, 3, 0]
+    assert scoring.device_flags() == 0                       # reading clears the word
+    good = torch.arange(10, dtype=torch.int32, device="cuda")
+    scoring.validate_ids(good, 10)
+    assert scoring.device_flags() == 0
+
+
+@pytest.mark.parametrize("model,neg_mode", [("TransE", "per_triple"), ("DistMult", "chunk_shared"), ("TransR", "per_triple")])
+def test_checked_scoring_skips_ids_outside_the_tables(model, neg_mode):
+    """KGE_FLAG_CHECK_IDS: a call whose ids leave the tables reports it and reads row 0 instead; the other triples are
+    scored as usual, and a clean batch gives the unchecked result bit for bit."""
+    from cuke_b200 import _lib, scoring
+    from cuke_b200.scoring import Scorer
+    chunk = 16 if neg_mode == "chunk_shared" else 0
+    p = make_problem(model, seed=31, ne=200, nr=7, d=40, B=32, nn=8, neg_mode=neg_mode, chunk=chunk)
+    E, R, P2 = to_dev(p["E"]), to_dev(p["R"]), to_dev(p["P2"])
+    plain = Scorer(model, E, R, P2, neg_mode, 0, chunk)
+    checked = Scorer(model, E, R, P2, neg_mode, 0, chunk, check_ids=True)
+    h, r, t, neg = gpu_ids(p)
+    pos0, neg0, _ = plain.forward(h, r, t, neg)
+    pos1, neg1, _ = checked.forward(h, r, t, neg)
+    assert scoring.device_flags() == 0
+    assert torch.equal(pos0, pos1) and torch.equal(neg0, neg1)
+    hb, rb, nb = h.clone(), r.clone(), neg.clone()
+    hb[3] = 200                      # one past the entity table
+    rb[5] = -2                       # (TransR too: the scorer builds its relation grouping from the checked ids)
+    nb.view(-1)[11] = 1 << 33
+    pos2, neg2, rinsp = checked.forward(hb, rb, t, nb)
+    assert scoring.device_flags() == _lib.ERR_ID_RANGE
+    keep = torch.ones(32, dtype=torch.bool, device="cuda")
+    keep[3] = keep[5] = False
+    assert torch.equal(pos2[keep], pos0[keep])
+    # backward with the same bad ids: reported again, finite rows everywhere
+    loss, dpos, dneg = scoring.logistic_loss(pos2, neg2)
+    sg = checked.backward(hb, rb, t, nb, pos2, neg2, dpos, dneg, rinsp)
+    assert scoring.device_flags() == _lib.ERR_ID_RANGE
+    assert torch.isfinite(sg.ent_slots).all()
+
+
+def test_bounded_wait_runs_out_harmlessly():
+    """The waits inside the tensor-core kernels are bounded polls; when one runs out the kernel records it and leaves.
+    The library's self-test kernel waits on a barrier nothing completes: it must return and report, and the context
+    must stay usable."""
+    from cuke_b200 import _lib, scoring
+    assert scoring.device_flags() == 0
+    scoring.selftest_wait_timeout(2048)
+    assert scoring.device_flags() == _lib.ERR_WAIT_TIMEOUT
+    assert scoring.device_flags() == 0
+    x = torch.arange(8, device="cuda").sum().item()          # the context still works
+    assert x == 28
+    from cuke_b200._lib import KgeError
+    with pytest.raises(KgeError):
+        scoring.selftest_wait_timeout(0)
+
+
+def test_backward_with_rows_that_are_not_quads():
+    """dim % 4 != 0 takes the element-wise row path: gradient slices then only need 4-byte alignment (B * dim * 4 is
+    not a multiple of 16 here)."""
+    for model, mode in (("TransE", "per_triple"), ("DistMult", "none"), ("TransH", "per_triple")):
+        p = make_problem(model, seed=8, ne=60, d=37, B=21, nn=3, neg_mode=mode, zipf=True)
+        if mode == "none":
+            p["neg"] = None
+        _check_grads(p, 1 if mode == "per_triple" else 0, 0)

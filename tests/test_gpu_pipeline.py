@@ -23,14 +23,15 @@ def sigmoid(x):
     return 1.0 / (1.0 + np.exp(-x))
 
 
-@pytest.mark.parametrize("models", [["TransE", "DistMult"], ["ComplEx"]])
-def test_step_matches_oracle(models):
+@pytest.mark.parametrize("models,precision,chunk,nn", [(["TransE", "DistMult"], "tensor", 256, 160), (["ComplEx"], "tensor", 64, 96),
+                                                       (["TransE", "DistMult"], "fp32", 64, 96)])
+def test_step_matches_oracle(models, precision, chunk, nn):
     from cuke_b200.pipeline import KgeStep
-    ne, d, B, chunk, nn, nr = 3000, 64, 256, 64, 96, 17
+    ne, d, B, nr = 3000, 64, 2 * chunk if chunk > 64 else 256, 17
     p = make_problem(models[0], seed=41, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
     g = p["g"]
     rel = {m: (g.standard_normal((nr, d)) / np.sqrt(d)).astype(np.float32) for m in models}
-    step = KgeStep(models, to_dev(p["E"]), {m: to_dev(rel[m]) for m in models}, ne, "chunk_shared", 0, chunk)
+    step = KgeStep(models, to_dev(p["E"]), {m: to_dev(rel[m]) for m in models}, ne, "chunk_shared", 0, chunk, precision=precision)
     h, r, t, neg = (to_dev(p[k]) for k in ("h", "r", "t", "neg"))
     out = step.step(h, r, t, neg)
     out2 = step.step(h, r, t, neg)
