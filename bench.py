@@ -60,6 +60,8 @@ def parse():
     ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor"],
                     help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
+    ap.add_argument("--no-optimizer", action="store_true", help="return gradients only (no sparse SGD update in the step)")
+    ap.add_argument("--no-prefetch", action="store_true", help="inspect every batch inside its own step")
     ap.add_argument("--no-side", action="store_true", help="skip the c1-c4 side measurements appended to the c5 line")
     return ap.parse_args()
 
@@ -233,7 +235,10 @@ def workload_config(cfg, models, n_gpus):
                         f"per {cfg.chunk}-triple chunk, Zipf(1.1) entity ids",
             "scorers": models, "triples_per_gpu": cfg.batch, "neg_mode": cfg.neg_mode, "n_neg": cfg.n_neg, "chunk": cfg.chunk,
             "dim": cfg.dim, "n_ent": cfg.n_ent, "n_rel": cfg.n_rel, "parallelism": f"dp{n_gpus}+row-sharded-entities",
-            "pipelining": "N>1: the last gradient return of a step overlaps the next step's inspector; the timed region ends after the last return",
+            "step": "inspector, staging (row exchange), forward + logistic loss + backward, segmented gradient reduction (owner-side sum), "
+                    "sparse SGD update of the touched rows, for both scorers",
+            "pipelining": "the inspection of batch i+1 (N>1: and its id exchange) runs on a side stream during step i; "
+                          "the timed region ends after the last update",
             "l2": "inputs larger than L2 (6.4 GB table, 76 MB staged rows, 2 x 268 MB of split gradient weights per scorer; "
                   "the 268 MB score matrix is consumed inside the tile kernel); no flush"}
 
@@ -271,7 +276,7 @@ def side_measure(cname, steps, warmup, precision, cpu_seconds=0.0):
                 loss, dpos, dneg = scoring.logistic_loss(pos, negs)
                 sg = sc.backward(h, r, t, neg, pos, negs, dpos, dneg, rinsp)
                 insp = scoring.inspect(ids, cfg.n_ent)
-                scoring.segment_reduce(sg.ent_slots, insp)
+                scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)
             return pos
 
         def timed(cold, bwd=True):
@@ -363,7 +368,7 @@ def parity_single_gpu(cfg, models, stepper, ent_local, rel, devb, dev):
     h, r, t, neg = devb[0]
     c, nn = cfg.chunk, cfg.n_neg
     hs, rs, ts, ns = h[:c].contiguous(), r[:c].contiguous(), t[:c].contiguous(), neg[:1].contiguous()
-    out = stepper.step(hs, rs, ts, ns)
+    out = stepper.step(hs, rs, ts, ns, update=False)
     U = int(out.n_ent_rows.item())
     ids = out.ent_ids[:U]
     E = ent_local[ids].cpu().numpy()                               # rows of the distinct ids, ascending
@@ -438,8 +443,10 @@ def main():
     for mi, m in enumerate(models):
         g = np.random.Generator(np.random.PCG64(synth.BASE_SEED + 1000 * cfg.cid + 2 + mi))
         rel[m] = torch.from_numpy((g.standard_normal((cfg.n_rel, d)) / np.sqrt(d)).astype(np.float32)).to(dev)
+    # a training step: sparse SGD on the rows the step touched (entity rows at their owner, relation tables everywhere)
+    optimizer = None if args.no_optimizer else ("sgd", 1e-3)
     stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group,
-                      precision=args.precision)
+                      precision=args.precision, optimizer=optimizer)
 
     nb = 4
     host = []
@@ -490,26 +497,38 @@ def main():
     # N GPUs: the last scorer's gradient return of step i may overlap the inspector of step i+1 (wait=False); the last
     # timed step waits for its own return, so the timed region covers all the work of its K steps
     w_main = max(args.warmup, 3)
-    ms_step = timed(lambda i: stepper.step(*devb[i % nb], wait=(i == w_main + args.steps - 1)), args.steps, w_main)
+    # the next batch's inspection (N GPUs: and its id exchange) is queued on a side stream while a step computes
+    nxt = (lambda i: devb[(i + 1) % nb]) if not args.no_prefetch else (lambda i: None)
+    ms_step = timed(lambda i: stepper.step(*devb[i % nb], wait=(i == w_main + args.steps - 1), prefetch=nxt(i)), args.steps, w_main)
     launches = (_lib.lib().kge_launch_count() - launches0) // (args.steps + max(args.warmup, 3))
     value = scored_per_gpu * world / (ms_step * 1e-3)
     # the same K-step region four more times: the spread of a 50-60 ms measurement
-    regions = [ms_step] + [timed(lambda i: stepper.step(*devb[i % nb], wait=(i == args.steps - 1)), args.steps, 0) for _ in range(4)]
+    regions = [ms_step] + [timed(lambda i: stepper.step(*devb[i % nb], wait=(i == args.steps - 1), prefetch=nxt(i)), args.steps, 0)
+                           for _ in range(4)]
     clocks = sampler.stop() if rank == 0 else None
     spread = {"regions": len(regions), "steps_each": args.steps, "ms_per_step_median": statistics.median(regions),
               "ms_per_step_min": min(regions), "ms_per_step_max": max(regions),
               "note": "`value` and `ms_per_step` are the first region (W warm-up steps, then exactly K timed steps)"}
 
-    ms_fwd = timed(lambda i: stepper.step(*devb[i % nb], backward=False), max(3, args.steps // 2), 2)
+    ms_fwd = timed(lambda i: stepper.step(*devb[i % nb], backward=False, prefetch=nxt(i)), max(3, args.steps // 2), 2)
 
     # ---- e2e: host ids in, losses out, every step --------------------------------------------------------------
     sink = []
 
+    uploaded = {}
+
+    def upload(i):          # pinned host ids -> device, once per step, inside the timed region
+        if i not in uploaded:
+            uploaded[i] = tuple(x.to(dev, non_blocking=True) for x in host[i % nb])
+        return uploaded[i]
+
     def e2e_step(i):
-        b = tuple(x.to(dev, non_blocking=True) for x in host[i % nb])
-        out = stepper.step(*b, wait=(i == 2 + args.steps - 1))
+        b = upload(i)
+        ahead = None if args.no_prefetch else upload(i + 1)        # the next step's ids travel while this step computes
+        out = stepper.step(*b, wait=(i == 2 + args.steps - 1), prefetch=ahead)
         res = torch.cat([out.loss[m] for m in models]).cpu()       # device -> host read of the step's result
         sink.append(float(res.sum()))
+        uploaded.pop(i, None)
 
     ms_e2e = timed(e2e_step, args.steps, 2)
     e2e = {"value": scored_per_gpu * world / (ms_e2e * 1e-3), "unit": "triples/s", "h2d_bytes_per_step": h2d_bytes,

@@ -79,6 +79,11 @@ SIGNATURES = {
     "kge_score_loss_backward": (C.c_int, [_PP, _PT, _f32, _vp, _vp, _PG, _vp, _sz, _vp]),
     "kge_logistic_loss": (C.c_int, [_vp, _i64, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _sz, _vp]),
     "kge_owner_counts": (C.c_int, [_vp, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "kge_sample_uniform": (C.c_int, [_vp, _i32, _i64, _i64, C.c_uint64, C.c_uint32, _vp]),
+    "kge_sample_cdf": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _i64, C.c_uint64, C.c_uint32, _vp]),
+    "kge_sample_triples": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _vp, _i64, C.c_uint64, C.c_uint32, _vp]),
+    "kge_apply_sgd": (C.c_int, [_vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _f32, _vp]),
+    "kge_apply_adagrad": (C.c_int, [_vp, _i32, _vp, _i32, _vp, _i64, _vp, _i64, _vp, _f32, _f32, _vp]),
 }
 
 

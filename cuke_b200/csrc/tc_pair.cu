@@ -286,6 +286,11 @@ constexpr int UM_EPI_WARPS = 8;
 // chunk goes through a 32x32 XOR-swizzled shared-memory staging square (conflict-free both ways) and comes back with
 // lane = COLUMN: global loads and stores are then 128-byte row segments, per-column operands are one register per lane,
 // per-row operands one shuffle per row, and the fix-up test is a mask bit instead of a branch per element.
+// GROUP selects which epilogues an instantiation carries: G_DENSE the dense chunk-shared products (store, distance, rank-1,
+// fused loss), G_GROUPED the relation-grouped products (store, norm, dL/dv rows, scatter).  Two instantiations keep the
+// register allocation of each set independent of the other's code.
+enum { G_DENSE = 0, G_GROUPED = 1 };
+template <int GROUP>
 __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
                                               int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot) {
     const int q = warp & 3;
@@ -295,7 +300,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     const int m = m0 + row;
     const bool row_ok = m < p.m_rows;
     const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
-    if (p.ep == EP_NORM) {
+    if (GROUP == G_GROUPED && p.ep == EP_NORM) {
         // squared norm of (acc + R[z]) over the row: nothing is stored per element, the thread-per-row form is kept
         float* ssq_part = epi_smem;                // [2 accumulators][2 halves][128 rows]
         float ssq = 0.f;
@@ -336,9 +341,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     // per-row operands live in the lane that owns the row and are broadcast by shuffle
     float row_op = 0.f;
     if (row_ok) {
-        if (p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist)) row_op = p.sq_a[grow0 + lane];
-        else if (p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
-        else if (p.ep == EP_GV) row_op = p.coef[m];
+        if (GROUP == G_DENSE && (p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist))) row_op = p.sq_a[grow0 + lane];
+        else if (GROUP == G_DENSE && p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
+        else if (GROUP == G_GROUPED && p.ep == EP_GV) row_op = p.coef[m];
     }
     float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; this thread's (= row's) sum of W
 #pragma unroll 1
@@ -348,7 +353,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         const bool col_ok = lane < lim;
         const int col = nbase + lane;
         float y[32];
-        if (p.ep == EP_RANK1) {          // the y rows come from memory: requested before the accumulator is read
+        if (GROUP == G_DENSE && p.ep == EP_RANK1) {          // the y rows come from memory: requested before the accumulator is read
             const float* yh = p.y_hi + grow0 * p.y_ld + col;
             const float* yl = p.y_lo + grow0 * p.y_ld + col;
 #pragma unroll
@@ -363,7 +368,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 #pragma unroll
         for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
         __syncwarp();
-        if (p.ep == EP_LOSS) {
+        if (GROUP == G_DENSE && p.ep == EP_LOSS) {
             float* wh = p.w_hi + grow0 * p.ldw + col;
             float* wl = p.w_lo + grow0 * p.ldw + col;
             const bool pad_ok = col < p.ldw;         // pitch padding past the last column is written as zero
@@ -480,7 +485,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 }
             }
             loss_acc = fmaf(nw, lsum, loss_acc);
-        } else if (p.ep == EP_DIST) {
+        } else if (GROUP == G_DENSE && p.ep == EP_DIST) {
             const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
             uint32_t bad = 0;
@@ -501,7 +506,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                     if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow0 + r) * p.n_cols + col;
                 }
             }
-        } else if (p.ep == EP_RANK1) {
+        } else if (GROUP == G_DENSE && p.ep == EP_RANK1) {
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
@@ -509,7 +514,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 const float rs = __shfl_sync(0xffffffffu, row_op, r);
                 if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[r], -x);
             }
-        } else if (p.ep == EP_GV) {          // dL/dv rows for the backward products, stored as bf16
+        } else if (GROUP == G_GROUPED && p.ep == EP_GV) {          // dL/dv rows for the backward products, stored as bf16
             float rv = 0.f;
             if (col_ok) {
                 const long long ri = static_cast<long long>(b) * p.n_cols + col;
@@ -523,11 +528,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 const float cf = __shfl_sync(0xffffffffu, row_op, r);
                 if (col_ok) *go = __float2bfloat16_rn(cf * (x + rv));
             }
-        } else if (p.ep == EP_SCATTER) {     // gradient of the difference row: to the replaced row's slot (signed) or to GD0
+        } else if (GROUP == G_GROUPED && p.ep == EP_SCATTER) {     // gradient of the difference row: to the replaced row's slot (signed) or to GD0
+            // lane r holds the destination of row r: one coalesced load per chunk instead of a dependent load per row
+            const long long dst_lane = lane < rows_here ? p.row_dst[mq + lane] : -1;
 #pragma unroll 4
             for (int r = 0; r < rows_here; ++r) {
                 const float x = stg[r * 32 + (lane ^ r)];
-                const long long dst = p.row_dst[mq + r];          // same address in every lane: one broadcast load
+                const long long dst = __shfl_sync(0xffffffffu, dst_lane, r);
                 if (dst == -1 || !col_ok) continue;
                 if (dst >= kTailSide) p.neg_out[(dst - kTailSide) * p.n_cols + col] = -x;
                 else if (dst >= 0) p.neg_out[dst * p.n_cols + col] = x;
@@ -547,7 +554,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     umma::tc_fence_before();
     __syncwarp();
     if (lane == 0) umma::mbar_arrive_cluster(drained);
-    if (p.ep == EP_LOSS) {
+    if (GROUP == G_DENSE && p.ep == EP_LOSS) {
         const long long total_rows = static_cast<long long>(p.batch) * p.m_rows;
         if (row_ok && p.loss_dist) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
         const float l = warp_sum(loss_acc);
@@ -558,6 +565,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 // Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
 // working at the same time share A rows in L2).  Two accumulators in tensor memory alternate, so the epilogue of tile i
 // (tcgen05.ld, scorer epilogue, global stores) overlaps the TMA/MMA main loop of tile i+1.
+template <int GROUP>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
@@ -673,6 +681,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
             const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
             const bool single = p.passes == 1;
+            const int kstep_elems = 32 / p.elem_bytes;      // k-values per MMA step
             int s = 0; uint32_t ph = 0;
             int lt = 0;                            // tiles done by this CTA
             bool ok = true;
@@ -688,23 +697,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     umma::tc_fence_after();
                     const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;     // start address field
                     uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
+                    // a stage holds four MMA steps of K (32 bytes each); the last k-block of a product only issues the
+                    // steps that hold data (the rest of the stage is the zero fill of the TMA box)
+                    const int ksteps = p.group_k ? 4 : min(4, (p.k_len - kb * bk + kstep_elems - 1) / kstep_elems);
                     if (single) {
                         if (f16) {
 #pragma unroll
                             for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
-                                umma::mma_f16(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                if (k8 < ksteps) umma::mma_f16(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
                         } else {
 #pragma unroll
                             for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
-                                umma::mma_tf32(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                if (k8 < ksteps) umma::mma_tf32(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
                         }
                     } else {
                         uint64_t dal = a_tmpl | (st + a_lo_off), dbl = b_tmpl | (st + b_lo_off);
 #pragma unroll
                         for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
-                            umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                            umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
-                            umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                            if (k8 < ksteps) {
+                                umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
+                                umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+                                umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                            }
                         }
                     }
                     umma::mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
@@ -729,7 +743,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             bool ok = umma::mbar_wait(&acc_full[buf], aph);                                           // warp-uniform result
-            if (p.ep == EP_NORM) {
+            if (GROUP == G_GROUPED && p.ep == EP_NORM) {
                 // the eight epilogue warps meet at a named barrier inside this epilogue: they give up together or not at all
                 if (!ok && lane == 0) *epi_fail = 1u;
                 asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -737,7 +751,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
-            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
+            epilogue_tile<GROUP>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
     umma::tc_fence_before();
@@ -864,6 +878,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
             const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
             const bool single = p.passes == 1;
+            const int kstep_elems = 32 / p.elem_bytes;
             int s = 0; uint32_t ph = 0;
             int lt = 0;
             bool ok = true;
@@ -881,23 +896,26 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                     umma::tc_fence_after();
                     const uint32_t st = (umma::smem_u32(smem + s * stage_bytes) & 0x3FFFFu) >> 4;
                     uint64_t dah = a_tmpl | st, dbh = b_tmpl | (st + b_hi_off);
+                    const int ksteps = min(4, (p.k_len - kb * bk + kstep_elems - 1) / kstep_elems);     // steps of this stage that hold data
                     if (single) {
                         if (f16) {
 #pragma unroll
                             for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
-                                umma::mma_f16_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                if (k8 < ksteps) umma::mma_f16_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
                         } else {
 #pragma unroll
                             for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step)
-                                umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                if (k8 < ksteps) umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
                         }
                     } else {
                         uint64_t dal = a_tmpl | (st + a_lo_off), dbl = b_tmpl | (st + b_lo_off);
 #pragma unroll
                         for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
-                            umma::mma_tf32_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                            umma::mma_tf32_pair(tmem_d, dah, dbl, idesc, 1u);
-                            umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, 1u);
+                            if (k8 < ksteps) {
+                                umma::mma_tf32_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
+                                umma::mma_tf32_pair(tmem_d, dah, dbl, idesc, 1u);
+                                umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, 1u);
+                            }
                         }
                     }
                     const uint32_t e0 = umma::smem_u32(&empty[s]);
@@ -923,7 +941,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
-            epilogue_tile(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
+            epilogue_tile<G_DENSE>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
                           umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank);
         }
     }
@@ -1110,7 +1128,8 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     // the shared-memory opt-in is a per-device attribute of the kernel: remembered per device ordinal
     static std::atomic<bool> attr_set[128];
     if (dev < 0 || dev >= 128 || !attr_set[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<G_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_gemm_kernel<G_GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
         if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(tile kernels)");
         if (dev >= 0 && dev < 128) attr_set[dev].store(true, std::memory_order_release);
@@ -1142,7 +1161,8 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
         umma_pair_kernel<<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_pair_kernel");
     } else {
-        umma_gemm_kernel<<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        if (p.tile_tab) umma_gemm_kernel<G_GROUPED><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        else umma_gemm_kernel<G_DENSE><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_gemm_kernel");
     }
     if (prof) {
@@ -1500,25 +1520,43 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
 }
 
 // Per triple: g_head = GD0 - sum of its tail-replaced g_neg rows, g_tail = -GD0 - sum of its head-replaced g_neg rows,
-// g_rel = sum of its dL/dv rows (bf16, consecutive in the packed order), all in ascending j.
+// g_rel = sum of its dL/dv rows (bf16, consecutive in the packed order), all in ascending j.  One warp per triple, lane L
+// owns quads L and L + 32 of a row (dim <= 256); four rows are requested before the first is added.
 __global__ void __launch_bounds__(256) transr_reduce_tc_kernel(ScoreArgs a, const __nv_bfloat16* gv, const float* gd0, const int* trow0) {
     const int lane = threadIdx.x & 31;
     const long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (i >= a.batch) return;
     const int dim = a.dim, n_neg = a.n_neg;
     const long long r0 = trow0[i];
-    for (int k = lane; k < dim; k += 32) {
-        const float g0 = gd0[i * dim + k];
-        float gh = g0, gt = -g0, gr = __bfloat162float(gv[r0 * dim + k]);
-        for (int j = 0; j < n_neg; ++j) {
-            const float gx = a.g_neg[(i * n_neg + j) * dim + k];
-            if (j < a.n_neg_head) gt -= gx; else gh -= gx;
-            gr += __bfloat162float(gv[(r0 + 1 + j) * dim + k]);
+    Row<2> g0, gh, gt, gr;
+    load_row_f32<2, true>(g0, gd0 + i * dim, dim, lane);
+    load_row<__nv_bfloat16, 2, true>(gr, gv + r0 * dim, dim, lane);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) { gh.v[q] = g0.v[q]; gt.v[q] = -1.f * g0.v[q]; }
+    for (int j0 = 0; j0 < n_neg; j0 += 4) {
+        Row<2> gx[4], gvr[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (j0 + u < n_neg) {
+                load_row_f32<2, true>(gx[u], a.g_neg + (i * n_neg + j0 + u) * dim, dim, lane);
+                load_row<__nv_bfloat16, 2, true>(gvr[u], gv + (r0 + 1 + j0 + u) * dim, dim, lane);
+            }
         }
-        a.g_head[i * dim + k] = gh;
-        a.g_tail[i * dim + k] = gt;
-        a.g_rel[i * dim + k] = gr;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (j0 + u < n_neg) {
+                const bool head_side = j0 + u < a.n_neg_head;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    if (head_side) gt.v[q] = gt.v[q] - gx[u].v[q]; else gh.v[q] = gh.v[q] - gx[u].v[q];
+                    gr.v[q] = gr.v[q] + gvr[u].v[q];
+                }
+            }
+        }
     }
+    store_row<2, true>(a.g_head + i * dim, gh, dim, lane);
+    store_row<2, true>(a.g_tail + i * dim, gt, dim, lane);
+    store_row<2, true>(a.g_rel + i * dim, gr, dim, lane);
 }
 
 struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, off_tab2, off_coef, off_trow0, off_gv, off_gd0, total;

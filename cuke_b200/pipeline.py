@@ -1,7 +1,8 @@
-"""One forward+backward step of the KGE scorers over a (possibly row-partitioned) entity table.
+"""One training step of the KGE scorers over a (possibly row-partitioned) entity table.
 
 Inspector-executor per step and rank:
   1. inspector over the batch's entity ids [h | t | neg]  -> sorted distinct ids, inverse map, segments
+     (and over r -> relation grouping)
   2. stage every distinct row once into a compact buffer:
         1 GPU : gather from the local table
         N GPUs: the table is row-partitioned (owner = id // rows_per_rank); distinct ids are already sorted, so
@@ -11,19 +12,43 @@ Inspector-executor per step and rank:
   4. segmented reduction: per-slot gradient rows -> one row per distinct id (fixed order, no atomics)
   5. N GPUs: gradient rows travel back to their owners (all-to-all), who sum the contributions of all ranks
      with the same inspector + segmented reduction (the "reduce-scatter"); relation gradients are all-reduced.
+  6. optional sparse optimizer (SGD / Adagrad) on exactly the rows the step touched.
 
-The reference has no counterpart of steps 2 and 5 (single GPU, `cuda:0`, apps/kge/data/data_init.py:6-15) and
-only the relation half of step 1 (apps/kge/kge.py:249-271).
+Steps 1 and the id half of 2 depend on the ids only, not on the tables: `step(..., prefetch=next_batch)` runs them for
+the NEXT batch on a side stream (and its own communicator) while this step computes, so the next step starts at the
+row exchange and never waits for the host to read split sizes.
+
+The reference has no counterpart of steps 2, 5 and 6 (single GPU, `cuda:0`, apps/kge/data/data_init.py:6-15; its
+backward_* functions stop at per-triple pieces, apps/kge/kge.py:393-515) and only the relation half of step 1
+(apps/kge/kge.py:249-271).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from . import scoring
+from ._lib import MATRIX_MODELS
 from .scoring import Inspection, Scorer
+
+
+@dataclass
+class StepPlan:
+    """Everything about a batch that depends on its ids only."""
+    batch: Tuple[torch.Tensor, ...]            # (h, r, t, neg) as given (kept alive: the plan is matched by identity)
+    ids: torch.Tensor                          # [h | t | neg]
+    insp: Inspection                           # over ids
+    r32: torch.Tensor                          # relation ids as int32
+    rinsp: Inspection                          # over r32
+    need: Optional[List[int]] = None           # N GPUs: distinct ids I need from each owner
+    serve: Optional[List[int]] = None          #         ids each rank needs from me
+    req_ids: Optional[torch.Tensor] = None     #         the ids I serve, grouped by requesting rank
+    owner_insp: Optional[Inspection] = None    #         inspection of req_ids (the owner-side sum of returned gradients)
+    ready: Optional[torch.cuda.Event] = None   # N GPUs: recorded after the copy of the split sizes to the host
+    counts_host: Optional[torch.Tensor] = None   # pinned (2, world) int64: need / serve, valid once `ready` has passed
+    done: Optional[torch.cuda.Event] = None    # prefetched plans: recorded on the side stream after their last kernel
 
 
 class RowExchange:
@@ -33,39 +58,70 @@ class RowExchange:
     cuke_b200.scoring (the CUDA kernels); tests drive the same protocol on CPU ranks over gloo with a
     numpy stand-in, which is how the multi-rank bookkeeping is checked without GPUs."""
 
-    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None, ops=scoring):
+    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None, ops=scoring, plan_group=None):
         self.ent_local, self.n_ent, self.rank, self.world, self.group, self.ops = ent_local, int(n_ent), rank, world, group, ops
+        self.plan_group = plan_group if plan_group is not None else group       # communicator of the id-only collectives
         self.rows_per_rank = (self.n_ent + world - 1) // world
         self.dim = ent_local.shape[1]
         self.need = self.serve = None
         self.req_ids = None
         self.owner_insp = None        # inspection of the ids this rank serves, shared by every gradient return of a step
 
-    def stage(self, insp: Inspection) -> torch.Tensor:
-        """Compact buffer holding row uniq[u] of the global table at position u (u < U)."""
+    # -- id half: depends on the batch's ids only ------------------------------------------------------------------
+    def plan_counts(self, insp: Inspection):
+        """Queues the count exchange; returns a (2, world) int64 host tensor (pinned on CUDA) holding need / serve once the
+        current stream has passed this point."""
         import torch.distributed as dist
-        dev = self.ent_local.device
         counts = self.ops.owner_counts(insp, self.rows_per_rank, self.world)       # ids I need from each owner
         wanted = torch.empty_like(counts)                                           # ids each rank needs from me
-        dist.all_to_all_single(wanted, counts, group=self.group)
-        both = torch.stack((counts, wanted)).cpu()                                  # the one host read: split sizes
-        self.need, self.serve = both[0].tolist(), both[1].tolist()
+        dist.all_to_all_single(wanted, counts, group=self.plan_group)
+        both = torch.stack((counts, wanted))
+        if both.is_cuda:
+            host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
+            host.copy_(both, non_blocking=True)
+            return host
+        return both
+
+    def plan_ids(self, insp: Inspection, counts_host: torch.Tensor):
+        """With the split sizes on the host: the id exchange and the owner-side inspection.  Sets need / serve / req_ids."""
+        import torch.distributed as dist
+        dev = self.ent_local.device
+        self.need, self.serve = counts_host[0].tolist(), counts_host[1].tolist()
         U, S = sum(self.need), sum(self.serve)
         self.req_ids = torch.empty(max(S, 1), dtype=torch.int64, device=dev)
         dist.all_to_all_single(self.req_ids[:S], insp.uniq[:U], output_split_sizes=self.serve,
-                               input_split_sizes=self.need, group=self.group)
+                               input_split_sizes=self.need, group=self.plan_group)
+        self.owner_insp = self.ops.inspect(self.req_ids[:S], self.n_ent) if S else None
+
+    def adopt(self, need, serve, req_ids, owner_insp):
+        self.need, self.serve, self.req_ids, self.owner_insp = need, serve, req_ids, owner_insp
+
+    # -- row half: depends on the tables -------------------------------------------------------------------------------
+    def stage_rows(self, staged: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Owners gather the requested rows, all-to-all of rows.  Returns the compact buffer (row u = row uniq[u])."""
+        import torch.distributed as dist
+        dev = self.ent_local.device
+        U, S = sum(self.need), sum(self.serve)
         if S:
             send_rows = self.ops.gather_rows(self.ent_local, self.req_ids[:S], first_row=self.rank * self.rows_per_rank)
         else:
             send_rows = torch.empty((0, self.dim), dtype=self.ent_local.dtype, device=dev)
-        self.owner_insp = None
-        staged = torch.empty((max(U, 1), self.dim), dtype=self.ent_local.dtype, device=dev)
+        if staged is None or staged.shape[0] < max(U, 1):
+            staged = torch.empty((max(U, 1), self.dim), dtype=self.ent_local.dtype, device=dev)
         dist.all_to_all_single(staged[:U], send_rows, output_split_sizes=self.need, input_split_sizes=self.serve,
                                group=self.group)
         return staged
 
+    def stage(self, insp: Inspection) -> torch.Tensor:
+        """Whole staging in one call (id half, host read of the split sizes, row half)."""
+        host = self.plan_counts(insp)
+        if host.is_pinned():
+            torch.cuda.current_stream().synchronize()                                # the one host read: split sizes
+        self.plan_ids(insp, host)
+        return self.stage_rows()
+
     def return_grads(self, grad_rows: torch.Tensor):
-        """grad_rows[u] belongs to uniq[u] of the last stage().  Returns (ids, n_rows, rows): one summed gradient
+        """grad_rows[u] belongs to uniq[u] of the staged batch.  Returns (ids, n_rows, rows): one summed gradient
         row per distinct OWNED id that any rank touched; ids int64 sorted, first n_rows entries valid."""
         import torch.distributed as dist
         U, S = sum(self.need), sum(self.serve)
@@ -88,109 +144,262 @@ class StepOutput:
     n_ent_rows: Optional[torch.Tensor] = None    # (1,) int64 device
     ent_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n, dim) fp32 rows aligned with ent_ids
     rel_grad: Dict[str, torch.Tensor] = field(default_factory=dict)    # model -> (n_rel, dim) dense fp32
+    rel2_grad: Dict[str, torch.Tensor] = field(default_factory=dict)   # TransH: (n_rel, dim) dense; TransR / RESCAL: (groups, dim, dim)
+    rel2_ids: Optional[torch.Tensor] = None      # TransR / RESCAL: relation id of each group of rel2_grad (first n_rel2_groups valid)
+    n_rel2_groups: Optional[torch.Tensor] = None
     n_staged: Optional[torch.Tensor] = None      # (1,) distinct entity rows this rank touched
     done: Optional[torch.cuda.Event] = None      # N GPUs, step(..., wait=False): recorded after the last gradient return
 
     def wait(self) -> None:
         """Make the current stream wait until the entity / relation gradients of this step have arrived."""
-        if self.done is not None:
-            torch.cuda.current_stream().wait_event(self.done)
+        if self.done is None:
+            return
+        cur = torch.cuda.current_stream()
+        cur.wait_event(self.done)
+        # the travelling results were allocated on the side stream: tell the allocator that this stream reads them too
+        for x in [self.ent_ids, self.n_ent_rows] + list(self.ent_grad.values()) + list(self.rel_grad.values()) + list(self.rel2_grad.values()):
+            if x is not None and x.is_cuda:
+                x.record_stream(cur)
 
 
 class KgeStep:
-    """models: scorers sharing one entity table; rel: model -> relation table (n_rel, dim).
+    """models: scorers sharing one entity table; rel: model -> relation table (n_rel, dim) (absent for RESCAL);
+    rel2: model -> TransH normals (n_rel, dim) or TransR / RESCAL matrices (n_rel, dim, dim).
 
     ent_local holds rows [rank * rows_per_rank, ...) of the global (n_ent, dim) table (the whole table when
-    world == 1).  `group` is a torch.distributed process group (NCCL) when world > 1."""
+    world == 1).  `group` is a torch.distributed process group (NCCL) when world > 1; relation tables are replicated.
+    optimizer: None (gradients are returned, tables untouched), ("sgd", lr) or ("adagrad", lr, eps): applied to the touched
+    rows at their owner at the end of the step (each scorer's gradient as its own update)."""
 
     def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
                  neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None,
-                 precision: str = "fp32", fused: bool = True):
-        self.models, self.ent_local, self.rel = list(models), ent_local, rel
+                 precision: str = "fp32", fused: bool = True, rel2: Optional[Dict[str, torch.Tensor]] = None,
+                 optimizer: Optional[tuple] = None):
+        self.models, self.ent_local, self.rel, self.rel2 = list(models), ent_local, rel, rel2 or {}
         self.fused = fused                    # use the fused forward+loss+backward call where the scorer supports it
         self.n_ent, self.rank, self.world, self.group = int(n_ent), int(rank), int(world), group
         self.neg_mode, self.n_neg_head, self.chunk, self.precision = neg_mode, n_neg_head, chunk, precision
         self.dim = ent_local.shape[1]
-        self.n_rel = {m: rel[m].shape[0] for m in self.models}
+        self.n_rel = {m: (rel[m] if m in rel else self.rel2[m]).shape[0] for m in self.models}
+        if len(set(self.n_rel.values())) != 1:
+            raise ValueError("the scorers of a step share one relation id space")
         for m in self.models:
-            if m in ("TransH", "TransR", "RESCAL"):
-                raise NotImplementedError("KgeStep covers the vector-relation scorers (TransE, DistMult, ComplEx, TransF)")
-        self.exchange = RowExchange(ent_local, n_ent, rank, world, group) if world > 1 else None
-        # gradient rows travel home on a side stream while the next scorer computes
-        self.comm_stream = torch.cuda.Stream(device=ent_local.device) if world > 1 else None
+            if m in MATRIX_MODELS and world > 1:
+                raise NotImplementedError("relation-matrix scorers run on one GPU per table replica (their matrices are not all-reduced)")
+            if m in ("TransH", "TransR", "RESCAL") and m not in self.rel2:
+                raise ValueError(f"{m} needs rel2[{m!r}]")
+        self.optimizer = optimizer
+        self.state = {}
+        if optimizer is not None:
+            if optimizer[0] not in ("sgd", "adagrad"):
+                raise ValueError("optimizer is ('sgd', lr) or ('adagrad', lr, eps)")
+            if optimizer[0] == "adagrad":
+                z = lambda t: torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+                self.state = {"ent": z(ent_local), **{("rel", m): z(rel[m]) for m in rel}, **{("rel2", m): z(self.rel2[m]) for m in self.rel2}}
+        dev = ent_local.device
+        self.plan_group = None
+        if world > 1:
+            import torch.distributed as dist
+            self.plan_group = dist.new_group(backend="nccl") if group is not None and dist.get_backend(group) == "nccl" else group
+        self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group) if world > 1 else None
+        # gradient rows travel home on a side stream while the next scorer computes; plans of the next batch on another
+        self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+        self.plan_stream = torch.cuda.Stream(device=dev)
+        self._planned: Optional[StepPlan] = None
 
-    def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True,
-             wait: bool = True) -> StepOutput:
-        """One step.  With several GPUs and wait=False the call returns while the last scorer's gradient rows are still
-        travelling to their owners (side stream); `StepOutput.wait()` orders a consumer after them.  The next step's
-        inspector then overlaps that return; its staging exchange runs on the same side stream, i.e. after it."""
+    # -- the id-only part of a step ---------------------------------------------------------------------------------------
+    def _make_plan(self, h, r, t, neg, ids=None, finish: bool = True) -> StepPlan:
+        """Inspections of the batch (current stream).  N GPUs: also the count exchange; with finish=True the host then
+        reads the split sizes (a synchronisation of the current stream) and the id exchange follows."""
+        if ids is None:
+            ids = scoring.entity_id_list(h, t, neg)
+        insp = scoring.inspect(ids, self.n_ent)
+        r32 = r if r.dtype == torch.int32 else r.to(torch.int32)
+        rinsp = scoring.inspect(r32, self.n_rel[self.models[0]])
+        plan = StepPlan((h, r, t, neg), ids, insp, r32, rinsp)
+        if self.exchange is not None:
+            plan.counts_host = self.exchange.plan_counts(insp)
+            plan.ready = torch.cuda.Event()
+            plan.ready.record()
+            if finish:
+                self._finish_plan(plan)
+        return plan
+
+    def _finish_plan(self, plan: StepPlan) -> None:
+        """N GPUs: the host reads the split sizes, then the id exchange and the owner-side inspection are queued on the
+        current stream."""
+        if self.exchange is None or plan.need is not None:
+            return
+        plan.ready.synchronize()
+        self.exchange.plan_ids(plan.insp, plan.counts_host)
+        plan.need, plan.serve = self.exchange.need, self.exchange.serve
+        plan.req_ids, plan.owner_insp = self.exchange.req_ids, self.exchange.owner_insp
+
+    def prefetch(self, h, r, t, neg, ids=None) -> None:
+        """Queues the plan of a coming batch on the side stream.  The tensors must be the very objects later passed to
+        step().  N GPUs: the host read of the split sizes is left to finish_prefetch()."""
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)                                # the batch tensors were produced on the current stream
+        with torch.cuda.stream(self.plan_stream):
+            self.plan_stream.wait_event(ev)
+            plan = self._make_plan(h, r, t, neg, ids, finish=False)
+            plan.done = torch.cuda.Event()
+            plan.done.record(self.plan_stream)
+        self._planned = plan
+
+    def finish_prefetch(self) -> None:
+        """N GPUs: completes a queued plan (host read of its split sizes, then the id exchange on the side stream).  step()
+        calls it after launching its own work, when the device has long passed the few kernels the read waits for."""
+        plan = self._planned
+        if plan is None or self.exchange is None or plan.need is not None:
+            return
+        with torch.cuda.stream(self.plan_stream):
+            self._finish_plan(plan)
+            plan.done = torch.cuda.Event()
+            plan.done.record(self.plan_stream)
+
+    def _take_plan(self, h, r, t, neg, ids) -> StepPlan:
+        plan, self._planned = self._planned, None
+        if plan is None or not all(a is b for a, b in zip(plan.batch, (h, r, t, neg))):
+            plan = self._make_plan(h, r, t, neg, ids)
+            self._hold(plan, torch.cuda.current_stream())
+            return plan
+        self._planned = plan
+        self.finish_prefetch()
+        self._planned = None
+        main = torch.cuda.current_stream()
+        main.wait_event(plan.done)
+        self._hold(plan, main)
+        return plan
+
+    def _hold(self, plan: StepPlan, main) -> None:
+        """The plan's tensors are read on streams other than the one they were allocated on."""
+        held = [plan.ids, plan.r32, plan.req_ids]
+        for ins in (plan.insp, plan.rinsp, plan.owner_insp):
+            if ins is not None:
+                held += [ins.uniq, ins.inverse, ins.perm, ins.seg, ins.n_unique]
+        for x in held:
+            if x is not None and x.is_cuda:
+                x.record_stream(main)
+                if self.comm_stream is not None:
+                    x.record_stream(self.comm_stream)
+
+    # -- optimizer --------------------------------------------------------------------------------------------------------
+    def _apply(self, table: torch.Tensor, key, grad_rows: torch.Tensor, ids=None, n_dev=None, first_row: int = 0) -> None:
+        """table and grad_rows as 2-D (rows, width) views; ids None = row i."""
+        if self.optimizer[0] == "sgd":
+            scoring.apply_sgd(table, grad_rows, self.optimizer[1], ids, n_dev, first_row)
+        else:
+            eps = self.optimizer[2] if len(self.optimizer) > 2 else 1e-10
+            scoring.apply_adagrad(table, self.state[key].view(table.shape), grad_rows, self.optimizer[1], eps, ids, n_dev, first_row)
+
+    def _allreduce(self, dense: torch.Tensor, main) -> None:
+        """N GPUs: sum of a replicated table's dense gradient over the ranks, on the side stream."""
+        if self.exchange is None:
+            return
         import torch.distributed as dist
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            dense.record_stream(self.comm_stream)
+            dist.all_reduce(dense, group=self.group)
+
+    def _update(self, table, key, rows, ids=None, n_dev=None, first_row: int = 0) -> None:
+        """Applies one gradient on the stream where it became ready (the side stream when it travelled)."""
+        if self.exchange is not None:
+            with torch.cuda.stream(self.comm_stream):
+                self._apply(table, key, rows, ids, n_dev, first_row)
+        else:
+            self._apply(table, key, rows, ids, n_dev, first_row)
+
+    # -- the step ---------------------------------------------------------------------------------------------------------
+    def step(self, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, neg: torch.Tensor, backward: bool = True,
+             wait: bool = True, ids: Optional[torch.Tensor] = None, prefetch: Optional[tuple] = None,
+             update: bool = True) -> StepOutput:
+        """One step.  `ids`: the list [h | t | neg] if the caller already holds it contiguously (h, t, neg being views).
+        `prefetch`: the next batch (h, r, t, neg[, ids]) - its inspection (and id exchange) is queued on a side stream
+        while this step computes.  With several GPUs and wait=False the call returns while the last gradient rows are
+        still travelling to their owners; `StepOutput.wait()` orders a consumer after them.  With an optimizer the
+        touched rows are updated before the call's work ends (update=False: the tables stay as they are).
+
+        Order of table accesses within a step: the entity table is read by the staging gather only, a scorer's relation
+        tables by that scorer only, and each update is queued after the kernels that produced its gradient - so every
+        scorer sees the tables as they were when the step began."""
         out = StepOutput()
         B = h.numel()
-        insp = scoring.inspect(scoring.entity_id_list(h, t, neg), self.n_ent)
+        plan = self._take_plan(h, r, t, neg, ids)
+        insp, rinsp, r32 = plan.insp, plan.rinsp, plan.r32
         out.n_staged = insp.n_unique
-        r32 = r.to(torch.int32)
-        rinsp = None
+        main = torch.cuda.current_stream()
+        first_row = 0
         if self.exchange is None:
             staged = scoring.gather_rows(self.ent_local, insp.uniq, n_dev=insp.n_unique)
         else:
-            # the staging exchange (three collectives and one host read of the split sizes) runs on the side stream;
-            # the relation-side inspector needs no entity row and is queued on the main stream first, so it runs meanwhile
-            main = torch.cuda.current_stream()
+            first_row = self.rank * self.exchange.rows_per_rank
+            self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp)
             ready = torch.cuda.Event()
             ready.record(main)
-            if backward:
-                rinsp = scoring.inspect(r32, self.n_rel[self.models[0]])
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                staged = self.exchange.stage(insp)
+                staged = self.exchange.stage_rows()
             main.wait_stream(self.comm_stream)
             staged.record_stream(main)
+        if prefetch is not None:
+            self.prefetch(*prefetch)
         sh, st = insp.inverse[:B], insp.inverse[B:2 * B]
         sneg = insp.inverse[2 * B:].view(neg.shape)
+        do_update = backward and update and self.optimizer is not None
         for m in self.models:
-            sc = Scorer(m, staged, self.rel[m], None, self.neg_mode, self.n_neg_head, self.chunk, self.precision)
+            nnh = 0 if m == "RESCAL" else self.n_neg_head
+            sc = Scorer(m, staged, self.rel.get(m), self.rel2.get(m), self.neg_mode, nnh, self.chunk, self.precision)
             if backward and self.fused and sc.supports_fused_step(sneg.shape[-1]):
                 # one call: the scores of the negatives become loss terms and gradient weights inside the tile kernel
                 pos, loss, sg = sc.loss_backward(sh, r32, st, sneg)
                 out.loss[m], out.pos[m] = loss, pos
             else:
-                pos, negs, _ = sc.forward(sh, r32, st, sneg)
+                pos, negs, _ = sc.forward(sh, r32, st, sneg, rinsp)
                 loss, dpos, dneg = scoring.logistic_loss(pos, negs)
                 out.loss[m], out.pos[m] = loss, pos
                 if not backward:
                     continue
-                sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg)
+                sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg, rinsp)
             grad_rows = scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)     # aligned with insp.uniq
             if self.exchange is None:
                 out.ent_ids, out.n_ent_rows, out.ent_grad[m] = insp.uniq, insp.n_unique, grad_rows
             else:
                 # the entity rows start their way home before the relation-side reduction is queued
-                main = torch.cuda.current_stream()
                 ready = torch.cuda.Event()
                 ready.record(main)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ready)
                     grad_rows.record_stream(self.comm_stream)
                     out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
-            if rinsp is None:
-                rinsp = scoring.inspect(r32, self.n_rel[m])
-            rel_rows = scoring.segment_reduce(sg.rel_slots, rinsp, zero_tail=False)
-            dense_rel = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
-            scoring.scatter_rows(rel_rows, rinsp.uniq, dense_rel, n_dev=rinsp.n_unique)
-            if self.exchange is not None:
-                ready2 = torch.cuda.Event()
-                ready2.record(torch.cuda.current_stream())
-                with torch.cuda.stream(self.comm_stream):
-                    self.comm_stream.wait_event(ready2)
-                    dense_rel.record_stream(self.comm_stream)
-                    dist.all_reduce(dense_rel, group=self.group)
-            out.rel_grad[m] = dense_rel
+            if do_update:
+                self._update(self.ent_local, "ent", out.ent_grad[m], out.ent_ids, out.n_ent_rows, first_row)
+            for slots, table, key, dest in ((sg.rel_slots, self.rel.get(m), ("rel", m), out.rel_grad),
+                                            (sg.rel2_slots, self.rel2.get(m), ("rel2", m), out.rel2_grad)):
+                if slots is None:
+                    continue
+                rows = scoring.segment_reduce(slots, rinsp, zero_tail=False)
+                dense = torch.zeros((self.n_rel[m], self.dim), dtype=torch.float32, device=staged.device)
+                scoring.scatter_rows(rows, rinsp.uniq, dense, n_dev=rinsp.n_unique)
+                self._allreduce(dense, main)
+                dest[m] = dense
+                if do_update:
+                    self._update(table, key, dense)
+            if sg.rel2_groups is not None:              # TransR / RESCAL: one summed (dim, dim) gradient per relation group
+                out.rel2_grad[m], out.rel2_ids, out.n_rel2_groups = sg.rel2_groups, rinsp.uniq, rinsp.n_unique
+                if do_update:
+                    d2 = self.dim * self.dim
+                    self._update(self.rel2[m].view(-1, d2), ("rel2", m), sg.rel2_groups.view(-1, d2), rinsp.uniq, rinsp.n_unique)
         if self.exchange is not None and backward:
             out.done = torch.cuda.Event()
             out.done.record(self.comm_stream)
-            if wait:
+            if wait or do_update:                      # an updated table must be complete before the next step gathers from it
                 out.wait()
+        self.finish_prefetch()
         return out
 
 

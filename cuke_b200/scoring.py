@@ -180,6 +180,26 @@ def segment_reduce_static(rows: torch.Tensor, insp: Inspection, out: torch.Tenso
     return out
 
 
+def apply_sgd(table: torch.Tensor, grad_rows: torch.Tensor, lr: float, ids: Optional[torch.Tensor] = None,
+              n_dev: Optional[torch.Tensor] = None, first_row: int = 0) -> None:
+    """table[ids[i] - first_row] -= lr * grad_rows[i] for i < min(len, *n_dev); ids distinct (None: row i)."""
+    _need_cuda(table, grad_rows, ids, n_dev)
+    n = grad_rows.shape[0] if ids is None else min(ids.numel(), grad_rows.shape[0])
+    check(_lib.lib().kge_apply_sgd(_ptr(table), DTYPES[_dtype_of(table)], table.shape[1], _ptr(ids), n, _ptr(n_dev), int(first_row),
+                                   _ptr(grad_rows), float(lr), _stream()))
+
+
+def apply_adagrad(table: torch.Tensor, state: torch.Tensor, grad_rows: torch.Tensor, lr: float, eps: float = 1e-10,
+                  ids: Optional[torch.Tensor] = None, n_dev: Optional[torch.Tensor] = None, first_row: int = 0) -> None:
+    """Adagrad on the touched rows: state += g^2, table -= lr * g / (sqrt(state) + eps); state is fp32, shaped like table."""
+    _need_cuda(table, state, grad_rows, ids, n_dev)
+    if state.shape != table.shape or state.dtype != torch.float32:
+        raise ValueError("state must be float32 with the table's shape")
+    n = grad_rows.shape[0] if ids is None else min(ids.numel(), grad_rows.shape[0])
+    check(_lib.lib().kge_apply_adagrad(_ptr(table), DTYPES[_dtype_of(table)], _ptr(state), table.shape[1], _ptr(ids), n, _ptr(n_dev),
+                                       int(first_row), _ptr(grad_rows), float(lr), float(eps), _stream()))
+
+
 def owner_counts(insp: Inspection, rows_per_rank: int, world: int) -> torch.Tensor:
     counts = torch.empty(world, dtype=torch.int64, device=insp.uniq.device)
     check(_lib.lib().kge_owner_counts(_ptr(insp.uniq), _ptr(insp.n_unique), insp.n, int(rows_per_rank), int(world),

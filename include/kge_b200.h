@@ -287,6 +287,40 @@ KGE_API int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg,
 KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank,
                      int32_t world, int64_t* counts, kge_stream_t stream);
 
+/* ---- batch ids generated on the device ---------------------------------------------------------------------
+ * Counter-based sampling (Philox4x32-10): element i of stream `stream_id` under `seed` is a pure function of
+ * (seed, stream_id, i) - counter words (i low, i high, stream_id, 0), key words (seed low, seed high), output words
+ * 0 and 1 joined into w = x0 * 2^32 + x1 - so a batch can be regenerated anywhere, bit for bit.  Takes the place of the
+ * host-side batch assembly of apps/kge/data/data_init.py:47-63 (ids drawn by CPU workers and copied to the GPU).
+ *   kge_sample_uniform  out[i] = floor(w * id_space / 2^64)
+ *   kge_sample_cdf      u = (w >> 11) * 2^-53; rank = first k with cdf[k] >= u, at most n_items - 1;
+ *                       out[i] = perm[rank], or rank when perm is NULL.  cdf (n_items,) float64 non-decreasing with
+ *                       cdf[n_items - 1] == 1; perm (n_items,) int64.  With cdf[k] = sum_{j<=k} (j+1)^-s / total this
+ *                       is the bounded Zipf(s) law over a permuted id space.
+ *   kge_sample_triples  row = floor(w * n_triples / 2^64); (h[i], r[i], t[i]) = triples[row][0..2], triples
+ *                       (n_triples, 3) int64: positives drawn from a stored triple list (the train.txt of
+ *                       apps/kge/data/preprocess.py:26-98 once mapped to ids).
+ * `out`, h, r, t have id_bits-wide elements. */
+KGE_API int kge_sample_uniform(void* out, int32_t id_bits, int64_t n, int64_t id_space, uint64_t seed, uint32_t stream_id,
+                               kge_stream_t stream);
+KGE_API int kge_sample_cdf(void* out, int32_t id_bits, int64_t n, const double* cdf, const int64_t* perm, int64_t n_items,
+                           uint64_t seed, uint32_t stream_id, kge_stream_t stream);
+KGE_API int kge_sample_triples(void* h, void* r, void* t, int32_t id_bits, int64_t n, const int64_t* triples, int64_t n_triples,
+                               uint64_t seed, uint32_t stream_id, kge_stream_t stream);
+
+/* ---- sparse optimizers ---------------------------------------------------------------------------------------
+ * Update of exactly the rows a batch touched, from one gradient row per distinct id (the output of
+ * kge_segment_reduce): for i < min(n, *n_dev) (n_dev may be NULL), row = ids[i] - first_row (row i when ids is NULL),
+ *   kge_apply_sgd      table[row] -= lr * grad[i]
+ *   kge_apply_adagrad  state[row] += grad[i]^2 (element-wise);  table[row] -= lr * grad[i] / (sqrt(state[row]) + eps)
+ * table (rows, dim) fp32 or bf16 (updated in fp32, rounded to nearest even), state (rows, dim) fp32, grad (n, dim) fp32.
+ * ids must be distinct.  No reference counterpart: the reference's backward_* functions (apps/kge/kge.py:393-515) stop
+ * at per-triple gradient pieces. */
+KGE_API int kge_apply_sgd(void* table, int32_t dtype, int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev,
+                          int64_t first_row, const float* grad, float lr, kge_stream_t stream);
+KGE_API int kge_apply_adagrad(void* table, int32_t dtype, float* state, int32_t dim, const int64_t* ids, int64_t n,
+                              const int64_t* n_dev, int64_t first_row, const float* grad, float lr, float eps, kge_stream_t stream);
+
 /* ---- measurement aid -----------------------------------------------------------------------------------
  * Launches `blocks` x 256 threads of independent fp32 FMA chains (iters x 128 FMAs per thread) and returns the
  * flop count (2 per FMA) in *flops_out; time it with CUDA events to get this GPU's attainable fp32 FMA rate,

@@ -53,6 +53,125 @@ def test_step_matches_oracle(models, precision, chunk, nn):
         assert torch.equal(out.ent_grad[m][:U], out2.ent_grad[m][:U])       # bit-reproducible step
 
 
+@pytest.mark.parametrize("model,neg_mode,bf16,precision", [("TransH", "per_triple", False, "fp32"), ("TransF", "per_triple", False, "fp32"),
+                                                           ("TransR", "per_triple", False, "fp32"), ("TransR", "per_triple", True, "tensor"),
+                                                           ("RESCAL", "chunk_shared", False, "tensor"), ("RESCAL", "per_triple", False, "fp32")])
+def test_step_covers_every_scorer(model, neg_mode, bf16, precision):
+    """The step pipeline with relation-side tables of every kind: normals (TransH), matrices (TransR, RESCAL)."""
+    from cuke_b200.pipeline import KgeStep
+    from tests.kge_testlib import BF16_TOL, bf16_round
+    ne, d, nr, nn = 1500, 64, 9, 24
+    chunk = 64 if neg_mode == "chunk_shared" else 0
+    B = 192
+    p = make_problem(model, seed=17, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode=neg_mode, chunk=chunk, zipf=True)
+    E, R, P2 = (bf16_round(p[k]) for k in ("E", "R", "P2")) if bf16 else (p["E"], p["R"], p["P2"])
+    nnh = 0 if model == "RESCAL" else nn // 2
+    if neg_mode == "chunk_shared":
+        nnh = 0
+    rel = {} if R is None else {model: to_dev(R, bf16=bf16)}
+    rel2 = {} if P2 is None else {model: to_dev(P2, bf16=bf16)}
+    step = KgeStep([model], to_dev(E, bf16=bf16), rel, ne, neg_mode, nnh, chunk, precision=precision, rel2=rel2)
+    out = step.step(*(to_dev(p[k]) for k in ("h", "r", "t", "neg")))
+    tol = BF16_TOL if bf16 else FP32_TOL
+    pos, negs = oracle.scores(model, E, R, P2, p["h"], p["r"], p["t"], p["neg"], neg_mode, nnh, chunk)
+    n_per = negs.shape[1]
+    loss = softplus(-pos.astype(np.float64)).sum() + softplus(negs.astype(np.float64)).sum() / n_per
+    assert abs(out.loss[model].item() - loss) / abs(loss) < tol
+    dpos = (-sigmoid(-pos.astype(np.float64))).astype(np.float32)
+    dneg = (sigmoid(negs.astype(np.float64)) / n_per).astype(np.float32)
+    gE, gR, gP = oracle.grads(model, E, R, P2, p["h"], p["r"], p["t"], dpos, p["neg"], dneg, neg_mode, nnh, chunk)
+    U = int(out.n_ent_rows.item())
+    dense = np.zeros_like(gE)
+    dense[out.ent_ids[:U].cpu().numpy()] = out.ent_grad[model][:U].double().cpu().numpy()
+    assert rel_err(dense, gE) < tol
+    if gR is not None:
+        assert rel_err(out.rel_grad[model].double().cpu().numpy(), gR) < tol
+    if model == "TransH":
+        assert rel_err(out.rel2_grad[model].double().cpu().numpy(), gP) < tol
+    if model in ("TransR", "RESCAL"):
+        G = int(out.n_rel2_groups.item())
+        dP = np.zeros_like(gP)
+        dP[out.rel2_ids[:G].cpu().numpy()] = out.rel2_grad[model][:G].double().cpu().numpy()
+        assert rel_err(dP, gP) < tol
+
+
+@pytest.mark.parametrize("opt", [("sgd", 0.5), ("adagrad", 0.1, 1e-8)])
+@pytest.mark.parametrize("models,neg_mode,precision", [(["TransE", "DistMult"], "chunk_shared", "tensor"), (["RESCAL"], "chunk_shared", "fp32"),
+                                                       (["TransH"], "per_triple", "fp32")])
+def test_three_training_steps_match_float64_updates(opt, models, neg_mode, precision):
+    """KgeStep with a sparse optimizer: three consecutive steps (inspector -> ... -> update of the touched rows) against
+    float64 numpy updates driven by the oracle's gradients of the same tables."""
+    from cuke_b200.pipeline import KgeStep
+    ne, d, nr, nn, B = 800, 64, 7, 32, 128
+    chunk = 64 if neg_mode == "chunk_shared" else 0
+    p0 = make_problem(models[0], seed=23, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode=neg_mode, chunk=chunk, zipf=True)
+    g = p0["g"]
+    T = {"E": p0["E"].astype(np.float64)}
+    rel, rel2 = {}, {}
+    for m in models:
+        pm = make_problem(m, seed=29 + len(m), ne=8, nr=nr, d=d, B=8, nn=2)
+        if pm["R"] is not None:
+            T[("R", m)] = pm["R"].astype(np.float64); rel[m] = to_dev(pm["R"])
+        if pm["P2"] is not None:
+            T[("P", m)] = pm["P2"].astype(np.float64); rel2[m] = to_dev(pm["P2"])
+    S = {k: np.zeros_like(v) for k, v in T.items()}
+    step = KgeStep(models, to_dev(p0["E"]), rel, ne, neg_mode, 0, chunk, precision=precision, rel2=rel2, optimizer=opt)
+
+    def upd(key, grad):
+        if opt[0] == "sgd":
+            T[key] -= opt[1] * grad
+        else:
+            S[key] += grad ** 2
+            T[key] -= opt[1] * grad / (np.sqrt(S[key]) + opt[2])
+
+    for it in range(3):
+        pb = make_problem(models[0], seed=100 + it, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode=neg_mode, chunk=chunk, zipf=True)
+        h, r, t, neg = pb["h"], pb["r"], pb["t"], pb["neg"]
+        step.step(to_dev(h), to_dev(r), to_dev(t), to_dev(neg))
+        f32 = lambda k: None if k not in T else T[k].astype(np.float32)
+        grads = []
+        for m in models:                   # every scorer sees the tables as they were when the step began
+            E, R, P2 = f32("E"), f32(("R", m)), f32(("P", m))
+            pos, negs = oracle.scores(m, E, R, P2, h, r, t, neg, neg_mode, 0, chunk)
+            dpos = (-sigmoid(-pos.astype(np.float64))).astype(np.float32)
+            dneg = (sigmoid(negs.astype(np.float64)) / negs.shape[1]).astype(np.float32)
+            grads.append((m, oracle.grads(m, E, R, P2, h, r, t, dpos, neg, dneg, neg_mode, 0, chunk)))
+        for m, (gE, gR, gP) in grads:
+            touched = np.unique(np.concatenate([h, t, neg.reshape(-1)]))
+            mask = np.zeros((ne, 1)); mask[touched] = 1.0        # only touched rows move (Adagrad: untouched rows have g = 0 anyway)
+            upd("E", gE * mask)
+            if gR is not None:
+                upd(("R", m), gR)
+            if gP is not None:
+                upd(("P", m), gP)
+    assert rel_err(step.ent_local.double().cpu().numpy(), T["E"]) < FP32_TOL
+    for m in models:
+        if m in rel:
+            assert rel_err(step.rel[m].double().cpu().numpy(), T[("R", m)]) < FP32_TOL
+        if m in rel2:
+            assert rel_err(step.rel2[m].double().cpu().numpy(), T[("P", m)]) < FP32_TOL
+
+
+def test_prefetched_plan_gives_identical_steps():
+    """step(..., prefetch=next_batch): the next batch's inspections run on a side stream; results are bit-identical."""
+    from cuke_b200.pipeline import KgeStep
+    ne, d, nr, nn, chunk, B = 3000, 64, 11, 96, 128, 256
+    p = make_problem("TransE", seed=5, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    rel = {m: to_dev((p["g"].standard_normal((nr, d)) / 8).astype(np.float32)) for m in ("TransE", "DistMult")}
+    batches = []
+    for it in range(3):
+        pb = make_problem("TransE", seed=50 + it, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+        batches.append(tuple(to_dev(pb[k]) for k in ("h", "r", "t", "neg")))
+    a = KgeStep(["TransE", "DistMult"], to_dev(p["E"]), rel, ne, "chunk_shared", 0, chunk, precision="tensor")
+    plain = [a.step(*b) for b in batches]
+    ahead = [a.step(*batches[i], prefetch=batches[i + 1] if i + 1 < 3 else None) for i in range(3)]
+    for x, y in zip(plain, ahead):
+        for m in ("TransE", "DistMult"):
+            U = int(x.n_ent_rows.item())
+            assert torch.equal(x.loss[m], y.loss[m]) and torch.equal(x.ent_grad[m][:U], y.ent_grad[m][:U])
+            assert torch.equal(x.rel_grad[m], y.rel_grad[m])
+
+
 @pytest.mark.parametrize("model", ["TransE", "TransH", "TransR", "TransF", "RESCAL", "DistMult", "ComplEx"])
 def test_compile_and_run_drop_in(model):
     """The reference's user code path: build the expression, print_cuda, compile_and_run(code, *args) with the
