@@ -11,7 +11,9 @@
 //           dP[g]       = sum_{i in group g} E[h_i] (x) GA[i]            (rescal_dproj_kernel)
 //   TransR  score(i,j)  = -|| (a - b) . P[r_i] + R[r_i] ||  for the positive (j = 0) and every negative
 //                                                                        (transr_fwd_kernel; backward: transr_gv/gd/dproj/reduce)
+#include <atomic>
 #include "tile_gemm.cuh"
+#include "rows.cuh"
 
 namespace kge {
 
@@ -248,6 +250,152 @@ __global__ void __launch_bounds__(256) transr_fwd_kernel(GroupArgs a, float* pos
     }
 }
 
+// =====================================================================================================================
+// Small groups: relation-grouped projections for tens of rows per relation (tens of rows per relation), fp32 CUDA cores.
+//
+// With ~33 triples per relation (RESCAL at 16,384 triples over 500 relations) a relation's dim x dim matrix is used by
+// so few rows that the products are bound by READING the matrices (131 MB at dim 256), not by arithmetic: a 128-row tile
+// engine would spend three quarters of its work on padding.  Here one CTA owns one relation group and streams P[r]
+// through once per block of 32 rows; the group's rows sit transposed in shared memory (Xs[k][m], so that four rows are
+// one 128-bit broadcast read) and thread t owns output column t (dim <= 256):
+//
+//   small_fwd    Y[m][j]  = sum_i X[m][i] P[r][i][j]      X = E[h] gathered        -> anchors          (RESCAL forward)
+//   small_bwd_x  Y[m][i]  = sum_j G[m][j] P[r][i][j]      G = anchor gradients     -> g_head           (thread t streams row P[t][:])
+//   small_dproj  dP[i][j] = sum_m X[m][i] G[m][j]         one (dim x dim) gradient per group, up to 64 rows per pass
+//
+// Orientation is the reference CPU path's (out[j] = sum_i x[i] P[r][i][j], apps/kge/kge.py:21-23,370-390).
+struct SmallGroupArgs {
+    const void* ent; const void* proj; const void* h;
+    const int* rel_perm; const int* rel_seg; const long long* rel_uniq; const long long* n_groups;
+    int dim;
+};
+
+constexpr int SG_MB = 32;          // rows per block
+constexpr int SG_LD = 36;          // padded pitch of the transposed row block (floats; multiple of 4)
+constexpr int SG_MAXROWS = 64;     // rows per pass of small_dproj
+constexpr int SG_LD2 = 68;
+
+__device__ __forceinline__ float sg_get(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float sg_get(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+// Rows [m0, m0 + rows) of the group -> Xs[k * LD + m] (zero for m >= rows).  Warp w takes rows w, w + 8, ...; a lane reads
+// consecutive elements of the row.  SRC: 0 = entity rows gathered through h (type T), 1 = fp32 rows `frows` indexed by triple.
+template <typename T, typename I, int SRC, int LD, int MB>
+__device__ __forceinline__ void sg_stage_rows(const SmallGroupArgs& a, const float* frows, int m0, int rows, float* Xs) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, dim = a.dim;
+    for (int m = w; m < MB; m += 8) {
+        const bool ok = m < rows;
+        const int tri = ok ? a.rel_perm[m0 + m] : 0;
+        if (SRC == 0) {
+            const T* row = reinterpret_cast<const T*>(a.ent) + (ok ? load_id<I>(a.h, tri) : 0) * dim;
+            for (int k = lane; k < dim; k += 32) Xs[k * LD + m] = ok ? sg_get(row + k) : 0.f;
+        } else {
+            const float* row = frows + (long long)tri * dim;
+            for (int k = lane; k < dim; k += 32) Xs[k * LD + m] = ok ? __ldg(row + k) : 0.f;
+        }
+    }
+}
+
+// acc[m] += Xs[k][m] * p for the first 4 * nq rows
+template <int LD>
+__device__ __forceinline__ void sg_fma_rows(float (&acc)[SG_MB], const float* xk, float p, int nq) {
+#pragma unroll
+    for (int q = 0; q < SG_MB / 4; ++q) {
+        if (q < nq) {
+            const float4 x = *reinterpret_cast<const float4*>(xk + 4 * q);
+            acc[4 * q + 0] = fmaf(x.x, p, acc[4 * q + 0]);
+            acc[4 * q + 1] = fmaf(x.y, p, acc[4 * q + 1]);
+            acc[4 * q + 2] = fmaf(x.z, p, acc[4 * q + 2]);
+            acc[4 * q + 3] = fmaf(x.w, p, acc[4 * q + 3]);
+        }
+    }
+}
+
+// TRANS = false: Y = X . P (thread t owns column j = t, reads P[k][t]: coalesced rows of P)
+// TRANS = true : Y = G . P^T (thread t owns output i = t, streams its own row P[t][k..k+3]; the other half of each 32-byte
+//                sector is used by the next k step out of L1)
+template <typename T, typename I, int SRC, bool TRANS>
+__global__ void __launch_bounds__(256) small_proj_kernel(SmallGroupArgs a, const float* frows, float* out) {
+    extern __shared__ __align__(16) float Xs[];                 // dim * SG_LD floats
+    const int g = blockIdx.x;
+    if (g >= *a.n_groups) return;
+    const int t = threadIdx.x, dim = a.dim;
+    const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    const T* P = reinterpret_cast<const T*>(a.proj) + a.rel_uniq[g] * (long long)dim * dim;
+    const bool col_ok = t < dim;
+    for (int m0 = s; m0 < e; m0 += SG_MB) {
+        const int rows = min(SG_MB, e - m0);
+        const int nq = (rows + 3) >> 2;
+        __syncthreads();                                        // the previous block's reads of Xs are done
+        sg_stage_rows<T, I, SRC, SG_LD, SG_MB>(a, frows, m0, rows, Xs);
+        __syncthreads();
+        float acc[SG_MB];
+#pragma unroll
+        for (int m = 0; m < SG_MB; ++m) acc[m] = 0.f;
+        if (col_ok) {
+            if (!TRANS) {
+                const T* pc = P + t;
+#pragma unroll 4
+                for (int k = 0; k < dim; ++k) sg_fma_rows<SG_LD>(acc, Xs + k * SG_LD, sg_get(pc + (long long)k * dim), nq);
+            } else {
+                const T* pr = P + (long long)t * dim;
+                for (int k = 0; k < dim; k += 4) {              // dim % 4 == 0
+                    const float4 p4 = load_quad<T, true>(pr, k >> 2, dim);
+                    sg_fma_rows<SG_LD>(acc, Xs + (k + 0) * SG_LD, p4.x, nq);
+                    sg_fma_rows<SG_LD>(acc, Xs + (k + 1) * SG_LD, p4.y, nq);
+                    sg_fma_rows<SG_LD>(acc, Xs + (k + 2) * SG_LD, p4.z, nq);
+                    sg_fma_rows<SG_LD>(acc, Xs + (k + 3) * SG_LD, p4.w, nq);
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < SG_MB; ++m)
+                if (m < rows) out[(long long)a.rel_perm[m0 + m] * dim + t] = acc[m];       // 256 threads: one contiguous row
+        }
+    }
+}
+
+// dP[g][i][j] = sum over the group's rows m of X[m][i] * G[m][j].  Thread t owns column j = t and keeps G[m][t] of up to
+// 64 rows in registers; groups with more rows take further passes that add to what the earlier ones stored.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) small_dproj_kernel(SmallGroupArgs a, const float* grows, float* dproj) {
+    extern __shared__ __align__(16) float Xs[];                 // dim * SG_LD2 floats
+    const int g = blockIdx.x;
+    if (g >= *a.n_groups) return;
+    const int t = threadIdx.x, dim = a.dim;
+    const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    float* out = dproj + (long long)g * dim * dim;
+    const bool col_ok = t < dim;
+    for (int m0 = s; m0 < e; m0 += SG_MAXROWS) {
+        const int rows = min(SG_MAXROWS, e - m0);
+        const int nq = (rows + 3) >> 2;
+        __syncthreads();
+        sg_stage_rows<T, I, 0, SG_LD2, SG_MAXROWS>(a, nullptr, m0, rows, Xs);
+        __syncthreads();
+        if (!col_ok) continue;
+        float gm[SG_MAXROWS];
+#pragma unroll
+        for (int m = 0; m < SG_MAXROWS; ++m) gm[m] = m < rows ? __ldg(grows + (long long)a.rel_perm[m0 + m] * dim + t) : 0.f;
+        for (int i = 0; i < dim; ++i) {
+            const float* xi = Xs + i * SG_LD2;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int q = 0; q < SG_MAXROWS / 4; ++q) {
+                if (q < nq) {
+                    const float4 x = *reinterpret_cast<const float4*>(xi + 4 * q);
+                    s0 = fmaf(x.x, gm[4 * q + 0], s0);
+                    s1 = fmaf(x.y, gm[4 * q + 1], s1);
+                    s2 = fmaf(x.z, gm[4 * q + 2], s2);
+                    s3 = fmaf(x.w, gm[4 * q + 3], s3);
+                }
+            }
+            const float v = (s0 + s1) + (s2 + s3);
+            float* o = out + (long long)i * dim + t;
+            *o = (m0 == s) ? v : *o + v;
+        }
+    }
+}
+
+
 // ---- host ---------------------------------------------------------------------------------------------------------
 static GroupArgs group_args(const kge_problem* p, const kge_tensors* t) {
     GroupArgs a;
@@ -273,8 +421,31 @@ static inline unsigned group_bound(const kge_problem* p) {
         }                                                                                  \
     } while (0)
 
+// The small-group kernels give each thread one output column: dim <= 256, vector rows.
+static bool small_groups(const kge_problem* p) { return p->dim <= 256 && p->dim % 4 == 0; }
+static SmallGroupArgs small_args(const kge_problem* p, const kge_tensors* t) {
+    SmallGroupArgs a;
+    a.ent = t->ent; a.proj = t->rel2; a.h = t->h; a.rel_perm = t->rel_perm; a.rel_seg = t->rel_seg;
+    a.rel_uniq = (const long long*)t->rel_uniq; a.n_groups = (const long long*)t->n_rel_groups; a.dim = p->dim;
+    return a;
+}
+#define KGE_SMALL_DISPATCH(CALL)                                                                  \
+    do {                                                                                          \
+        if (p->dtype == KGE_F32) { if (p->id_bits == 64) { CALL(float, int64_t); } else { CALL(float, int32_t); } }            \
+        else { if (p->id_bits == 64) { CALL(__nv_bfloat16, int64_t); } else { CALL(__nv_bfloat16, int32_t); } }                \
+    } while (0)
+
 int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anchors, cudaStream_t s) {
     if (p->batch <= 0) return 0;
+    if (small_groups(p)) {
+        const SmallGroupArgs sa = small_args(p, t);
+        const size_t smem = (size_t)p->dim * SG_LD * sizeof(float);
+#define KGE_CALL(T, I) small_proj_kernel<T, I, 0, false><<<group_bound(p), 256, smem, s>>>(sa, nullptr, anchors)
+        KGE_SMALL_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+        KGE_LAUNCH_CHECK("small_proj_kernel(anchors)");
+        return 0;
+    }
     const GroupArgs a = group_args(p, t);
     const dim3 grid(group_bound(p), (p->dim + TG_BN - 1) / TG_BN);
 #define KGE_CALL(T, I, V) rescal_anchor_kernel<T, I, V><<<grid, 256, 0, s>>>(a, anchors)
@@ -287,6 +458,31 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
 int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const float* ga, float* g_head, float* dproj,
                            cudaStream_t s) {
     if (p->batch <= 0) return 0;
+    if (small_groups(p)) {
+        const SmallGroupArgs sa = small_args(p, t);
+        const size_t smem = (size_t)p->dim * SG_LD * sizeof(float), smem2 = (size_t)p->dim * SG_LD2 * sizeof(float);
+#define KGE_CALL(T, I) small_proj_kernel<T, I, 1, true><<<group_bound(p), 256, smem, s>>>(sa, ga, g_head)
+        KGE_SMALL_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+        KGE_LAUNCH_CHECK("small_proj_kernel(g_head)");
+        // 68 KB of dynamic shared memory at dim 256: above the 48 KB default, opted in per device
+        static std::atomic<bool> opted[128];
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status(cudaGetLastError(), "cudaGetDevice");
+        if (dev < 0 || dev >= 128 || !opted[dev].load(std::memory_order_acquire)) {
+            cudaError_t e = cudaSuccess;
+#define KGE_CALL(T, I) if (e == cudaSuccess) e = cudaFuncSetAttribute(small_dproj_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * SG_LD2 * (int)sizeof(float))
+            KGE_CALL(float, int64_t); KGE_CALL(float, int32_t); KGE_CALL(__nv_bfloat16, int64_t); KGE_CALL(__nv_bfloat16, int32_t);
+#undef KGE_CALL
+            if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(small_dproj_kernel)");
+            if (dev >= 0 && dev < 128) opted[dev].store(true, std::memory_order_release);
+        }
+#define KGE_CALL(T, I) small_dproj_kernel<T, I><<<group_bound(p), 256, smem2, s>>>(sa, ga, dproj)
+        KGE_SMALL_DISPATCH(KGE_CALL);
+#undef KGE_CALL
+        KGE_LAUNCH_CHECK("small_dproj_kernel");
+        return 0;
+    }
     const GroupArgs a = group_args(p, t);
     const unsigned nt = (p->dim + TG_BN - 1) / TG_BN;
     const dim3 grid1(group_bound(p), nt);

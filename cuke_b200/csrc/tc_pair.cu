@@ -286,9 +286,9 @@ constexpr int UM_EPI_WARPS = 8;
 // chunk goes through a 32x32 XOR-swizzled shared-memory staging square (conflict-free both ways) and comes back with
 // lane = COLUMN: global loads and stores are then 128-byte row segments, per-column operands are one register per lane,
 // per-row operands one shuffle per row, and the fix-up test is a mask bit instead of a branch per element.
-// GROUP selects which epilogues an instantiation carries: G_DENSE the dense chunk-shared products (store, distance, rank-1,
-// fused loss), G_GROUPED the relation-grouped products (store, norm, dL/dv rows, scatter).  Two instantiations keep the
-// register allocation of each set independent of the other's code.
+// GROUP selects which epilogues an instantiation of the one-CTA kernel carries: G_DENSE the dense chunk-shared products
+// (store, distance, rank-1, fused loss; epilogue_tile below), G_GROUPED the relation-grouped products (store, norm, dL/dv
+// rows, scatter; epilogue_grouped).  Two instantiations keep the register allocation of each set independent of the other.
 enum { G_DENSE = 0, G_GROUPED = 1 };
 template <int GROUP>
 __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
@@ -300,40 +300,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     const int m = m0 + row;
     const bool row_ok = m < p.m_rows;
     const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
-    if (GROUP == G_GROUPED && p.ep == EP_NORM) {
-        // squared norm of (acc + R[z]) over the row: nothing is stored per element, the thread-per-row form is kept
-        float* ssq_part = epi_smem;                // [2 accumulators][2 halves][128 rows]
-        float ssq = 0.f;
-#pragma unroll 1
-        for (int c = half; c < n_chunks32; c += 2) {
-            float v[32];
-            umma::tmem_ld32(t_row + c * 32, v);     // warp-collective
-            const int nbase = n0 + c * 32;
-            const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (j < lim) {
-                    const long long ri = static_cast<long long>(b) * p.n_cols + nbase + j;
-                    const float rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
-                                                   : reinterpret_cast<const float*>(p.rel_vec)[ri];
-                    const float t = v[j] + rv;
-                    ssq = fmaf(t, t, ssq);
-                }
-            }
-        }
-        umma::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) umma::mbar_arrive_cluster(drained);
-        ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
-        asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight epilogue warps
-        if (half == 0) {
-            const long long dst = p.row_dst[m];               // >= 0: negative score index, <= -2: positive -2-i, -1: padding
-            const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
-            if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
-        }
-        return;
-    }
-
     float* stg = epi_smem + (warp - 2) * 1024;                  // this warp's 32x32 staging square
     const int mq = m0 + q * 32;                                  // first row of this warp's quarter
     const int rows_here = min(32, p.m_rows - mq);               // rows of the quarter that exist (may be <= 0)
@@ -343,7 +309,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     if (row_ok) {
         if (GROUP == G_DENSE && (p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist))) row_op = p.sq_a[grow0 + lane];
         else if (GROUP == G_DENSE && p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
-        else if (GROUP == G_GROUPED && p.ep == EP_GV) row_op = p.coef[m];
     }
     float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; this thread's (= row's) sum of W
 #pragma unroll 1
@@ -514,32 +479,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 const float rs = __shfl_sync(0xffffffffu, row_op, r);
                 if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[r], -x);
             }
-        } else if (GROUP == G_GROUPED && p.ep == EP_GV) {          // dL/dv rows for the backward products, stored as bf16
-            float rv = 0.f;
-            if (col_ok) {
-                const long long ri = static_cast<long long>(b) * p.n_cols + col;
-                rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
-                                   : reinterpret_cast<const float*>(p.rel_vec)[ri];
-            }
-            __nv_bfloat16* go = p.gv_out + static_cast<long long>(mq) * p.n_cols + col;
-#pragma unroll 8
-            for (int r = 0; r < rows_here; ++r, go += p.n_cols) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                const float cf = __shfl_sync(0xffffffffu, row_op, r);
-                if (col_ok) *go = __float2bfloat16_rn(cf * (x + rv));
-            }
-        } else if (GROUP == G_GROUPED && p.ep == EP_SCATTER) {     // gradient of the difference row: to the replaced row's slot (signed) or to GD0
-            // lane r holds the destination of row r: one coalesced load per chunk instead of a dependent load per row
-            const long long dst_lane = lane < rows_here ? p.row_dst[mq + lane] : -1;
-#pragma unroll 4
-            for (int r = 0; r < rows_here; ++r) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                const long long dst = __shfl_sync(0xffffffffu, dst_lane, r);
-                if (dst == -1 || !col_ok) continue;
-                if (dst >= kTailSide) p.neg_out[(dst - kTailSide) * p.n_cols + col] = -x;
-                else if (dst >= 0) p.neg_out[dst * p.n_cols + col] = x;
-                else p.pos_out[(-2 - dst) * p.n_cols + col] = x;
-            }
         } else {                             // EP_STORE
             float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
 #pragma unroll 8
@@ -559,6 +498,109 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         if (row_ok && p.loss_dist) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
         const float l = warp_sum(loss_acc);
         if (lane == 0) p.loss_part[slot * UM_EPI_WARPS + (warp - 2)] = l;
+    }
+}
+
+// Epilogues of the relation-grouped products (norm, dL/dv rows, scatter, plain store), in the layout tcgen05.ld delivers:
+// thread = row, 32 consecutive columns per chunk.  Everything that is per ROW (destination, coefficient, sign) is then a
+// register of the owning thread, computed once per tile, and a thread's 32 values are one contiguous 128-byte (fp32) or
+// 64-byte (bf16) piece of its destination row, written with 16-byte stores; the per-COLUMN vector R[z] sits in a
+// shared-memory strip of the warp and is read as 128-bit broadcasts.  (The dense epilogues go through a transposing
+// staging square instead, because their per-column operands and row-contiguous destinations favour lane = column.)
+__device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
+                                                 int bn_tile, int buf, uint32_t drained, float* epi_smem) {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = q * 32 + lane;
+    const int n_chunks32 = (bn_tile + 31) / 32;
+    const int m = m0 + row;
+    const bool row_ok = m < p.m_rows;
+    const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
+    float* rs = epi_smem + 1024 + (warp - 2) * 256;            // this warp's copy of R[z] (n_cols <= 256), zero padded
+    if (p.ep == EP_NORM || p.ep == EP_GV) {
+        for (int c = lane; c < 256; c += 32) {
+            float rv = 0.f;
+            if (c < p.n_cols) {
+                const long long ri = static_cast<long long>(b) * p.n_cols + c;
+                rv = p.rel_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.rel_vec)[ri])
+                                   : reinterpret_cast<const float*>(p.rel_vec)[ri];
+            }
+            rs[c] = rv;
+        }
+        __syncwarp();
+    }
+    // per-row operands of the owning thread
+    float coef = 0.f, sign = 1.f;
+    float* orow = nullptr;                                     // fp32 destination row (scatter, store)
+    __nv_bfloat16* grow = nullptr;                             // bf16 destination row (dL/dv)
+    if (row_ok) {
+        if (p.ep == EP_GV) { coef = p.coef[m]; grow = p.gv_out + static_cast<long long>(m) * p.n_cols; }
+        else if (p.ep == EP_SCATTER) {
+            const long long dst = p.row_dst[m];                // >= kTailSide: slot, minus sign; >= 0: slot; <= -2: positive -2-i; -1: padding
+            if (dst >= kTailSide) { orow = p.neg_out + (dst - kTailSide) * p.n_cols; sign = -1.f; }
+            else if (dst >= 0) orow = p.neg_out + dst * p.n_cols;
+            else if (dst <= -2) orow = p.pos_out + (-2 - dst) * p.n_cols;
+        } else if (p.ep == EP_STORE) {
+            orow = p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld;
+        }
+    }
+    float ssq = 0.f;
+#pragma unroll 1
+    for (int c = half; c < n_chunks32; c += 2) {
+        float v[32];
+        umma::tmem_ld32(t_row + c * 32, v);                     // warp-collective
+        const int nbase = n0 + c * 32;
+        const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));      // valid columns of this chunk (a multiple of 4)
+        if (p.ep == EP_NORM) {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rs + c * 32 + 4 * j4);
+                if (4 * j4 < lim) {
+                    const float t0 = v[4 * j4 + 0] + r4.x, t1 = v[4 * j4 + 1] + r4.y, t2 = v[4 * j4 + 2] + r4.z, t3 = v[4 * j4 + 3] + r4.w;
+                    ssq = fmaf(t0, t0, fmaf(t1, t1, fmaf(t2, t2, fmaf(t3, t3, ssq))));
+                }
+            }
+        } else if (p.ep == EP_GV) {
+            if (grow != nullptr) {
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {
+                    if (8 * j8 < lim) {
+                        const float4 ra = *reinterpret_cast<const float4*>(rs + c * 32 + 8 * j8);
+                        const float4 rb = *reinterpret_cast<const float4*>(rs + c * 32 + 8 * j8 + 4);
+                        __nv_bfloat162 o0 = __floats2bfloat162_rn(coef * (v[8 * j8 + 0] + ra.x), coef * (v[8 * j8 + 1] + ra.y));
+                        __nv_bfloat162 o1 = __floats2bfloat162_rn(coef * (v[8 * j8 + 2] + ra.z), coef * (v[8 * j8 + 3] + ra.w));
+                        __nv_bfloat162 o2 = __floats2bfloat162_rn(coef * (v[8 * j8 + 4] + rb.x), coef * (v[8 * j8 + 5] + rb.y));
+                        __nv_bfloat162 o3 = __floats2bfloat162_rn(coef * (v[8 * j8 + 6] + rb.z), coef * (v[8 * j8 + 7] + rb.w));
+                        uint4 u;
+                        u.x = *reinterpret_cast<unsigned*>(&o0); u.y = *reinterpret_cast<unsigned*>(&o1);
+                        u.z = *reinterpret_cast<unsigned*>(&o2); u.w = *reinterpret_cast<unsigned*>(&o3);
+                        *reinterpret_cast<uint4*>(grow + nbase + 8 * j8) = u;
+                    }
+                }
+            }
+        } else {                                               // EP_SCATTER (signed) and EP_STORE
+            if (orow != nullptr) {
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4)
+                    if (4 * j4 < lim)
+                        *reinterpret_cast<float4*>(orow + nbase + 4 * j4) =
+                            make_float4(sign * v[4 * j4 + 0], sign * v[4 * j4 + 1], sign * v[4 * j4 + 2], sign * v[4 * j4 + 3]);
+            }
+        }
+    }
+    // this warp is done reading the accumulator: hand it back to the MMA thread
+    umma::tc_fence_before();
+    __syncwarp();
+    if (lane == 0) umma::mbar_arrive_cluster(drained);
+    if (p.ep == EP_NORM) {
+        float* ssq_part = epi_smem;                            // [2 accumulators][2 halves][128 rows]
+        ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
+        asm volatile("bar.sync 1, 256;" ::: "memory");         // the eight epilogue warps
+        if (half == 0) {
+            const long long dst = p.row_dst[m];                // >= 0: negative score index, <= -2: positive -2-i, -1: padding
+            const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
+            if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
+        }
     }
 }
 
@@ -751,7 +793,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
-            epilogue_tile<GROUP>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
+            if (GROUP == G_GROUPED) epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem);
+            else epilogue_tile<G_DENSE>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
     umma::tc_fence_before();

@@ -95,7 +95,10 @@ def test_step_covers_every_scorer(model, neg_mode, bf16, precision):
         assert rel_err(dP, gP) < tol
 
 
-@pytest.mark.parametrize("opt", [("sgd", 0.5), ("adagrad", 0.1, 1e-8)])
+# Adagrad divides by sqrt(sum g^2) + eps: with a tiny eps the first update of an element is +-lr whatever the size of its
+# gradient, which turns rounding noise in near-zero gradient entries into full-size steps; eps at the scale of the
+# gradients keeps the comparison about the optimizer, not about the sign of noise
+@pytest.mark.parametrize("opt", [("sgd", 0.5), ("adagrad", 0.1, 1e-3)])
 @pytest.mark.parametrize("models,neg_mode,precision", [(["TransE", "DistMult"], "chunk_shared", "tensor"), (["RESCAL"], "chunk_shared", "fp32"),
                                                        (["TransH"], "per_triple", "fp32")])
 def test_three_training_steps_match_float64_updates(opt, models, neg_mode, precision):
