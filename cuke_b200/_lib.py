@@ -47,6 +47,12 @@ class KgeGrads(C.Structure):
                 ("g_rel", C.c_void_p), ("g_rel2", C.c_void_p)]
 
 
+class KgeProgram(C.Structure):
+    _fields_ = [("n_ops", C.c_int32), ("n_vreg", C.c_int32), ("n_sreg", C.c_int32),
+                ("out_kind", C.c_int32), ("out_a", C.c_int32), ("out_b", C.c_int32), ("out_s", C.c_int32),
+                ("out_table", C.c_int32), ("out_ids", C.c_int32), ("ops", (C.c_int32 * 5) * 64)]
+
+
 _lib = None
 
 _vp, _i32, _i64, _sz, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t, C.c_float
@@ -79,6 +85,7 @@ SIGNATURES = {
     "kge_score_loss_backward": (C.c_int, [_PP, _PT, _f32, _vp, _vp, _PG, _vp, _sz, _vp]),
     "kge_logistic_loss": (C.c_int, [_vp, _i64, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _sz, _vp]),
     "kge_owner_counts": (C.c_int, [_vp, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "kge_eval_program": (C.c_int, [C.POINTER(KgeProgram), _i32, _i64, _vp, _i32, _vp, _i32, _i32, _vp, _vp]),
     "kge_sample_uniform": (C.c_int, [_vp, _i32, _i64, _i64, C.c_uint64, C.c_uint32, _vp]),
     "kge_sample_cdf": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _i64, C.c_uint64, C.c_uint32, _vp]),
     "kge_sample_triples": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _vp, _i64, C.c_uint64, C.c_uint32, _vp]),

@@ -270,131 +270,150 @@ struct SmallGroupArgs {
     int dim;
 };
 
-constexpr int SG_MB = 32;          // rows per block
-constexpr int SG_LD = 36;          // padded pitch of the transposed row block (floats; multiple of 4)
-constexpr int SG_MAXROWS = 64;     // rows per pass of small_dproj
-constexpr int SG_LD2 = 68;
+// Register tile of a thread: 16 rows x 4 columns.  256 threads = 4 row groups (two warps each) x 64 column groups, so a
+// pass covers 64 rows x 256 columns; per k a thread reads its 16 row values as four 128-bit shared-memory BROADCASTS (the
+// whole warp shares the row group) and its 4 matrix values as one 128-bit load: 5 memory instructions per 64 FMAs.
+// (One row per thread-register and one column per thread would need a shared-memory instruction per 4 FMAs and is bound
+// by the shared-memory pipe, not by arithmetic.)
+constexpr int SG_ROWS = 64;        // rows per pass
+constexpr int SG_LD = 68;          // pitch of the transposed row block Xs[k][m] (floats; multiple of 4)
+constexpr int SG_DP_ROWS = 32;     // rows per pass of small_dproj (X and G rows side by side in shared memory)
 
 __device__ __forceinline__ float sg_get(const float* p) { return __ldg(p); }
 __device__ __forceinline__ float sg_get(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
-// Rows [m0, m0 + rows) of the group -> Xs[k * LD + m] (zero for m >= rows).  Warp w takes rows w, w + 8, ...; a lane reads
-// consecutive elements of the row.  SRC: 0 = entity rows gathered through h (type T), 1 = fp32 rows `frows` indexed by triple.
-template <typename T, typename I, int SRC, int LD, int MB>
-__device__ __forceinline__ void sg_stage_rows(const SmallGroupArgs& a, const float* frows, int m0, int rows, float* Xs) {
+// Rows [m0, m0 + rows) of the group -> Xs[k * SG_LD + m], transposed (zero for m >= rows).  Warp w takes rows w, w + 8, ...;
+// a lane reads consecutive elements of the row.  SRC: 0 = entity rows gathered through h (type T), 1 = fp32 rows `frows`
+// indexed by triple.
+template <typename T, typename I, int SRC>
+__device__ __forceinline__ void sg_stage_transposed(const SmallGroupArgs& a, const float* frows, int m0, int rows, float* Xs) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, dim = a.dim;
-    for (int m = w; m < MB; m += 8) {
+    for (int m = w; m < SG_ROWS; m += 8) {
         const bool ok = m < rows;
         const int tri = ok ? a.rel_perm[m0 + m] : 0;
         if (SRC == 0) {
             const T* row = reinterpret_cast<const T*>(a.ent) + (ok ? load_id<I>(a.h, tri) : 0) * dim;
-            for (int k = lane; k < dim; k += 32) Xs[k * LD + m] = ok ? sg_get(row + k) : 0.f;
+            for (int k = lane; k < dim; k += 32) Xs[k * SG_LD + m] = ok ? sg_get(row + k) : 0.f;
         } else {
             const float* row = frows + (long long)tri * dim;
-            for (int k = lane; k < dim; k += 32) Xs[k * LD + m] = ok ? __ldg(row + k) : 0.f;
+            for (int k = lane; k < dim; k += 32) Xs[k * SG_LD + m] = ok ? __ldg(row + k) : 0.f;
         }
     }
 }
 
-// acc[m] += Xs[k][m] * p for the first 4 * nq rows
-template <int LD>
-__device__ __forceinline__ void sg_fma_rows(float (&acc)[SG_MB], const float* xk, float p, int nq) {
+// acc[r][c] += x[r] * p[c] for the first 4 * nq of the thread's 16 rows
+__device__ __forceinline__ void sg_fma_tile(float (&acc)[16][4], const float* xk, const float4 p, int nq) {
 #pragma unroll
-    for (int q = 0; q < SG_MB / 4; ++q) {
+    for (int q = 0; q < 4; ++q) {
         if (q < nq) {
             const float4 x = *reinterpret_cast<const float4*>(xk + 4 * q);
-            acc[4 * q + 0] = fmaf(x.x, p, acc[4 * q + 0]);
-            acc[4 * q + 1] = fmaf(x.y, p, acc[4 * q + 1]);
-            acc[4 * q + 2] = fmaf(x.z, p, acc[4 * q + 2]);
-            acc[4 * q + 3] = fmaf(x.w, p, acc[4 * q + 3]);
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                acc[4 * q + r][0] = fmaf(xs[r], p.x, acc[4 * q + r][0]);
+                acc[4 * q + r][1] = fmaf(xs[r], p.y, acc[4 * q + r][1]);
+                acc[4 * q + r][2] = fmaf(xs[r], p.z, acc[4 * q + r][2]);
+                acc[4 * q + r][3] = fmaf(xs[r], p.w, acc[4 * q + r][3]);
+            }
         }
     }
 }
 
-// TRANS = false: Y = X . P (thread t owns column j = t, reads P[k][t]: coalesced rows of P)
-// TRANS = true : Y = G . P^T (thread t owns output i = t, streams its own row P[t][k..k+3]; the other half of each 32-byte
-//                sector is used by the next k step out of L1)
+// TRANS = false: Y = X . P      thread columns j = 4cg..4cg+3: P[k][4cg..] is one 128-bit load, a warp reads 512 B of a row of P
+// TRANS = true : Y = G . P^T    thread outputs i = 4cg..4cg+3: the thread streams four rows of P, 4 k-values at a time
 template <typename T, typename I, int SRC, bool TRANS>
 __global__ void __launch_bounds__(256) small_proj_kernel(SmallGroupArgs a, const float* frows, float* out) {
     extern __shared__ __align__(16) float Xs[];                 // dim * SG_LD floats
     const int g = blockIdx.x;
     if (g >= *a.n_groups) return;
-    const int t = threadIdx.x, dim = a.dim;
+    const int dim = a.dim;
+    const int cg = threadIdx.x & 63, rg = threadIdx.x >> 6;     // column group, row group (uniform within a warp)
     const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
     const T* P = reinterpret_cast<const T*>(a.proj) + a.rel_uniq[g] * (long long)dim * dim;
-    const bool col_ok = t < dim;
-    for (int m0 = s; m0 < e; m0 += SG_MB) {
-        const int rows = min(SG_MB, e - m0);
-        const int nq = (rows + 3) >> 2;
-        __syncthreads();                                        // the previous block's reads of Xs are done
-        sg_stage_rows<T, I, SRC, SG_LD, SG_MB>(a, frows, m0, rows, Xs);
+    const bool col_ok = 4 * cg < dim;                           // dim % 4 == 0
+    for (int m0 = s; m0 < e; m0 += SG_ROWS) {
+        const int rows = min(SG_ROWS, e - m0);
+        const int my_rows = min(16, rows - 16 * rg);            // rows of this thread's row group that exist (may be <= 0)
+        const int nq = (my_rows + 3) >> 2;
+        __syncthreads();                                        // the previous pass's reads of Xs are done
+        sg_stage_transposed<T, I, SRC>(a, frows, m0, rows, Xs);
         __syncthreads();
-        float acc[SG_MB];
+        if (!col_ok || my_rows <= 0) continue;                  // no barrier below this point inside the pass
+        float acc[16][4];
 #pragma unroll
-        for (int m = 0; m < SG_MB; ++m) acc[m] = 0.f;
-        if (col_ok) {
-            if (!TRANS) {
-                const T* pc = P + t;
-#pragma unroll 4
-                for (int k = 0; k < dim; ++k) sg_fma_rows<SG_LD>(acc, Xs + k * SG_LD, sg_get(pc + (long long)k * dim), nq);
-            } else {
-                const T* pr = P + (long long)t * dim;
-                for (int k = 0; k < dim; k += 4) {              // dim % 4 == 0
-                    const float4 p4 = load_quad<T, true>(pr, k >> 2, dim);
-                    sg_fma_rows<SG_LD>(acc, Xs + (k + 0) * SG_LD, p4.x, nq);
-                    sg_fma_rows<SG_LD>(acc, Xs + (k + 1) * SG_LD, p4.y, nq);
-                    sg_fma_rows<SG_LD>(acc, Xs + (k + 2) * SG_LD, p4.z, nq);
-                    sg_fma_rows<SG_LD>(acc, Xs + (k + 3) * SG_LD, p4.w, nq);
-                }
+        for (int r = 0; r < 16; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; acc[r][2] = 0.f; acc[r][3] = 0.f; }
+        const float* xr = Xs + 16 * rg;
+        if (!TRANS) {
+            const T* pc = P + 4 * cg;
+#pragma unroll 2
+            for (int k = 0; k < dim; ++k) sg_fma_tile(acc, xr + k * SG_LD, load_quad<T, true>(pc + (long long)k * dim, 0, 4), nq);
+        } else {
+            const T* pr = P + (long long)(4 * cg) * dim;
+            for (int k = 0; k < dim; k += 4) {
+                const float4 p0 = load_quad<T, true>(pr, k >> 2, dim), p1 = load_quad<T, true>(pr + dim, k >> 2, dim);
+                const float4 p2 = load_quad<T, true>(pr + 2 * dim, k >> 2, dim), p3 = load_quad<T, true>(pr + 3 * dim, k >> 2, dim);
+                sg_fma_tile(acc, xr + (k + 0) * SG_LD, make_float4(p0.x, p1.x, p2.x, p3.x), nq);
+                sg_fma_tile(acc, xr + (k + 1) * SG_LD, make_float4(p0.y, p1.y, p2.y, p3.y), nq);
+                sg_fma_tile(acc, xr + (k + 2) * SG_LD, make_float4(p0.z, p1.z, p2.z, p3.z), nq);
+                sg_fma_tile(acc, xr + (k + 3) * SG_LD, make_float4(p0.w, p1.w, p2.w, p3.w), nq);
             }
-#pragma unroll
-            for (int m = 0; m < SG_MB; ++m)
-                if (m < rows) out[(long long)a.rel_perm[m0 + m] * dim + t] = acc[m];       // 256 threads: one contiguous row
         }
+#pragma unroll
+        for (int r = 0; r < 16; ++r)
+            if (r < my_rows)
+                *reinterpret_cast<float4*>(out + (long long)a.rel_perm[m0 + 16 * rg + r] * dim + 4 * cg) =
+                    make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
     }
 }
 
-// dP[g][i][j] = sum over the group's rows m of X[m][i] * G[m][j].  Thread t owns column j = t and keeps G[m][t] of up to
-// 64 rows in registers; groups with more rows take further passes that add to what the earlier ones stored.
+// dP[g][i][j] = sum over the group's rows m of X[m][i] * G[m][j].  Up to 32 rows of X and of G sit row-major in shared
+// memory; the output is produced in four blocks of 64 i-values, a thread owning 16 i x 4 j of a block: per row m four
+// 128-bit broadcasts of X[m][i0..i0+15] and one 128-bit read of G[m][4cg..].  Groups with more than 32 rows take further
+// passes that add to what the earlier ones stored.
 template <typename T, typename I>
 __global__ void __launch_bounds__(256) small_dproj_kernel(SmallGroupArgs a, const float* grows, float* dproj) {
-    extern __shared__ __align__(16) float Xs[];                 // dim * SG_LD2 floats
+    extern __shared__ __align__(16) float sm[];                 // X rows: SG_DP_ROWS * dim, then G rows: SG_DP_ROWS * dim
     const int g = blockIdx.x;
     if (g >= *a.n_groups) return;
-    const int t = threadIdx.x, dim = a.dim;
+    const int dim = a.dim;
+    const int cg = threadIdx.x & 63, ig = threadIdx.x >> 6;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int s = a.rel_seg[g], e = a.rel_seg[g + 1];
+    float* Xr = sm;
+    float* Gr = sm + SG_DP_ROWS * dim;
     float* out = dproj + (long long)g * dim * dim;
-    const bool col_ok = t < dim;
-    for (int m0 = s; m0 < e; m0 += SG_MAXROWS) {
-        const int rows = min(SG_MAXROWS, e - m0);
-        const int nq = (rows + 3) >> 2;
+    const bool col_ok = 4 * cg < dim;
+    for (int m0 = s; m0 < e; m0 += SG_DP_ROWS) {
+        const int rows = min(SG_DP_ROWS, e - m0);
         __syncthreads();
-        sg_stage_rows<T, I, 0, SG_LD2, SG_MAXROWS>(a, nullptr, m0, rows, Xs);
+        for (int m = w; m < rows; m += 8) {
+            const int tri = a.rel_perm[m0 + m];
+            const T* xrow = reinterpret_cast<const T*>(a.ent) + load_id<I>(a.h, tri) * dim;
+            const float* grow = grows + (long long)tri * dim;
+            for (int k = lane; k < dim; k += 32) { Xr[m * dim + k] = sg_get(xrow + k); Gr[m * dim + k] = __ldg(grow + k); }
+        }
         __syncthreads();
         if (!col_ok) continue;
-        float gm[SG_MAXROWS];
+        for (int ib = 0; ib < dim; ib += 64) {
+            const int i0 = ib + 16 * ig;
+            if (i0 >= dim) continue;
+            float acc[16][4];
 #pragma unroll
-        for (int m = 0; m < SG_MAXROWS; ++m) gm[m] = m < rows ? __ldg(grows + (long long)a.rel_perm[m0 + m] * dim + t) : 0.f;
-        for (int i = 0; i < dim; ++i) {
-            const float* xi = Xs + i * SG_LD2;
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            for (int r = 0; r < 16; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; acc[r][2] = 0.f; acc[r][3] = 0.f; }
+            for (int m = 0; m < rows; ++m)
+                sg_fma_tile(acc, Xr + m * dim + i0, *reinterpret_cast<const float4*>(Gr + m * dim + 4 * cg), 4);
 #pragma unroll
-            for (int q = 0; q < SG_MAXROWS / 4; ++q) {
-                if (q < nq) {
-                    const float4 x = *reinterpret_cast<const float4*>(xi + 4 * q);
-                    s0 = fmaf(x.x, gm[4 * q + 0], s0);
-                    s1 = fmaf(x.y, gm[4 * q + 1], s1);
-                    s2 = fmaf(x.z, gm[4 * q + 2], s2);
-                    s3 = fmaf(x.w, gm[4 * q + 3], s3);
+            for (int r = 0; r < 16; ++r) {
+                if (i0 + r < dim) {
+                    float4* o = reinterpret_cast<float4*>(out + (long long)(i0 + r) * dim + 4 * cg);
+                    float4 v = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+                    if (m0 != s) { const float4 old = *o; v = v + old; }
+                    *o = v;
                 }
             }
-            const float v = (s0 + s1) + (s2 + s3);
-            float* o = out + (long long)i * dim + t;
-            *o = (m0 == s) ? v : *o + v;
         }
     }
 }
-
 
 // ---- host ---------------------------------------------------------------------------------------------------------
 static GroupArgs group_args(const kge_problem* p, const kge_tensors* t) {
@@ -429,6 +448,25 @@ static SmallGroupArgs small_args(const kge_problem* p, const kge_tensors* t) {
     a.rel_uniq = (const long long*)t->rel_uniq; a.n_groups = (const long long*)t->n_rel_groups; a.dim = p->dim;
     return a;
 }
+// Dynamic shared memory of the small-group kernels at dim 256: 68 KB (projections), 64 KB (matrix gradient) - above the
+// 48 KB default, so every instantiation is opted in once per device.
+static int small_opt_in() {
+    static std::atomic<bool> opted[128];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status(cudaGetLastError(), "cudaGetDevice");
+    if (dev >= 0 && dev < 128 && opted[dev].load(std::memory_order_acquire)) return 0;
+    const int bytes = 256 * SG_LD * (int)sizeof(float);
+    cudaError_t e = cudaSuccess;
+#define KGE_OPT(T, I)                                                                                                              \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(small_proj_kernel<T, I, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(small_proj_kernel<T, I, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);  \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(small_dproj_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    KGE_OPT(float, int64_t) KGE_OPT(float, int32_t) KGE_OPT(__nv_bfloat16, int64_t) KGE_OPT(__nv_bfloat16, int32_t)
+#undef KGE_OPT
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(small-group kernels)");
+    if (dev >= 0 && dev < 128) opted[dev].store(true, std::memory_order_release);
+    return 0;
+}
 #define KGE_SMALL_DISPATCH(CALL)                                                                  \
     do {                                                                                          \
         if (p->dtype == KGE_F32) { if (p->id_bits == 64) { CALL(float, int64_t); } else { CALL(float, int32_t); } }            \
@@ -440,6 +478,7 @@ int launch_rescal_anchors(const kge_problem* p, const kge_tensors* t, float* anc
     if (small_groups(p)) {
         const SmallGroupArgs sa = small_args(p, t);
         const size_t smem = (size_t)p->dim * SG_LD * sizeof(float);
+        if (int rc = small_opt_in()) return rc;
 #define KGE_CALL(T, I) small_proj_kernel<T, I, 0, false><<<group_bound(p), 256, smem, s>>>(sa, nullptr, anchors)
         KGE_SMALL_DISPATCH(KGE_CALL);
 #undef KGE_CALL
@@ -460,23 +499,12 @@ int launch_rescal_backward(const kge_problem* p, const kge_tensors* t, const flo
     if (p->batch <= 0) return 0;
     if (small_groups(p)) {
         const SmallGroupArgs sa = small_args(p, t);
-        const size_t smem = (size_t)p->dim * SG_LD * sizeof(float), smem2 = (size_t)p->dim * SG_LD2 * sizeof(float);
+        const size_t smem = (size_t)p->dim * SG_LD * sizeof(float), smem2 = (size_t)2 * SG_DP_ROWS * p->dim * sizeof(float);
+        if (int rc = small_opt_in()) return rc;
 #define KGE_CALL(T, I) small_proj_kernel<T, I, 1, true><<<group_bound(p), 256, smem, s>>>(sa, ga, g_head)
         KGE_SMALL_DISPATCH(KGE_CALL);
 #undef KGE_CALL
         KGE_LAUNCH_CHECK("small_proj_kernel(g_head)");
-        // 68 KB of dynamic shared memory at dim 256: above the 48 KB default, opted in per device
-        static std::atomic<bool> opted[128];
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status(cudaGetLastError(), "cudaGetDevice");
-        if (dev < 0 || dev >= 128 || !opted[dev].load(std::memory_order_acquire)) {
-            cudaError_t e = cudaSuccess;
-#define KGE_CALL(T, I) if (e == cudaSuccess) e = cudaFuncSetAttribute(small_dproj_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * SG_LD2 * (int)sizeof(float))
-            KGE_CALL(float, int64_t); KGE_CALL(float, int32_t); KGE_CALL(__nv_bfloat16, int64_t); KGE_CALL(__nv_bfloat16, int32_t);
-#undef KGE_CALL
-            if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(small_dproj_kernel)");
-            if (dev >= 0 && dev < 128) opted[dev].store(true, std::memory_order_release);
-        }
 #define KGE_CALL(T, I) small_dproj_kernel<T, I><<<group_bound(p), 256, smem2, s>>>(sa, ga, dproj)
         KGE_SMALL_DISPATCH(KGE_CALL);
 #undef KGE_CALL

@@ -169,12 +169,14 @@ class KgeStep:
     ent_local holds rows [rank * rows_per_rank, ...) of the global (n_ent, dim) table (the whole table when
     world == 1).  `group` is a torch.distributed process group (NCCL) when world > 1; relation tables are replicated.
     optimizer: None (gradients are returned, tables untouched), ("sgd", lr) or ("adagrad", lr, eps): applied to the touched
-    rows at their owner at the end of the step (each scorer's gradient as its own update)."""
+    rows at their owner at the end of the step (each scorer's gradient as its own update).
+    relation_partitioned: every rank's batches hold only relations that no other rank sees (see cuke_b200.partition):
+    relation-side gradients stay local (no all-reduce), which is what makes TransR / RESCAL usable on several GPUs."""
 
     def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
                  neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None,
                  precision: str = "fp32", fused: bool = True, rel2: Optional[Dict[str, torch.Tensor]] = None,
-                 optimizer: Optional[tuple] = None):
+                 optimizer: Optional[tuple] = None, relation_partitioned: bool = False):
         self.models, self.ent_local, self.rel, self.rel2 = list(models), ent_local, rel, rel2 or {}
         self.fused = fused                    # use the fused forward+loss+backward call where the scorer supports it
         self.n_ent, self.rank, self.world, self.group = int(n_ent), int(rank), int(world), group
@@ -183,9 +185,13 @@ class KgeStep:
         self.n_rel = {m: (rel[m] if m in rel else self.rel2[m]).shape[0] for m in self.models}
         if len(set(self.n_rel.values())) != 1:
             raise ValueError("the scorers of a step share one relation id space")
+        # relation_partitioned: the batches were split by relation (cuke_b200.partition), so every relation's triples are
+        # scored by ONE rank; relation-side gradients then need no all-reduce and each rank updates only its own relations
+        self.relation_partitioned = bool(relation_partitioned)
         for m in self.models:
-            if m in MATRIX_MODELS and world > 1:
-                raise NotImplementedError("relation-matrix scorers run on one GPU per table replica (their matrices are not all-reduced)")
+            if m in MATRIX_MODELS and world > 1 and not self.relation_partitioned:
+                raise NotImplementedError("relation-matrix scorers on several GPUs need relation-partitioned batches "
+                                          "(relation_partitioned=True): their dim x dim gradients are not all-reduced")
             if m in ("TransH", "TransR", "RESCAL") and m not in self.rel2:
                 raise ValueError(f"{m} needs rel2[{m!r}]")
         self.optimizer = optimizer
@@ -296,7 +302,7 @@ class KgeStep:
 
     def _allreduce(self, dense: torch.Tensor, main) -> None:
         """N GPUs: sum of a replicated table's dense gradient over the ranks, on the side stream."""
-        if self.exchange is None:
+        if self.exchange is None or self.relation_partitioned:
             return
         import torch.distributed as dist
         ready = torch.cuda.Event()

@@ -287,6 +287,30 @@ KGE_API int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg,
 KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank,
                      int32_t world, int64_t* counts, kge_stream_t stream);
 
+/* ---- general expressions ----------------------------------------------------------------------------------------
+ * Evaluates, for every batch element i, a small register program over per-element VECTOR registers (dim floats) and
+ * SCALAR registers: the target of the Python front-end for expressions of the reference's batched operators that are
+ * not one of the seven score functions (what cuke's generator does for any composition of bvv / bsv / bvm / bov / bsm
+ * over gathered rows, apps/kge/kge.py:13-84, pycuke1/codegen/gpu.py:182-236).  Instructions are (op, dst, a, b, c):
+ *    0 GATHER  v[dst] = tables[a][ids[b][i]]           1..4 VADD VSUB VMUL VDIV  v[dst] = v[a] op v[b]
+ *    5 SPLAT   v[dst][:] = s[a]                        6 DOT   s[dst] = v[a] . v[b]
+ *    7..10 SADD SSUB SMUL SDIV  s[dst] = s[a] op s[b]  11 SCONST  s[dst] = float with bit pattern a
+ *   12 VECMAT  v[dst][j] = sum_k v[a][k] M[k][j]       13 COLSUM  v[dst][j] = sum_k M[k][j] (M = tables[a][ids[b][i]])
+ *   14 MATVEC  v[dst][k] = sum_j M[k][j] v[a][j]       (12, 14: M = tables[b][ids[c][i]], a (dim, dim) matrix per row id)
+ *   15 ROW     v[dst] = tables[a][i]  ((batch, dim))   16 LOADS  s[dst] = tables[a][i]  ((batch,) operand)
+ * Result (out_kind): 0 vector v[out_a] -> out (batch, dim); 1 scalar s[out_a] -> out (batch,); 2 outer product
+ * s[out_s] * v[out_a] (x) v[out_b] -> out (batch, dim, dim); 3 s[out_s] * tables[out_table][ids[out_ids][i]] -> out
+ * (batch, dim, dim); out_s < 0 means no scalar factor.  Tables are fp32, row-major, (rows, dim) or (rows, dim, dim).
+ * Limits: 64 instructions, 16 vector and 16 scalar registers, 8 tables, 4 id arrays, dim <= 1024 and
+ * n_vreg * dim * 4 bytes <= 48 KB. */
+typedef struct kge_program {
+    int32_t n_ops, n_vreg, n_sreg;
+    int32_t out_kind, out_a, out_b, out_s, out_table, out_ids;
+    int32_t ops[64][5];
+} kge_program;
+KGE_API int kge_eval_program(const kge_program* prog, int32_t dim, int64_t batch, const float* const* tables, int32_t n_tables,
+                             const void* const* ids, int32_t id_bits, int32_t n_ids, float* out, kge_stream_t stream);
+
 /* ---- batch ids generated on the device ---------------------------------------------------------------------
  * Counter-based sampling (Philox4x32-10): element i of stream `stream_id` under `seed` is a pure function of
  * (seed, stream_id, i) - counter words (i low, i high, stream_id, 0), key words (seed low, seed high), output words
