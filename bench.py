@@ -246,6 +246,52 @@ def workload_config(cfg, models, n_gpus):
 # ---------------------------------------------------------------------------------------------------------
 # side measurements: the parity configurations c1-c4, one scorer at a time, single GPU
 # ---------------------------------------------------------------------------------------------------------
+def reference_gpu_anchor(cfg, sc, h, r, t, neg, flush, steps):
+    """GPU against GPU on c1's flattened batch (positives + flattened negatives, the reference's own layout,
+    apps/kge/data/data_init.py:55-61): the kernel the reference's generator emits for TransE without relation reuse
+    (apps/kge/test_cuke.py:27-54; built ahead of time for sm_100 by oracle/build_ref.py --cuda-anchor) beside this
+    library's drop-in forward producing the same (batch, dim) vectors.  Both are timed as bare calls with CUDA events
+    (the reference's own timing loop also pays a file compare and a module lookup per call, pycuke1/run/gpu.py:4-19)."""
+    import torch
+    from oracle import oracle
+    if not oracle.have_ref_cuda():
+        return {"unavailable": "oracle/_ref/ref_transE_cuda.so was not built (needs the reference checkout and nvcc)"}
+    try:
+        mod = oracle.load_ref_cuda()
+        fh, fr, ft = oracle.flatten(h.cpu().numpy(), r.cpu().numpy(), t.cpu().numpy(), neg.cpu().numpy(), "per_triple", 0)
+        dev = h.device
+        ah = torch.cat([h, torch.from_numpy(fh).to(dev)]); ar = torch.cat([r, torch.from_numpy(fr).to(dev)])
+        at = torch.cat([t, torch.from_numpy(ft).to(dev)])
+        n, d = ah.numel(), sc.dim
+        assert n % 16 == 0
+        call_ref = lambda: mod.run(n, d, sc.ent.shape[0], sc.ent, ah, at, sc.rel.shape[0], sc.rel, ar)
+        call_ours = lambda: sc.ref_forward(ah, ar, at)
+        same = bool(torch.allclose(call_ref(), call_ours(), rtol=1e-6, atol=1e-7))
+
+        def timed(fn, cold):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            tot = 0.0
+            for _ in range(max(steps, 5)):
+                if cold:
+                    flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                tot += e0.elapsed_time(e1)
+            return tot / max(steps, 5)
+        res = {"triples": n, "outputs_equal": same,
+               "reference_ms_cold_l2": timed(call_ref, True), "reference_ms_warm_l2": timed(call_ref, False),
+               "ours_ms_cold_l2": timed(call_ours, True), "ours_ms_warm_l2": timed(call_ours, False),
+               "what": "(batch, dim) vectors h - t + r of the flattened batch; reference = cuke's generated kernel (grid batch/16, "
+                       "block 32x16, scalar loads), ours = kge_ref_forward"}
+        res["speedup_cold_l2"] = res["reference_ms_cold_l2"] / res["ours_ms_cold_l2"]
+        return res
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
 def side_measure(cname, steps, warmup, precision, cpu_seconds=0.0):
     """Times forward (and backward + gradient reduction where the configuration has one) of a parity configuration on
     one GPU, one scorer at a time; returns one record per scorer with the HBM view of the roofline and, if
@@ -319,6 +365,8 @@ def side_measure(cname, steps, warmup, precision, cpu_seconds=0.0):
             _, bf16_peak, _ = peaks()
             rec["roofline"]["tensor"] = {"useful_flops": flops, "achieved": flops / (ms_cold * 1e-3) / 1e12, "peak": bf16_peak,
                                          "unit": "TFLOP/s", "frac": flops / (ms_cold * 1e-3) / 1e12 / bf16_peak}
+        if cname == "c1":
+            rec["reference_gpu_kernel"] = reference_gpu_anchor(cfg, sc, h, r, t, neg, flush, steps)
         if cpu_seconds > 0:
             try:
                 res = cpu_reference_rate(cfg, [model], seconds=cpu_seconds, steps=2, warmup=1)

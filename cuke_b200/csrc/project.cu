@@ -343,19 +343,36 @@ __global__ void __launch_bounds__(256) small_proj_kernel(SmallGroupArgs a, const
 #pragma unroll
         for (int r = 0; r < 16; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; acc[r][2] = 0.f; acc[r][3] = 0.f; }
         const float* xr = Xs + 16 * rg;
+        // The matrix comes straight from HBM (each element is used by this group only): eight 16-byte loads per thread are
+        // requested before the first is consumed, so that a CTA keeps ~24 KB in flight and the loop is not a chain of
+        // memory round trips.
         if (!TRANS) {
             const T* pc = P + 4 * cg;
-#pragma unroll 2
-            for (int k = 0; k < dim; ++k) sg_fma_tile(acc, xr + k * SG_LD, load_quad<T, true>(pc + (long long)k * dim, 0, 4), nq);
+            for (int k0 = 0; k0 < dim; k0 += 8) {
+                float4 pv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) pv[u] = k0 + u < dim ? load_quad<T, true>(pc + (long long)(k0 + u) * dim, 0, 4) : f4(0.f);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) if (k0 + u < dim) sg_fma_tile(acc, xr + (k0 + u) * SG_LD, pv[u], nq);
+            }
         } else {
             const T* pr = P + (long long)(4 * cg) * dim;
-            for (int k = 0; k < dim; k += 4) {
-                const float4 p0 = load_quad<T, true>(pr, k >> 2, dim), p1 = load_quad<T, true>(pr + dim, k >> 2, dim);
-                const float4 p2 = load_quad<T, true>(pr + 2 * dim, k >> 2, dim), p3 = load_quad<T, true>(pr + 3 * dim, k >> 2, dim);
-                sg_fma_tile(acc, xr + (k + 0) * SG_LD, make_float4(p0.x, p1.x, p2.x, p3.x), nq);
-                sg_fma_tile(acc, xr + (k + 1) * SG_LD, make_float4(p0.y, p1.y, p2.y, p3.y), nq);
-                sg_fma_tile(acc, xr + (k + 2) * SG_LD, make_float4(p0.z, p1.z, p2.z, p3.z), nq);
-                sg_fma_tile(acc, xr + (k + 3) * SG_LD, make_float4(p0.w, p1.w, p2.w, p3.w), nq);
+            for (int k0 = 0; k0 < dim; k0 += 8) {
+                float4 pv[2][4];
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) pv[u][c] = load_quad<T, true>(pr + (long long)c * dim, (k0 >> 2) + u, dim);      // zero past dim
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int k = k0 + 4 * u;
+                    if (k < dim) {
+                        sg_fma_tile(acc, xr + (k + 0) * SG_LD, make_float4(pv[u][0].x, pv[u][1].x, pv[u][2].x, pv[u][3].x), nq);
+                        sg_fma_tile(acc, xr + (k + 1) * SG_LD, make_float4(pv[u][0].y, pv[u][1].y, pv[u][2].y, pv[u][3].y), nq);
+                        sg_fma_tile(acc, xr + (k + 2) * SG_LD, make_float4(pv[u][0].z, pv[u][1].z, pv[u][2].z, pv[u][3].z), nq);
+                        sg_fma_tile(acc, xr + (k + 3) * SG_LD, make_float4(pv[u][0].w, pv[u][1].w, pv[u][2].w, pv[u][3].w), nq);
+                    }
+                }
             }
         }
 #pragma unroll

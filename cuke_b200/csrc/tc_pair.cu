@@ -1515,70 +1515,48 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
     }
     const int dim = a.dim;
     const __nv_bfloat16* E = reinterpret_cast<const __nv_bfloat16*>(a.ent);
-    // a warp takes rows warp, warp + 8, ...; four rows at a time, so that the id chains (rel_perm -> h / t / neg -> row) and
-    // the row loads of four rows are in flight together
-    for (int r0 = warp; r0 < UM_BM; r0 += 32) {
-        const __nv_bfloat16 *pa[4], *pb[4];
-        int tri[4], jj[4];
-        bool live[4];
+    for (int rr = warp; rr < UM_BM; rr += 8) {
+        const long long prow = (long long)tt.x + rr;
+        if (rr >= valid) {                                                       // padding row: zeros, no score, no gradient
+            for (int k = lane * 4; k < dim; k += 128) *reinterpret_cast<uint2*>(rows_out + prow * dim + k) = make_uint2(0u, 0u);
+            if (lane == 0) { row_dst[prow] = -1; if (coef) coef[prow] = 0.f; }
+            continue;
+        }
+        const long long rho = first + rr;                                        // row within the group
+        const int p = pl.rel_seg[g] + (int)(rho / pl.per), j = (int)(rho % pl.per);
+        const int i = pl.rel_perm[p];
+        const __nv_bfloat16* hrow = E + load_id<I>(a.h, i) * dim;
+        const __nv_bfloat16* trow = E + load_id<I>(a.t, i) * dim;
+        const __nv_bfloat16 *pa = hrow, *pb = trow;
+        if (j > 0) {
+            const __nv_bfloat16* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * dim;
+            if (j - 1 < a.n_neg_head) pa = x; else pb = x;
+        }
+        Row<NV> ra, rb;
+        load_row<__nv_bfloat16, NV, true>(ra, pa, dim, lane);
+        load_row<__nv_bfloat16, NV, true>(rb, pb, dim, lane);
+        __nv_bfloat16* out = rows_out + prow * dim;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int rr = r0 + 8 * u;
-            live[u] = rr < valid;
-            pa[u] = pb[u] = E;
-            tri[u] = 0; jj[u] = 0;
-            if (live[u]) {
-                const long long rho = first + rr;                                    // row within the group
-                const int p = pl.rel_seg[g] + (int)(rho / pl.per), j = (int)(rho % pl.per);
-                const int i = pl.rel_perm[p];
-                tri[u] = i; jj[u] = j;
-                pa[u] = E + load_id<I>(a.h, i) * dim;
-                pb[u] = E + load_id<I>(a.t, i) * dim;
-                if (j > 0) {
-                    const __nv_bfloat16* x = E + load_id<I>(a.neg, (long long)i * a.n_neg + (j - 1)) * dim;
-                    if (j - 1 < a.n_neg_head) pa[u] = x; else pb[u] = x;
-                }
+        for (int q = 0; q < NV; ++q) {
+            const int k = 4 * (lane + 32 * q);
+            if (k < dim) {
+                const float4 d = ra.v[q] - rb.v[q];
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(d.x, d.y), p1 = __floats2bfloat162_rn(d.z, d.w);
+                uint2 u;
+                u.x = *reinterpret_cast<unsigned*>(&p0); u.y = *reinterpret_cast<unsigned*>(&p1);
+                *reinterpret_cast<uint2*>(out + k) = u;
             }
         }
-        Row<NV> ra[4], rb[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (live[u]) { load_row<__nv_bfloat16, NV, true>(ra[u], pa[u], dim, lane); load_row<__nv_bfloat16, NV, true>(rb[u], pb[u], dim, lane); }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int rr = r0 + 8 * u;
-            if (rr >= UM_BM) continue;
-            const long long prow = (long long)tt.x + rr;
-            __nv_bfloat16* out = rows_out + prow * dim;
-            if (!live[u]) {                                                          // padding row: zeros, no score, no gradient
-                for (int k = lane * 4; k < dim; k += 128) *reinterpret_cast<uint2*>(out + k) = make_uint2(0u, 0u);
-                if (lane == 0) { row_dst[prow] = -1; if (coef) coef[prow] = 0.f; }
-                continue;
-            }
-#pragma unroll
-            for (int q = 0; q < NV; ++q) {
-                const int k = 4 * (lane + 32 * q);
-                if (k < dim) {
-                    const float4 d = ra[u].v[q] - rb[u].v[q];
-                    __nv_bfloat162 p0 = __floats2bfloat162_rn(d.x, d.y), p1 = __floats2bfloat162_rn(d.z, d.w);
-                    uint2 w2;
-                    w2.x = *reinterpret_cast<unsigned*>(&p0); w2.y = *reinterpret_cast<unsigned*>(&p1);
-                    *reinterpret_cast<uint2*>(out + k) = w2;
-                }
-            }
-            if (lane == 0) {
-                const int i = tri[u], j = jj[u];
-                // backward: a tail-replaced negative receives minus the row gradient; the side is folded into the slot number
-                // here (+ kTailSide) so that the scatter epilogue needs no division per row
-                const bool tail_side = coef != nullptr && j > 0 && j - 1 >= a.n_neg_head;
-                row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1) + (tail_side ? kTailSide : 0);
-                if (coef) {      // dL/dv = (dS / S) v
-                    const float sc = j == 0 ? a.pos[i] : a.negs[(long long)i * a.n_neg + (j - 1)];
-                    const float ds = j == 0 ? a.dpos[i] : a.dneg[(long long)i * a.n_neg + (j - 1)];
-                    coef[prow] = sc != 0.f ? ds / sc : 0.f;
-                    if (j == 0) trow0[i] = (int)prow;
-                }
+        if (lane == 0) {
+            // backward: a tail-replaced negative receives minus the row gradient; the side is folded into the slot number
+            // here (+ kTailSide) so that the scatter epilogue needs no division per row
+            const bool tail_side = coef != nullptr && j > 0 && j - 1 >= a.n_neg_head;
+            row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1) + (tail_side ? kTailSide : 0);
+            if (coef) {      // dL/dv = (dS / S) v
+                const float sc = j == 0 ? a.pos[i] : a.negs[(long long)i * a.n_neg + (j - 1)];
+                const float ds = j == 0 ? a.dpos[i] : a.dneg[(long long)i * a.n_neg + (j - 1)];
+                coef[prow] = sc != 0.f ? ds / sc : 0.f;
+                if (j == 0) trow0[i] = (int)prow;
             }
         }
     }

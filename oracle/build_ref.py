@@ -23,7 +23,10 @@ with torch.utils.cpp_extension.  Two variants per scorer:
 Outputs go only to oracle/_ref/ (git-ignored; it travels to the GPU box as built files).
 No reference source is copied: the .cpp files are outputs of running the reference.
 
-Usage:  python oracle/build_ref.py [--ref <cuke checkout>] [--only transE,...] [--threads T]
+  ref_transE_cuda  (--cuda-anchor) the reference's generated CUDA kernel for TransE without relation reuse, for sm_100:
+                   the GPU-against-GPU anchor of the benchmark's side records.
+
+Usage:  python oracle/build_ref.py [--ref <cuke checkout>] [--only transE,...] [--threads T] [--cuda-anchor]
 """
 from __future__ import annotations
 
@@ -161,6 +164,39 @@ def compile_all(made):
         print("built", modname, flush=True)
 
 
+def generate_cuda_anchor(ref_root: str):
+    """The reference's OWN GPU kernel for one scorer, as a GPU-against-GPU anchor: TransE without relation reuse, exactly as
+    apps/kge/test_cuke.py:27-54 builds it, printed by pycuke1.codegen.gpu.print_cuda (pycuke1/codegen/gpu.py:182-236) under
+    the reference's default pass list (apps/kge/kge.py:226) and compiled for sm_100.  Only this variant: it has no shared
+    memory and no inspector, its index arithmetic stays inside the batch for batch % 16 == 0 (grid batch / 16, block
+    32 x 16, rows 16 b .. 16 b + 15 per block)."""
+    sys.path[:0] = [ref_root, os.path.join(ref_root, "apps", "kge")]
+    sys.dont_write_bytecode = True
+    import importlib
+    import kge  # noqa
+    importlib.reload(kge)                      # restores transform.passes to the reference's default GPU pass list
+    from pycuke1.asg import Tensor, Var
+    from pycuke1.asg2ir import gen_ir
+    from pycuke1.codegen import gpu
+    nnodes, nedges, dim, batch_size = Var(name="nnodes"), Var(name="nedges"), Var(name="dim"), Var(name="batch_size")
+    Eemb, Remb = Tensor((nnodes, dim), name="Eemb"), Tensor((nedges, dim), name="Remb")
+    h = Tensor((batch_size,), dtype="int", name="h"); t = Tensor((batch_size,), dtype="int", name="t")
+    r = Tensor((batch_size,), dtype="int", name="r")
+    code = gpu.print_cuda(gen_ir(Eemb[h] - Eemb[t] + Remb[r]))
+    os.makedirs(OUT, exist_ok=True)
+    path = os.path.join(OUT, "ref_transE_cuda.cu")
+    with open(path, "w") as f:
+        f.write(code)
+    os.environ["CXX"], os.environ["CC"] = "/usr/bin/g++", "/usr/bin/gcc"
+    os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0"
+    from torch.utils.cpp_extension import load
+    bdir = os.path.join(OUT, "build_ref_transE_cuda")
+    os.makedirs(bdir, exist_ok=True)
+    load(name="ref_transE_cuda", sources=[path], build_directory=bdir, verbose=False)
+    os.replace(os.path.join(bdir, "ref_transE_cuda.so"), os.path.join(OUT, "ref_transE_cuda.so"))
+    print("built ref_transE_cuda", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("CUKE_REFERENCE", os.path.join(HERE, "..", "..", "reference")),
@@ -169,12 +205,17 @@ def main():
     ap.add_argument("--threads", type=int, default=256,
                     help="num_threads() written into the OpenMP pragma; OMP_NUM_THREADS / "
                          "omp_set_num_threads cannot raise it, the runtime clamps it to the cores")
+    ap.add_argument("--cuda-anchor", action="store_true", help="also build the reference's generated TransE CUDA kernel (oracle/_ref/ref_transE_cuda.so)")
+    ap.add_argument("--cuda-anchor-only", action="store_true")
     a = ap.parse_args()
     if not os.path.isdir(a.ref):
         print("reference checkout not present; keeping prebuilt oracle/_ref as is")
         return 0
-    made = generate(a.ref, a.only.split(","), a.threads)
-    compile_all(made)
+    if not a.cuda_anchor_only:
+        made = generate(a.ref, a.only.split(","), a.threads)
+        compile_all(made)
+    if a.cuda_anchor or a.cuda_anchor_only:
+        generate_cuda_anchor(a.ref)
     return 0
 
 

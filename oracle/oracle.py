@@ -213,3 +213,21 @@ def ref_run(model: str, E, R, P2, h, r, t, omp: bool = False):
         Rre, Rim = R[:, 0::2].contiguous(), R[:, 1::2].contiguous()
         return mod.run(B, d // 2, ne, Ere, h, nr, Rre, r, Eim, Rim, t)
     raise KeyError(model)
+
+
+def have_ref_cuda() -> bool:
+    return os.path.exists(os.path.join(REF_DIR, "ref_transE_cuda.so"))
+
+
+def load_ref_cuda():
+    """The reference's own generated CUDA kernel for TransE without relation reuse (oracle/build_ref.py --cuda-anchor):
+    module.run(batch_size, dim, nnodes, Eemb, h, t, nedges, Remb, r) with CUDA float32 tables and int64 ids, batch a
+    multiple of 16; returns the (batch, dim) vectors h - t + r."""
+    name = "ref_transE_cuda"
+    if name not in _ref_mods:
+        import torch  # noqa: F401
+        spec = importlib.util.spec_from_file_location(name, os.path.join(REF_DIR, name + ".so"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _ref_mods[name] = mod
+    return _ref_mods[name]
