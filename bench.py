@@ -316,14 +316,19 @@ def side_measure(cname, steps, warmup, precision, cpu_seconds=0.0):
         d = synth.row_floats(cfg, model)
         ids = scoring.entity_id_list(h, t, neg)
 
+        # fwd+bwd configurations run through the same step pipeline as the headline workload (inspector, dedup staging,
+        # forward + loss + backward - fused where the scorer has a fused call -, entity- and relation-side reductions);
+        # the forward-only configuration c1 is the bare scoring call
+        stepper = None
+        if backward:
+            from cuke_b200.pipeline import KgeStep
+            stepper = KgeStep([model], sc.ent, {} if sc.rel is None else {model: sc.rel}, cfg.n_ent, cfg.neg_mode,
+                              cfg.n_neg_head, cfg.chunk, precision=precision, rel2={} if sc.rel2 is None else {model: sc.rel2})
+
         def step(bwd=True):
-            pos, negs, rinsp = sc.forward(h, r, t, neg)
-            if backward and bwd:
-                loss, dpos, dneg = scoring.logistic_loss(pos, negs)
-                sg = sc.backward(h, r, t, neg, pos, negs, dpos, dneg, rinsp)
-                insp = scoring.inspect(ids, cfg.n_ent)
-                scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)
-            return pos
+            if stepper is not None:
+                return stepper.step(h, r, t, neg, backward=bwd, ids=ids)
+            return sc.forward(h, r, t, neg)[0]
 
         def timed(cold, bwd=True):
             for _ in range(max(warmup, 3)):

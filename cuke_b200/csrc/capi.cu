@@ -72,6 +72,9 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float
 int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, float* loss, float* ga, const float** ga_scale,
                                  void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_loss_add(const float* part, long long n, float* loss, cudaStream_t s);
+int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss, float* dproj, const int* rel_perm, const int* rel_seg,
+                                   const long long* rel_uniq, const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes,
+                                   cudaStream_t s);
 int launch_validate_ids(const void* ids, int id_bits, long long n, long long limit, void* out, cudaStream_t s);
 int launch_wait_timeout_selftest(int polls, cudaStream_t s);
 
@@ -469,6 +472,8 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
 }
 
 size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p) {
+    if (p && p->batch > 0 && tc_transr(p))
+        return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 2) + 256 + check_ids_bytes(p);
     if (!p || p->batch <= 0 || !tc_fused(p)) return 256;
     const size_t dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
     return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2) + 256 + check_ids_bytes(p);
@@ -479,12 +484,37 @@ int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float ne
     const char* fn = "kge_score_loss_backward";
     int rc = check_problem(fn, p, t, true);
     if (rc) return rc;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (tc_transr(p)) {
+        // TransR over bf16 tables: forward, loss and backward share ONE pack of the difference rows
+        KGE_REQUIRE_PTR(loss_out, "loss_out");
+        if (p->batch == 0) return cuda_status(cudaMemsetAsync(loss_out, 0, 4, s), "kge_score_loss_backward(batch=0)");
+        if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }
+        KGE_REQUIRE_PTR(pos_score, "pos_score");
+        KGE_REQUIRE_ROWS(g->g_head, "g_head", p->dim); KGE_REQUIRE_ROWS(g->g_tail, "g_tail", p->dim);
+        KGE_REQUIRE_ROWS(g->g_rel, "g_rel", p->dim); KGE_REQUIRE_ROWS(g->g_rel2, "g_rel2", p->dim);
+        if (p->neg_mode != KGE_NEG_NONE) KGE_REQUIRE_ROWS(g->g_neg, "g_neg", p->dim);
+        const size_t need = kge_score_loss_backward_workspace_bytes(p);
+        KGE_REQUIRE_PTR(workspace, "workspace");
+        if (workspace_bytes < need) { set_error("%s: workspace needs %zu bytes, got %zu", fn, need, workspace_bytes); return KGE_E_WORKSPACE; }
+        kge_tensors ts;
+        if (p->reserved & KGE_FLAG_CHECK_IDS) {
+            if (p->n_ent <= 0 || p->n_rel <= 0) { set_error("%s: KGE_FLAG_CHECK_IDS needs n_ent and n_rel", fn); return KGE_E_SHAPE; }
+            rc = sanitise_ids(p, t, &ts, static_cast<char*>(workspace) + need - check_ids_bytes(p), s);
+            if (rc) return rc;
+            t = &ts;
+        }
+        ScoreArgs a = score_args(p, t);
+        a.pos = pos_score;
+        a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel;
+        return launch_transr_loss_backward_tc(a, neg_weight, loss_out, g->g_rel2, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq,
+                                              (const long long*)t->n_rel_groups, p->n_rel, workspace, workspace_bytes, s);
+    }
     if (!tc_fused(p)) {
-        set_error("%s: needs precision KGE_PREC_TENSOR, chunk-shared negatives, dim %% 4 == 0 and "
-                  "TransE, DistMult or ComplEx; use kge_score_forward / kge_logistic_loss / kge_score_backward otherwise", fn);
+        set_error("%s: needs precision KGE_PREC_TENSOR and either chunk-shared negatives with dim %% 4 == 0 and TransE, DistMult or "
+                  "ComplEx, or TransR over bf16 tables; use kge_score_forward / kge_logistic_loss / kge_score_backward otherwise", fn);
         return KGE_E_UNSUPPORTED;
     }
-    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     KGE_REQUIRE_PTR(loss_out, "loss_out");
     if (p->batch == 0) return cuda_status(cudaMemsetAsync(loss_out, 0, 4, s), "kge_score_loss_backward(batch=0)");
     if (!g) { set_error("%s: grads is NULL", fn); return KGE_E_NULL; }

@@ -322,7 +322,7 @@ __device__ __forceinline__ void sg_fma_tile(float (&acc)[16][4], const float* xk
 // TRANS = false: Y = X . P      thread columns j = 4cg..4cg+3: P[k][4cg..] is one 128-bit load, a warp reads 512 B of a row of P
 // TRANS = true : Y = G . P^T    thread outputs i = 4cg..4cg+3: the thread streams four rows of P, 4 k-values at a time
 template <typename T, typename I, int SRC, bool TRANS>
-__global__ void __launch_bounds__(256) small_proj_kernel(SmallGroupArgs a, const float* frows, float* out) {
+__global__ void __launch_bounds__(256, 2) small_proj_kernel(SmallGroupArgs a, const float* frows, float* out) {
     extern __shared__ __align__(16) float Xs[];                 // dim * SG_LD floats
     const int g = blockIdx.x;
     if (g >= *a.n_groups) return;
@@ -343,35 +343,46 @@ __global__ void __launch_bounds__(256) small_proj_kernel(SmallGroupArgs a, const
 #pragma unroll
         for (int r = 0; r < 16; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; acc[r][2] = 0.f; acc[r][3] = 0.f; }
         const float* xr = Xs + 16 * rg;
-        // The matrix comes straight from HBM (each element is used by this group only): eight 16-byte loads per thread are
-        // requested before the first is consumed, so that a CTA keeps ~24 KB in flight and the loop is not a chain of
-        // memory round trips.
+        // The matrix comes straight from HBM (each element is used by this group only).  Loads run three batches (twelve
+        // 16-byte loads per thread) ahead of their use: a batch of four is re-requested right after it has been consumed,
+        // so every load has two batches of arithmetic (512 FMAs per thread) to arrive.
+        float4 pv[3][4];
         if (!TRANS) {
             const T* pc = P + 4 * cg;
-            for (int k0 = 0; k0 < dim; k0 += 8) {
-                float4 pv[8];
+            auto fetch = [&](int b, int k) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) pv[u] = k0 + u < dim ? load_quad<T, true>(pc + (long long)(k0 + u) * dim, 0, 4) : f4(0.f);
+                for (int u = 0; u < 4; ++u) pv[b][u] = k + u < dim ? load_quad<T, true>(pc + (long long)(k + u) * dim, 0, 4) : f4(0.f);
+            };
 #pragma unroll
-                for (int u = 0; u < 8; ++u) if (k0 + u < dim) sg_fma_tile(acc, xr + (k0 + u) * SG_LD, pv[u], nq);
+            for (int b = 0; b < 3; ++b) fetch(b, 4 * b);
+            for (int k0 = 0; k0 < dim; k0 += 12) {
+#pragma unroll
+                for (int b = 0; b < 3; ++b) {
+                    const int k = k0 + 4 * b;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (k + u < dim) sg_fma_tile(acc, xr + (k + u) * SG_LD, pv[b][u], nq);
+                    fetch(b, k + 12);
+                }
             }
         } else {
             const T* pr = P + (long long)(4 * cg) * dim;
-            for (int k0 = 0; k0 < dim; k0 += 8) {
-                float4 pv[2][4];
+            auto fetch = [&](int b, int k) {          // four k-values of the thread's four rows of P; zero past dim
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
+                for (int c = 0; c < 4; ++c) pv[b][c] = load_quad<T, true>(pr + (long long)c * dim, k >> 2, dim);
+            };
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) pv[u][c] = load_quad<T, true>(pr + (long long)c * dim, (k0 >> 2) + u, dim);      // zero past dim
+            for (int b = 0; b < 3; ++b) fetch(b, 4 * b);
+            for (int k0 = 0; k0 < dim; k0 += 12) {
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int k = k0 + 4 * u;
+                for (int b = 0; b < 3; ++b) {
+                    const int k = k0 + 4 * b;
                     if (k < dim) {
-                        sg_fma_tile(acc, xr + (k + 0) * SG_LD, make_float4(pv[u][0].x, pv[u][1].x, pv[u][2].x, pv[u][3].x), nq);
-                        sg_fma_tile(acc, xr + (k + 1) * SG_LD, make_float4(pv[u][0].y, pv[u][1].y, pv[u][2].y, pv[u][3].y), nq);
-                        sg_fma_tile(acc, xr + (k + 2) * SG_LD, make_float4(pv[u][0].z, pv[u][1].z, pv[u][2].z, pv[u][3].z), nq);
-                        sg_fma_tile(acc, xr + (k + 3) * SG_LD, make_float4(pv[u][0].w, pv[u][1].w, pv[u][2].w, pv[u][3].w), nq);
+                        sg_fma_tile(acc, xr + (k + 0) * SG_LD, make_float4(pv[b][0].x, pv[b][1].x, pv[b][2].x, pv[b][3].x), nq);
+                        sg_fma_tile(acc, xr + (k + 1) * SG_LD, make_float4(pv[b][0].y, pv[b][1].y, pv[b][2].y, pv[b][3].y), nq);
+                        sg_fma_tile(acc, xr + (k + 2) * SG_LD, make_float4(pv[b][0].z, pv[b][1].z, pv[b][2].z, pv[b][3].z), nq);
+                        sg_fma_tile(acc, xr + (k + 3) * SG_LD, make_float4(pv[b][0].w, pv[b][1].w, pv[b][2].w, pv[b][3].w), nq);
                     }
+                    fetch(b, k + 12);
                 }
             }
         }

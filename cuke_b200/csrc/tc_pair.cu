@@ -597,7 +597,8 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
         ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
         asm volatile("bar.sync 1, 256;" ::: "memory");         // the eight epilogue warps
         if (half == 0) {
-            const long long dst = p.row_dst[m];                // >= 0: negative score index, <= -2: positive -2-i, -1: padding
+            long long dst = p.row_dst[m];                      // >= 0: negative score index (+ kTailSide), <= -2: positive -2-i, -1: padding
+            if (dst >= kTailSide) dst -= kTailSide;
             const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
             if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
         }
@@ -1548,9 +1549,9 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
             }
         }
         if (lane == 0) {
-            // backward: a tail-replaced negative receives minus the row gradient; the side is folded into the slot number
-            // here (+ kTailSide) so that the scatter epilogue needs no division per row
-            const bool tail_side = coef != nullptr && j > 0 && j - 1 >= a.n_neg_head;
+            // a tail-replaced negative receives minus the row gradient in the backward; the side is folded into the slot
+            // number here (+ kTailSide) so that the scatter epilogue needs no division per row (the norm epilogue strips it)
+            const bool tail_side = j > 0 && j - 1 >= a.n_neg_head;
             row_dst[prow] = j == 0 ? -2 - (long long)i : (long long)i * a.n_neg + (j - 1) + (tail_side ? kTailSide : 0);
             if (coef) {      // dL/dv = (dS / S) v
                 const float sc = j == 0 ? a.pos[i] : a.negs[(long long)i * a.n_neg + (j - 1)];
@@ -1560,6 +1561,19 @@ __global__ void __launch_bounds__(256) transr_pack_kernel(ScoreArgs a, TransRPla
             }
         }
     }
+}
+
+// dL/dv coefficients of the packed rows from the scores and their gradients (fused step: the rows were packed before the
+// scores existed): coef[row] = dS / S, and trow0[i] = packed row of triple i's positive.
+__global__ void __launch_bounds__(256) transr_coef_kernel(ScoreArgs a, const long long* row_dst, const long long* n_tiles, float* coef, int* trow0) {
+    const long long prow = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (prow >= *n_tiles * UM_BM) return;
+    long long dst = row_dst[prow];
+    if (dst == -1) { coef[prow] = 0.f; return; }
+    float sc, ds;
+    if (dst <= -2) { const long long i = -2 - dst; sc = a.pos[i]; ds = a.dpos[i]; trow0[i] = (int)prow; }
+    else { if (dst >= kTailSide) dst -= kTailSide; sc = a.negs[dst]; ds = a.dneg[dst]; }
+    coef[prow] = sc != 0.f ? ds / sc : 0.f;
 }
 
 // Per triple: g_head = GD0 - sum of its tail-replaced g_neg rows, g_tail = -GD0 - sum of its head-replaced g_neg rows,
@@ -1602,9 +1616,11 @@ __global__ void __launch_bounds__(256) transr_reduce_tc_kernel(ScoreArgs a, cons
     store_row<2, true>(a.g_rel + i * dim, gr, dim, lane);
 }
 
-struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, off_tab2, off_coef, off_trow0, off_gv, off_gd0, total;
+struct TransRLayout { size_t off_rows, off_dst, off_tab, off_nt, off_tab2, off_coef, off_trow0, off_gv, off_gd0, off_negs, off_dpos, off_dneg, off_loss, total;
                       long long rows_cap, tile_cap, gmax; int tiles_m2; };
-static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel, bool backward = false) {
+// mode 0: forward, 1: backward, 2: fused forward + loss + backward (scores of the negatives and the score gradients live in the workspace)
+static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long n_rel, int mode = 0) {
+    const bool backward = mode != 0;
     TransRLayout L;
     const long long gmax = n_rel < batch ? n_rel : batch;
     L.rows_cap = batch * (1 + n_neg) + gmax * UM_BM;
@@ -1620,26 +1636,44 @@ static TransRLayout transr_layout(long long batch, int n_neg, int dim, long long
     L.off_trow0 = o; o += backward ? al256((size_t)batch * 4) : 0;
     L.off_gv = o; o += backward ? al256((size_t)L.rows_cap * dim * 2) : 0;
     L.off_gd0 = o; o += backward ? al256((size_t)batch * dim * 4) : 0;
+    const size_t nneg = (size_t)batch * (n_neg > 0 ? n_neg : 0);
+    L.off_negs = o; o += mode == 2 ? al256(nneg * 4 + 16) : 0;
+    L.off_dpos = o; o += mode == 2 ? al256((size_t)batch * 4) : 0;
+    L.off_dneg = o; o += mode == 2 ? al256(nneg * 4 + 16) : 0;
+    L.off_loss = o; o += mode == 2 ? 4096 : 0;
     L.total = o;
     return L;
 }
-size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel, int backward) {
-    return transr_layout(batch, n_neg, dim, n_rel, backward != 0).total;
+size_t tc_transr_workspace_bytes(long long batch, int n_neg, int dim, long long n_rel, int mode) {
+    return transr_layout(batch, n_neg, dim, n_rel, mode).total;
 }
+int launch_logistic_loss(const float* pos, long long n_pos, const float* neg, long long n_neg, float neg_w, float* dpos,
+                         float* dneg, float* loss, void* ws, size_t ws_bytes, cudaStream_t s);      // inspector.cu
 
 // a: ScoreArgs of the problem (bf16 tables); rel grouping from the inspector over r.  backward == false: scores into
 // a.pos / a.negs.  backward == true: a.pos/a.negs/a.dpos/a.dneg are inputs, gradients go to a.g_head, a.g_tail, a.g_neg,
 // a.g_rel and dproj (n_groups, dim, dim).
-static int transr_tc(const ScoreArgs& a, bool backward, float* dproj, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
-                     const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+// mode 0: scores into a.pos / a.negs.  mode 1: a.pos / a.negs / a.dpos / a.dneg are inputs, gradients go to a.g_head, a.g_tail,
+// a.g_neg, a.g_rel and dproj (n_groups, dim, dim).  mode 2: both in one pass over ONE pack of the difference rows, with the
+// logistic loss in between (a.pos and `loss` are outputs; negative scores and score gradients stay in the workspace).
+static int transr_tc(const ScoreArgs& a_in, int mode, float neg_w, float* loss, float* dproj, const int* rel_perm, const int* rel_seg,
+                     const long long* rel_uniq, const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
+    ScoreArgs a = a_in;
     if (a.batch <= 0) return 0;
-    const TransRLayout L = transr_layout(a.batch, a.n_neg, a.dim, n_rel, backward);
+    const bool backward = mode != 0;
+    const TransRLayout L = transr_layout(a.batch, a.n_neg, a.dim, n_rel, mode);
     if (ws_bytes < L.total) { set_error("TransR tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
     __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(w + L.off_rows);
     long long* dst = reinterpret_cast<long long*>(w + L.off_dst);
     float* coef = backward ? reinterpret_cast<float*>(w + L.off_coef) : nullptr;
     int* trow0 = backward ? reinterpret_cast<int*>(w + L.off_trow0) : nullptr;
+    if (mode == 2) {
+        a.negs = reinterpret_cast<float*>(w + L.off_negs);
+        a.dpos = reinterpret_cast<float*>(w + L.off_dpos);
+        a.dneg = reinterpret_cast<float*>(w + L.off_dneg);
+    }
+    float* pack_coef = mode == 1 ? coef : nullptr;          // the fused step packs before the scores exist
     __nv_bfloat16* gv = reinterpret_cast<__nv_bfloat16*>(w + L.off_gv);
     float* gd0 = reinterpret_cast<float*>(w + L.off_gd0);
     TransRPlan pl;
@@ -1654,8 +1688,8 @@ static int transr_tc(const ScoreArgs& a, bool backward, float* dproj, const int*
         const unsigned blocks = (unsigned)L.tile_cap;            // one CTA per tile; CTAs past the device-side tile count exit
         const int nv = quads_per_lane(a.dim);
 #define KGE_TP(N)                                                                                          \
-        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, coef, trow0);  \
-                else transr_pack_kernel<int32_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, coef, trow0); break;
+        case N: if (a.id_bits == 64) transr_pack_kernel<int64_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, pack_coef, trow0);  \
+                else transr_pack_kernel<int32_t, N><<<blocks, 256, 0, s>>>(a, pl, rows, dst, pack_coef, trow0); break;
         switch (nv) { KGE_TP(1) KGE_TP(2) default: set_error("TransR tensor-core path needs dim <= 256"); return KGE_E_UNSUPPORTED; }
 #undef KGE_TP
         KGE_LAUNCH_CHECK("transr_pack_kernel");
@@ -1673,9 +1707,15 @@ static int transr_tc(const ScoreArgs& a, bool backward, float* dproj, const int*
     p.a_mn = 0; p.b_mn = 1; p.elem_bytes = 2; p.passes = 1;
     p.tile_tab = pl.tile_tab; p.n_tiles_dev = pl.n_tiles; p.tile_cap = L.tile_cap;
     p.row_dst = dst; p.rel_vec = a.rel; p.rel_is_bf16 = 1;
-    if (!backward) {
+    if (mode != 1) {
         p.ep = EP_NORM; p.pos_out = a.pos; p.neg_out = a.negs;
-        return run_gemm(ma, ma, mb, mb, p, 1, s);
+        if ((rc = run_gemm(ma, ma, mb, mb, p, 1, s))) return rc;
+        if (mode == 0) return 0;
+        const long long nneg = a.batch * (long long)a.n_neg;
+        if ((rc = launch_logistic_loss(a.pos, a.batch, a.negs, nneg, neg_w, const_cast<float*>(a.dpos), const_cast<float*>(a.dneg), loss,
+                                       w + L.off_loss, 4096, s))) return rc;
+        transr_coef_kernel<<<(unsigned)((L.tile_cap * UM_BM + 255) / 256), 256, 0, s>>>(a, dst, pl.n_tiles, coef, trow0);
+        KGE_LAUNCH_CHECK("transr_coef_kernel");
     }
     p.ep = EP_GV; p.coef = coef; p.gv_out = gv;
     if ((rc = run_gemm(ma, ma, mb, mb, p, 1, s))) return rc;
@@ -1718,11 +1758,18 @@ int launch_wait_timeout_selftest(int polls, cudaStream_t s) {
 
 int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                              const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
-    return transr_tc(a, false, nullptr, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+    return transr_tc(a, 0, 0.f, nullptr, nullptr, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
 }
 int launch_transr_backward_tc(const ScoreArgs& a, float* dproj, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                               const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes, cudaStream_t s) {
-    return transr_tc(a, true, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+    return transr_tc(a, 1, 0.f, nullptr, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+}
+// Forward, logistic loss and backward of TransR over bf16 tables with ONE pack of the difference rows: a.pos (batch) and
+// loss (1,) are written, gradients as in launch_transr_backward_tc.  ws: tc_transr_workspace_bytes(..., 2).
+int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss, float* dproj, const int* rel_perm, const int* rel_seg,
+                                   const long long* rel_uniq, const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes,
+                                   cudaStream_t s) {
+    return transr_tc(a, 2, neg_w, loss, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
 }
 
 }  // namespace kge

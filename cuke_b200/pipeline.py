@@ -362,7 +362,7 @@ class KgeStep:
             sc = Scorer(m, staged, self.rel.get(m), self.rel2.get(m), self.neg_mode, nnh, self.chunk, self.precision)
             if backward and self.fused and sc.supports_fused_step(sneg.shape[-1]):
                 # one call: the scores of the negatives become loss terms and gradient weights inside the tile kernel
-                pos, loss, sg = sc.loss_backward(sh, r32, st, sneg)
+                pos, loss, sg = sc.loss_backward(sh, r32, st, sneg, rel_insp=rinsp)
                 out.loss[m], out.pos[m] = loss, pos
             else:
                 pos, negs, _ = sc.forward(sh, r32, st, sneg, rinsp)

@@ -385,21 +385,30 @@ class Scorer:
 
 
     def supports_fused_step(self, n_neg: int) -> bool:
-        """True where loss_backward applies: tensor precision, chunk-shared negatives, TransE / DistMult / ComplEx."""
-        return (self.precision == PRECISIONS["tensor"] and self.neg_mode == "chunk_shared" and self.dim % 4 == 0
-                and n_neg > 0 and self.model in ("TransE", "DistMult", "ComplEx"))
+        """True where loss_backward applies: tensor precision and either chunk-shared negatives with TransE / DistMult /
+        ComplEx, or TransR over bf16 tables with per-triple negatives."""
+        if self.precision != PRECISIONS["tensor"]:
+            return False
+        if self.model == "TransR":
+            return (self.ent.dtype == torch.bfloat16 and self.dim % 8 == 0 and self.dim <= 256 and self.neg_mode != "chunk_shared")
+        return (self.neg_mode == "chunk_shared" and self.dim % 4 == 0 and n_neg > 0 and self.model in ("TransE", "DistMult", "ComplEx"))
 
     def loss_backward(self, h, r, t, neg, neg_weight: Optional[float] = None,
-                      ent_slots: Optional[torch.Tensor] = None):
+                      ent_slots: Optional[torch.Tensor] = None, rel_insp: Optional[Inspection] = None):
         """forward -> logistic_loss -> backward in one call (kge_score_loss_backward): returns (pos, loss, SlotGrads).
-        The scores of the negatives are consumed inside the tile kernel and are not returned."""
+        The scores of the negatives are consumed inside the call and are not returned."""
         self._check_ids(h, r, t, neg)
         B, d, dev = h.numel(), self.dim, self.ent.device
         p = self._problem(h, neg)
-        kt = self._tensors(h, r, t, neg, None)
+        rel2_groups = None
+        if self.model in MATRIX_MODELS:
+            if rel_insp is None:
+                rel_insp = self._group_by_relation(r)
+            rel2_groups = torch.zeros((min(self.n_rel, B), d, d), dtype=torch.float32, device=dev)
+        kt = self._tensors(h, r, t, neg, rel_insp)
         if neg_weight is None:
             neg_weight = 1.0 / max(p.n_neg, 1)
-        n_slots = 2 * B + neg.numel()
+        n_slots = 2 * B + (neg.numel() if p.n_neg else 0)
         if ent_slots is None:
             ent_slots = torch.empty((n_slots, d), dtype=torch.float32, device=dev)
         elif ent_slots.shape != (n_slots, d):
@@ -407,12 +416,13 @@ class Scorer:
         rel_slots = torch.empty((B, d), dtype=torch.float32, device=dev)
         pos = torch.empty(B, dtype=torch.float32, device=dev)
         loss = torch.empty(1, dtype=torch.float32, device=dev)
-        g = KgeGrads(_ptr(ent_slots[:B]), _ptr(ent_slots[B:2 * B]), _ptr(ent_slots[2 * B:]), _ptr(rel_slots), None)
+        g = KgeGrads(_ptr(ent_slots[:B]), _ptr(ent_slots[B:2 * B]), _ptr(ent_slots[2 * B:]) if p.n_neg else None, _ptr(rel_slots),
+                     _ptr(rel2_groups))
         L = _lib.lib()
         ws = workspace(L.kge_score_loss_backward_workspace_bytes(C.byref(p)), dev, "score")
         check(L.kge_score_loss_backward(C.byref(p), C.byref(kt), float(neg_weight), _ptr(pos), _ptr(loss), C.byref(g),
                                         _ptr(ws), ws.numel(), _stream()))
-        return pos, loss, SlotGrads(ent_slots, rel_slots, None, None, None)
+        return pos, loss, SlotGrads(ent_slots, rel_slots, None, rel2_groups, rel_insp)
 
 
 def entity_id_list(h, t, neg) -> torch.Tensor:

@@ -264,8 +264,10 @@ KGE_API int kge_score_backward(const kge_problem* p, const kge_tensors* t,
  * negative is turned into its loss term and its gradient weight inside the tile that produced it, so the
  * (batch, n_neg) score matrix, its gradient and a second operand pack never reach memory.  Writes pos_score (batch,),
  * loss_out (1,) and the gradient rows of `g`; scores of the negatives are not returned.  Needs precision
- * KGE_PREC_TENSOR, neg_mode KGE_NEG_CHUNK_SHARED, dim % 4 == 0 and TransE, DistMult or ComplEx
- * (KGE_E_UNSUPPORTED otherwise).  No reference counterpart: the reference stops at per-triple outputs
+ * KGE_PREC_TENSOR and either neg_mode KGE_NEG_CHUNK_SHARED, dim % 4 == 0 and TransE, DistMult or ComplEx, or TransR over
+ * bf16 tables (any per-triple negatives; the relation-grouped difference rows are then packed once for the forward and
+ * the three backward products, and the rel_* grouping of kge_tensors is required); KGE_E_UNSUPPORTED otherwise.
+ * No reference counterpart: the reference stops at per-triple outputs
  * (apps/kge/kge.py:273-390) and leaves loss and gradients to the caller's framework. */
 KGE_API size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p);
 KGE_API int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float neg_weight,

@@ -519,3 +519,23 @@ def test_backward_with_rows_that_are_not_quads():
         if mode == "none":
             p["neg"] = None
         _check_grads(p, 1 if mode == "per_triple" else 0, 0)
+
+
+@pytest.mark.parametrize("d,B,nn,nnh,nr", [(200, 64, 16, 8, 11), (64, 300, 5, 0, 3), (256, 40, 33, 33, 40), (200, 1024, 128, 64, 50)])
+def test_transr_fused_step_matches_separate_calls(d, B, nn, nnh, nr):
+    """kge_score_loss_backward for TransR over bf16 tables packs the relation-grouped difference rows once; loss, positives
+    and every gradient must equal forward -> logistic loss -> backward (same kernels on the same packed rows: bit for bit)."""
+    from cuke_b200 import scoring
+    p = make_problem("TransR", seed=3 * d + B, ne=150, nr=nr, d=d, B=B, nn=nn, zipf=True)
+    sc = gpu_scorer(p, nnh, bf16=True, precision="tensor")
+    assert sc.supports_fused_step(nn)
+    h, r, t, neg = gpu_ids(p)
+    pos, loss, sg = sc.loss_backward(h, r, t, neg)
+    assert scoring.device_flags() == 0
+    pos_u, negs_u, rinsp = sc.forward(h, r, t, neg)
+    loss_u, dpos, dneg = scoring.logistic_loss(pos_u, negs_u)
+    sg_u = sc.backward(h, r, t, neg, pos_u, negs_u, dpos, dneg, rinsp)
+    assert torch.equal(pos, pos_u) and torch.equal(loss, loss_u)
+    assert torch.equal(sg.ent_slots, sg_u.ent_slots) and torch.equal(sg.rel_slots, sg_u.rel_slots)
+    G = rinsp.count()
+    assert torch.equal(sg.rel2_groups[:G], sg_u.rel2_groups[:G])
