@@ -57,7 +57,7 @@ def parse():
                     help="profiling aid: run forward+backward of the scorers 3 times on a reduced case (--chunks chunks, "
                          "entity table scaled down to fit a few GB) and exit; meant to be run under ncu -k <kernel>")
     ap.add_argument("--chunks", type=int, default=32)
-    ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor"],
+    ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor", "tensor_tf32"],
                     help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
     ap.add_argument("--no-optimizer", action="store_true", help="return gradients only (no sparse SGD update in the step)")
@@ -94,6 +94,13 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+
+    def settle(self, samples: int = 3, limit_s: float = 8.0):
+        """Returns once nvidia-smi has printed a few samples: its start-up (driver queries that can stall the GPU for
+        milliseconds) then lies before the timed region, not inside its first steps."""
+        t0 = time.time()
+        while self.proc is not None and len(self.lines) < samples and time.time() - t0 < limit_s and self.proc.poll() is None:
+            time.sleep(0.05)
 
     def stop(self):
         if self.proc is None:
@@ -549,6 +556,9 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.settle()
+    if world > 1:
+        dist.barrier(group=group)
     launches0 = _lib.lib().kge_launch_count()
     # N GPUs: the last scorer's gradient return of step i may overlap the inspector of step i+1 (wait=False); the last
     # timed step waits for its own return, so the timed region covers all the work of its K steps
@@ -624,7 +634,7 @@ def main():
         # once, one gradient row per distinct entity / relation row and scorer; the score matrix and its gradient are
         # consumed inside the tile kernel (fused loss), so they contribute nothing.  Forward rows are read again by the
         # backward only from the compact staging buffer, counted once more.
-        fused = args.precision == "tensor"
+        fused = args.precision != "fp32"
         S1 = synth.scored_triples(cfg)
         bytes_fwd = U * d * 4 + len(models) * U_r * d * 4 + 8 * n_ids + (0 if fused else len(models) * 4 * S1)
         bytes_bwd = len(models) * (U * d * 4 + U_r * d * 4) + U * d * 4 + (0 if fused else len(models) * 4 * S1)
@@ -635,12 +645,12 @@ def main():
                     "distinct_entity_rows": U, "distinct_relation_rows": U_r,
                     "note": "c5 with chunk-shared negatives is bound by the contraction, not by HBM: this fraction is small by construction"}
         L = _lib.lib()
-        if args.precision == "tensor":
+        if args.precision != "fp32":
             # the six contractions of a step (forward S with the loss epilogue, backward GA and GX, for both scorers) are
             # launches of ONE kernel; the same calls as KgeStep.step makes
             def fwd_bwd():
                 for m in models:
-                    sc = scoring.Scorer(m, staged, rel[m], None, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, "tensor")
+                    sc = scoring.Scorer(m, staged, rel[m], None, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, args.precision)
                     if sc.supports_fused_step(sneg.shape[-1]):
                         sc.loss_backward(sh, r32, st, sneg)
                     else:
@@ -668,13 +678,15 @@ def main():
                 traffic = pt[0] * scale
                 traffic_note = (f"dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of the {pt[1]} launches of one step captured by "
                                 f"ncu at 32 chunks ({pt[2]}), x {scale:g} for this run's {B // cfg.chunk} chunks (traffic grows with the chunk count)")
-            roof = {"kernel": "umma_pair_kernel (tcgen05 cta_group::2, 3xTF32; average over the step's contraction launches: "
+            split = "two-term bf16 split, three kind::f16 MMAs per product" if args.precision == "tensor" else "3xTF32"
+            pipe_x = 3 if args.precision == "tensor" else 6
+            roof = {"kernel": f"umma_pair_kernel (tcgen05 cta_group::2, {split}; average over the step's contraction launches: "
                               "per scorer the forward product with the fused loss epilogue and two backward products)",
                     "bound": "tensor", "achieved": ach, "peak": bf16_peak, "unit": "TFLOP/s", "frac": ach / bf16_peak,
                     "peak_source": f"MEASURED_PEAKS.json bf16 dense, burst ({peak_kind})",
-                    "note": "achieved counts useful fp32 flops (2MNK); each is 3 tf32 MMAs at half the bf16 rate, so the "
-                            "tensor pipe does 6x this many bf16-equivalent flops",
-                    "tensor_pipe_equiv_frac": 6 * ach / bf16_peak, "launches_timed": n.value, "launches_per_step": per_step,
+                    "note": "achieved counts useful fp32 flops (2MNK); each is 3 MMAs (bf16 split: at the bf16 rate; tf32 split: "
+                            f"at half of it), so the tensor pipe does {pipe_x}x this many bf16-equivalent flops",
+                    "tensor_pipe_equiv_frac": pipe_x * ach / bf16_peak, "launches_timed": n.value, "launches_per_step": per_step,
                     "ms": t_k * 1e3, "share_of_step": per_step * t_k * 1e3 / ms_step,
                     "traffic": traffic, "traffic_note": traffic_note,
                     "traffic_per_step": None if traffic is None else traffic * per_step,
@@ -727,9 +739,11 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), arithmetic=(
-                    "fp32 storage and accumulation; contractions as 3xTF32 on the tensor cores (error-compensated, "
-                    "max rel. error ~2e-6 vs fp64, inside the 1e-4 fp32 tolerance)" if args.precision == "tensor"
-                    else "fp32 CUDA cores")),
+                    "fp32 storage and accumulation; contractions on the tensor cores over a two-term bf16 split of each fp32 "
+                    "operand (three MMAs per product, error-compensated; see the parity block for the measured error)"
+                    if args.precision == "tensor" else
+                    "fp32 storage and accumulation; contractions as 3xTF32 on the tensor cores (error-compensated)"
+                    if args.precision == "tensor_tf32" else "fp32 CUDA cores")),
                 "spread": spread,
                 "value_fwd_only": scored_per_gpu * world / (ms_fwd * 1e-3), "ms_per_step_fwd_only": ms_fwd,
                 "e2e": e2e, "gpu_launches": int(launches) * args.steps, "gpu_launches_per_step": int(launches),

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libkge_b200.so")
 MODELS = {"TransE": 0, "TransH": 1, "TransR": 2, "TransF": 3, "DistMult": 4, "RESCAL": 5, "ComplEx": 6}
 DTYPES = {"f32": 0, "bf16": 1}
 NEG_MODES = {"none": 0, "per_triple": 1, "chunk_shared": 2}
-PRECISIONS = {"fp32": 0, "tensor": 1}
+PRECISIONS = {"fp32": 0, "tensor": 1, "tensor_tf32": 2}
 FLAG_CHECK_IDS = 1            # kge_problem.reserved
 ERR_WAIT_TIMEOUT, ERR_ID_RANGE = 2, 8     # values of the device error word (kge_check)
 VECTOR_MODELS = ("TransE", "TransH", "TransR")

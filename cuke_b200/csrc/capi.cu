@@ -64,7 +64,7 @@ int launch_transr_forward_tc(const ScoreArgs& a, const int* rel_perm, const int*
 size_t transr_backward_workspace_bytes(const kge_problem* p);
 int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const float* pos, const float* negs, const float* dpos,
                            const float* dneg, const kge_grads* g, void* ws, cudaStream_t s);
-size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int backward);
+size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode, int es);
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
 void gemm_profile_enable(int on);
 int gemm_profile_read(double* ms, long long* launches, double* flops);
@@ -115,7 +115,7 @@ static int check_problem(const char* fn, const kge_problem* p, const kge_tensors
     if (p->model == KGE_COMPLEX && (p->dim & 1)) { set_error("%s: ComplEx needs an even dim (re,im interleaved), got %d", fn, p->dim); return KGE_E_SHAPE; }
     if (p->dtype == KGE_BF16 && (p->dim & 7)) { set_error("%s: bf16 tables need dim %% 8 == 0 (16-byte rows), got %d", fn, p->dim); return KGE_E_UNSUPPORTED; }
     if (p->batch < 0) { set_error("%s: negative batch", fn); return KGE_E_SHAPE; }
-    if (p->precision != KGE_PREC_FP32 && p->precision != KGE_PREC_TENSOR) { set_error("%s: unknown precision %d", fn, p->precision); return KGE_E_UNSUPPORTED; }
+    if (p->precision != KGE_PREC_FP32 && p->precision != KGE_PREC_TENSOR && p->precision != KGE_PREC_TENSOR_TF32) { set_error("%s: unknown precision %d", fn, p->precision); return KGE_E_UNSUPPORTED; }
     if (p->reserved & ~KGE_FLAG_CHECK_IDS) { set_error("%s: unknown flags 0x%x in reserved", fn, p->reserved); return KGE_E_UNSUPPORTED; }
     if (!scored && p->reserved) { set_error("%s: KGE_FLAG_CHECK_IDS needs a workspace; check the ids with kge_validate_ids first", fn); return KGE_E_UNSUPPORTED; }
     if (p->batch == 0) return 0;
@@ -159,25 +159,28 @@ static ScoreArgs score_args(const kge_problem* p, const kge_tensors* t) {
     a.n_neg = p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg;
     a.n_neg_head = p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg_head;
     a.model = p->model; a.dtype = p->dtype; a.id_bits = p->id_bits;
+    a.tc_es = p->precision == KGE_PREC_TENSOR_TF32 ? 4 : 2;
     return a;
 }
 
 static inline size_t rows_bytes(const kge_problem* p) { return ((size_t)p->batch * p->dim * 4 + 255) / 256 * 256; }
 
 // The tensor-core contractions exist for the scorers that support chunk-shared negatives.
+static bool tensor_precision(const kge_problem* p) { return p->precision == KGE_PREC_TENSOR || p->precision == KGE_PREC_TENSOR_TF32; }
+static int tc_es(const kge_problem* p) { return p->precision == KGE_PREC_TENSOR_TF32 ? 4 : 2; }
 static bool tc_forward(const kge_problem* p) {
-    return p->precision == KGE_PREC_TENSOR && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 &&
+    return tensor_precision(p) && p->neg_mode == KGE_NEG_CHUNK_SHARED && p->dim % 4 == 0 &&
            (p->model == KGE_TRANSE || p->model == KGE_DISTMULT || p->model == KGE_COMPLEX || p->model == KGE_RESCAL);
 }
 // TransR forward on the tensor cores: bf16 tables, one n-tile per row.
 static bool tc_transr(const kge_problem* p) {
-    return p->precision == KGE_PREC_TENSOR && p->model == KGE_TRANSR && p->dtype == KGE_BF16 && p->dim % 8 == 0 && p->dim <= 256 &&
+    return tensor_precision(p) && p->model == KGE_TRANSR && p->dtype == KGE_BF16 && p->dim % 8 == 0 && p->dim <= 256 &&
            p->neg_mode != KGE_NEG_CHUNK_SHARED;
 }
 static bool tc_backward(const kge_problem* p) { return tc_forward(p); }
 static size_t tc_bytes(const kge_problem* p, int backward) {
     if (backward ? !tc_backward(p) : !tc_forward(p)) return 0;
-    return tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, backward);
+    return tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, backward, tc_es(p));
 }
 // Fused forward + loss + backward: the chunk-shared tensor-core scorers whose anchors are built from table rows alone.
 static bool tc_fused(const kge_problem* p) { return tc_backward(p) && p->model != KGE_RESCAL; }
@@ -476,7 +479,7 @@ size_t kge_score_loss_backward_workspace_bytes(const kge_problem* p) {
         return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 2) + 256 + check_ids_bytes(p);
     if (!p || p->batch <= 0 || !tc_fused(p)) return 256;
     const size_t dpos_bytes = ((size_t)p->batch * 4 + 255) / 256 * 256;
-    return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2) + 256 + check_ids_bytes(p);
+    return rows_bytes(p) + dpos_bytes + 4096 + tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2, tc_es(p)) + 256 + check_ids_bytes(p);
 }
 
 int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float neg_weight, float* pos_score, float* loss_out,
@@ -545,7 +548,7 @@ int kge_score_loss_backward(const kge_problem* p, const kge_tensors* t, float ne
     const bool head = p->n_neg_head > 0;
     const float* ga_scale = nullptr;
     rc = launch_pair_loss_backward_tc(a, head ? 1 : 0, neg_weight, loss_out, ga, &ga_scale, tcw,
-                                      tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2), s);
+                                      tc_pair_workspace_bytes(p->batch, p->chunk, p->n_neg, p->dim, 2, tc_es(p)), s);
     if (rc) return rc;
     // positives: score, loss term, dS and their gradient rows in the per-triple kernel, on top of the anchor gradients
     ScoreArgs b = a;

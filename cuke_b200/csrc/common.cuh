@@ -126,6 +126,7 @@ struct ScoreArgs {
     unsigned long long guard_cap;
     long long batch; int dim; int n_neg; int n_neg_head; int chunk;
     int model; int dtype; int id_bits;
+    int tc_es;                               // tensor-core split of fp32 operands: 2 = bf16 pairs, 4 = tf32 pairs
 };
 
 int launch_ref_forward(const kge_problem* p, const kge_tensors* t, float* out, cudaStream_t s);

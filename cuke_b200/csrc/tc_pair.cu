@@ -82,20 +82,61 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
     return make_tensor_map_3d(out, base, elem_bytes, 1, rows, cols, row_stride_bytes, rows * row_stride_bytes, box_rows, box_cols);
 }
 
-// ---- pack kernels --------------------------------------------------------------------------------------------
+// ---- operand split ----------------------------------------------------------------------------------------------
+// A contraction of fp32 operands runs on the tensor cores as three MMAs over a two-term split of each operand,
+// v ~ hi + lo:  lo*hi + hi*lo + hi*hi  (the lo*lo term is below the target accuracy).  Two element formats:
+//   ES = 2  bf16 split (default): hi = bf16(v), lo = bf16(v - hi); hi + lo carries 16 mantissa bits, products are exact to
+//           ~2^-16 relative, and the MMAs are kind::f16 at the full tensor rate with 4 bytes of operands per element.
+//   ES = 4  tf32 split in fp32 storage: hi = top 19 bits of v (exact in tf32), lo = v - hi exactly; products exact to
+//           ~2^-20, kind::tf32 at half the rate with 8 bytes per element ("3xTF32").
+// Both stay inside the 1e-4 tolerance of the fp32 path (a single bf16 or tf32 pass, 2^-9 / 2^-11, would not).
 __device__ __forceinline__ float tf32_trunc(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
-__device__ __forceinline__ void split4(float4 v, float4& hi, float4& lo) {
-    hi = make_float4(tf32_trunc(v.x), tf32_trunc(v.y), tf32_trunc(v.z), tf32_trunc(v.w));
-    // v - hi is exact (the low mantissa bits of v); the tensor core reads only its top 19 bits, and hi + lo == v
-    lo = make_float4(v.x - hi.x, v.y - hi.y, v.z - hi.z, v.w - hi.w);
+template <int ES> struct Split;
+template <> struct Split<4> {
+    using T = float;
+    __device__ static __forceinline__ void put(T* hi, T* lo, float v) { const float h = tf32_trunc(v); *hi = h; *lo = v - h; }
+    __device__ static __forceinline__ float get(const T* hi, const T* lo) { return __ldg(hi) + __ldg(lo); }
+};
+template <> struct Split<2> {
+    using T = __nv_bfloat16;
+    __device__ static __forceinline__ void put(T* hi, T* lo, float v) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        *hi = h; *lo = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+    __device__ static __forceinline__ float get(const T* hi, const T* lo) { return __bfloat162float(*hi) + __bfloat162float(*lo); }
+};
+// quad (4 consecutive elements) forms for the row kernels; `b2` (bf16 split only, may be NULL) receives the third term
+// v - hi - lo, which makes hi + lo + b2 == v exactly for the rows an epilogue has to rebuild
+__device__ __forceinline__ void put_quad(float* hi, float* lo, float* /*b2*/, float4 v) {
+    const float4 h = make_float4(tf32_trunc(v.x), tf32_trunc(v.y), tf32_trunc(v.z), tf32_trunc(v.w));
+    *reinterpret_cast<float4*>(hi) = h;
+    *reinterpret_cast<float4*>(lo) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+}
+__device__ __forceinline__ uint2 bf16x4(float4 v, float4& back) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v.x, v.y), p1 = __floats2bfloat162_rn(v.z, v.w);
+    const float2 f0 = __bfloat1622float2(p0), f1 = __bfloat1622float2(p1);
+    back = make_float4(f0.x, f0.y, f1.x, f1.y);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&p0); u.y = *reinterpret_cast<unsigned*>(&p1);
+    return u;
+}
+__device__ __forceinline__ void put_quad(__nv_bfloat16* hi, __nv_bfloat16* lo, __nv_bfloat16* b2, float4 v) {
+    float4 h, l, t;
+    *reinterpret_cast<uint2*>(hi) = bf16x4(v, h);
+    const float4 r1 = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+    *reinterpret_cast<uint2*>(lo) = bf16x4(r1, l);
+    if (b2) *reinterpret_cast<uint2*>(b2) = bf16x4(make_float4(r1.x - l.x, r1.y - l.y, r1.z - l.z, r1.w - l.w), t);
 }
 
+// ---- pack kernels --------------------------------------------------------------------------------------------
 // Rows [0, n_a): anchors of the triples; rows [n_a, n_a + n_x): the negative rows, in id-list order.
-// One warp per row; hi / lo are (n_a + n_x) rows of fp32 with a pitch of ldp floats (dim rounded up to whole 128-byte
-// slabs, the padding written as zero), sq (n_a + n_x) the squared norms of the unsplit rows.
-template <int MODEL, typename T, typename I, int NV>
+// One warp per row; hi / lo (/ b2) are (n_a + n_x) rows of split elements with a pitch of ldp elements (dim rounded up to
+// whole 128-byte slabs, the padding written as zero), sq (n_a + n_x) the squared norms of the unsplit rows.
+template <int MODEL, typename T, typename I, int NV, int ES>
 __global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, long long n_a, long long n_x, int ldp,
-                                                      float* hi, float* lo, float* sq) {
+                                                      void* hi_v, void* lo_v, void* b2_v, float* sq) {
+    using S = typename Split<ES>::T;
+    S* hi = static_cast<S*>(hi_v); S* lo = static_cast<S*>(lo_v); S* b2 = static_cast<S*>(b2_v);
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n_a + n_x) return;
@@ -121,32 +162,30 @@ __global__ void __launch_bounds__(256) tc_pack_kernel(ScoreArgs a, int head, lon
         load_row<T, NV, true>(v, E + load_id<I>(a.neg, row - n_a) * dim, dim, lane);
     }
     float s = 0.f;
-    Row<NV> h, l;
+    const long long base = row * ldp;
 #pragma unroll
-    for (int q = 0; q < NV; ++q) { s = dot4(v.v[q], v.v[q], s); split4(v.v[q], h.v[q], l.v[q]); }
-    store_row<NV, true>(hi + row * ldp, h, dim, lane);
-    store_row<NV, true>(lo + row * ldp, l, dim, lane);
-    if (dim + 4 * lane < ldp) {                       // at most 7 quads of padding
-        *reinterpret_cast<float4*>(hi + row * ldp + dim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
-        *reinterpret_cast<float4*>(lo + row * ldp + dim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < NV; ++q) {
+        s = dot4(v.v[q], v.v[q], s);
+        const int k = 4 * (lane + 32 * q);
+        if (k < dim) put_quad(hi + base + k, lo + base + k, b2 ? b2 + base + k : nullptr, v.v[q]);
     }
+    for (int k = dim + 4 * lane; k < ldp; k += 128)       // zero padding up to the slab boundary
+        put_quad(hi + base + k, lo + base + k, b2 ? b2 + base + k : nullptr, make_float4(0.f, 0.f, 0.f, 0.f));
     s = warp_sum(s);
     if (lane == 0 && sq) sq[row] = s;
 }
 
 // W = dS split into hi / lo (dot-product scorers).  One warp per row of the (batch, n_neg) matrix; hi / lo have a pitch
 // of ldw floats (n_neg rounded up to whole slabs, padding zero).
-__global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, long long rows, int n_neg, int ldw, float* hi, float* lo) {
+template <int ES>
+__global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, long long rows, int n_neg, int ldw, void* hi_v, void* lo_v) {
+    using S = typename Split<ES>::T;
+    S* hi = static_cast<S*>(hi_v); S* lo = static_cast<S*>(lo_v);
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const float* d = ds + row * n_neg;
-    for (int j = lane; j < ldw; j += 32) {
-        const float w = j < n_neg ? d[j] : 0.f;
-        const float h = tf32_trunc(w);
-        hi[row * ldw + j] = h;
-        lo[row * ldw + j] = tf32_trunc(w - h);
-    }
+    for (int j = lane; j < ldw; j += 32) Split<ES>::put(hi + row * ldw + j, lo + row * ldw + j, j < n_neg ? d[j] : 0.f);
 }
 // TransE: W = dS / S (0 where S == 0) split into hi / lo, with its row sums and per-block column sums in the same pass.
 // A block takes TW_ROWS consecutive rows of one chunk; thread t owns columns t, t + 256, ...: for a fixed row the block
@@ -154,9 +193,12 @@ __global__ void __launch_bounds__(256) tc_pack_w_kernel(const float* ds, long lo
 // reduced once per block.  colpart[(chunk * blocks_per_chunk + block)][j] holds the block's column sums; all sums are
 // added in a fixed order, so the result does not depend on scheduling.
 constexpr int TW_ROWS = 32;
+template <int ES>
 __global__ void __launch_bounds__(256) tc_pack_w_sums_kernel(const float* __restrict__ ds, const float* __restrict__ sc, int chunk, int n_neg,
-                                                             int ldw, float* __restrict__ hi, float* __restrict__ lo,
+                                                             int ldw, void* hi_v, void* lo_v,
                                                              float* __restrict__ rowsum, float* __restrict__ colpart) {
+    using S = typename Split<ES>::T;
+    S* hi = static_cast<S*>(hi_v); S* lo = static_cast<S*>(lo_v);
     __shared__ float row_part[8][TW_ROWS];
     const int c = blockIdx.y, r0 = blockIdx.x * TW_ROWS;
     const int rows = min(TW_ROWS, chunk - r0);
@@ -181,9 +223,7 @@ __global__ void __launch_bounds__(256) tc_pack_w_sums_kernel(const float* __rest
         for (int i = 0; i < TW_ROWS; ++i) {
             if (i < rows) {
                 const float w = sv[i] != 0.f ? dv[i] / sv[i] : 0.f;
-                const float h = tf32_trunc(w);
-                hi[(row0 + i) * ldw + j] = h;
-                lo[(row0 + i) * ldw + j] = tf32_trunc(w - h);
+                Split<ES>::put(hi + (row0 + i) * ldw + j, lo + (row0 + i) * ldw + j, w);
                 cs += w;
                 rs[i] += w;
             }
@@ -237,7 +277,7 @@ struct GemmTc {
     const float* sq_a; const float* sq_b;                        // (batch * m_rows), (batch * n_cols)
     unsigned long long* fix_count; unsigned long long* fix_list; unsigned long long fix_cap;
     // EP_RANK1: out = scale[b * m_rows + m] * (y_hi + y_lo)[(b * m_rows + m) * out_ld + n] - acc
-    const float* scale; const float* y_hi; const float* y_lo;
+    const float* scale; const void* y_hi; const void* y_lo;      // y in the operands' split format
     // element type and split: elem_bytes 4 (tf32) or 2 (bf16); passes 3 (hi/lo split) or 1 (hi only)
     int elem_bytes; int passes;
     // grouped mode (relation-grouped projections): tile list in device memory, one n-tile
@@ -253,9 +293,10 @@ struct GemmTc {
     // stored split into w_hi / w_lo (pitch ldw) for the backward products, with partial row sums
     // rowpart[(n_tile * 2 + half)][row], partial column sums colpart[(batch * ceil(m_rows / 32) + row block)][col]
     // and one loss partial per epilogue warp and tile, loss_part[slot].
-    float* w_hi; float* w_lo; long long ldw; float neg_w; int loss_dist;
+    void* w_hi; void* w_lo; long long ldw; float neg_w; int loss_dist;      // W in the operands' split format, pitch in elements
     float* rowpart; float* colpart; float* loss_part;
-    const float* ex_a_hi; const float* ex_a_lo; const float* ex_x_hi; const float* ex_x_lo; long long ex_ld;   // exact rows
+    const void* ex_a_hi; const void* ex_a_lo; const void* ex_x_hi; const void* ex_x_lo; long long ex_ld;   // exact rows: hi + lo
+    const void* ex_a_b2; const void* ex_x_b2;                     // (+ b2 for the bf16 split)
     int pair;                         // 1: CTA pairs (256-row tiles, umma_pair_kernel)
     int a_slabs4d, b_slabs4d;         // MN-major operand read through a 4-D slab map: one copy per stage instead of one per slab
     long long y_ld;                   // EP_RANK1: row pitch of y_hi / y_lo
@@ -290,7 +331,7 @@ constexpr int UM_EPI_WARPS = 8;
 // (store, distance, rank-1, fused loss; epilogue_tile below), G_GROUPED the relation-grouped products (store, norm, dL/dv
 // rows, scatter; epilogue_grouped).  Two instantiations keep the register allocation of each set independent of the other.
 enum { G_DENSE = 0, G_GROUPED = 1 };
-template <int GROUP>
+template <int GROUP, int ES>
 __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
                                               int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot) {
     const int q = warp & 3;
@@ -319,12 +360,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         const int col = nbase + lane;
         float y[32];
         if (GROUP == G_DENSE && p.ep == EP_RANK1) {          // the y rows come from memory: requested before the accumulator is read
-            const float* yh = p.y_hi + grow0 * p.y_ld + col;
-            const float* yl = p.y_lo + grow0 * p.y_ld + col;
+            using S = typename Split<ES>::T;
+            const S* yh = static_cast<const S*>(p.y_hi) + grow0 * p.y_ld + col;
+            const S* yl = static_cast<const S*>(p.y_lo) + grow0 * p.y_ld + col;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
                 const long long off = static_cast<long long>(r) * p.y_ld;
-                y[r] = (col_ok && r < rows_here) ? __ldg(yh + off) + __ldg(yl + off) : 0.f;
+                y[r] = (col_ok && r < rows_here) ? Split<ES>::get(yh + off, yl + off) : 0.f;
             }
         }
         float v[32];
@@ -334,8 +376,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
         __syncwarp();
         if (GROUP == G_DENSE && p.ep == EP_LOSS) {
-            float* wh = p.w_hi + grow0 * p.ldw + col;
-            float* wl = p.w_lo + grow0 * p.ldw + col;
+            using S = typename Split<ES>::T;
+            S* wh = static_cast<S*>(p.w_hi) + grow0 * p.ldw + col;
+            S* wl = static_cast<S*>(p.w_lo) + grow0 * p.ldw + col;
             const bool pad_ok = col < p.ldw;         // pitch padding past the last column is written as zero
             const float nw = p.neg_w;
             float lsum = 0.f;                        // loss terms of this chunk, scaled by neg_w once at the end
@@ -377,11 +420,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                         const int r = r0 + i;
                         if (r < rows_here) {
                             stg[r * 32 + (lane ^ r)] = wv[i];                     // kept for the row sums below
-                            if (pad_ok) {
-                                const float h = __uint_as_float(__float_as_uint(wv[i]) & 0xFFFFE000u);
-                                wh[static_cast<long long>(r) * p.ldw] = h;
-                                wl[static_cast<long long>(r) * p.ldw] = wv[i] - h;
-                            }
+                            if (pad_ok) Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, wv[i]);
                         }
                     }
                 }
@@ -395,7 +434,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                             const long long ao = (grow0 + r) * p.ex_ld, xo = (static_cast<long long>(b) * p.n_cols + nbase + cl) * p.ex_ld;
                             float e2 = 0.f;
                             for (int k = lane; k < p.k_len; k += 32) {
-                                const float df = (p.ex_a_hi[ao + k] + p.ex_a_lo[ao + k]) - (p.ex_x_hi[xo + k] + p.ex_x_lo[xo + k]);
+                                float av = Split<ES>::get(static_cast<const S*>(p.ex_a_hi) + ao + k, static_cast<const S*>(p.ex_a_lo) + ao + k);
+                                float xv = Split<ES>::get(static_cast<const S*>(p.ex_x_hi) + xo + k, static_cast<const S*>(p.ex_x_lo) + xo + k);
+                                if (ES == 2) {        // third term of the bf16 split: hi + lo + b2 is the row itself
+                                    av += static_cast<float>(static_cast<const S*>(p.ex_a_b2)[ao + k]);
+                                    xv += static_cast<float>(static_cast<const S*>(p.ex_x_b2)[xo + k]);
+                                }
+                                const float df = av - xv;
                                 e2 = fmaf(df, df, e2);
                             }
                             e2 = warp_sum(e2);
@@ -406,9 +451,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                                 lsum += log1pf(e);
                                 col_acc += w;
                                 stg[r * 32 + (lane ^ r)] = w;
-                                const float h = __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
-                                wh[static_cast<long long>(r) * p.ldw] = h;
-                                wl[static_cast<long long>(r) * p.ldw] = w - h;
+                                Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, w);
                             }
                         }
                     }
@@ -441,11 +484,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int r = r0 + i;
-                        if (pad_ok && r < rows_here) {
-                            const float h = __uint_as_float(__float_as_uint(wv[i]) & 0xFFFFE000u);
-                            wh[static_cast<long long>(r) * p.ldw] = h;
-                            wl[static_cast<long long>(r) * p.ldw] = wv[i] - h;
-                        }
+                        if (pad_ok && r < rows_here) Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, wv[i]);
                     }
                 }
             }
@@ -608,15 +647,15 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
 // Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
 // working at the same time share A rows in L2).  Two accumulators in tensor memory alternate, so the epilogue of tile i
 // (tcgen05.ld, scorer epilogue, global stores) overlaps the TMA/MMA main loop of tile i+1.
-template <int GROUP>
+template <int GROUP, int ES>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     // element size 4: tf32 (fp32 storage), 2: bf16.  A shared-memory row is always 128 bytes of K (K-major) or of M/N (MN-major).
-    const int bk = 128 / p.elem_bytes;                  // k-values per stage
-    const int slab_cols = 128 / p.elem_bytes;           // M/N-columns per MN-major slab
+    const int bk = 128 / ES;                  // k-values per stage
+    const int slab_cols = 128 / ES;           // M/N-columns per MN-major slab
     const int slab_bytes = bk * 128;                    // MN-major slab: bk k-rows x 128 bytes
     const int a_slabs = UM_BM / slab_cols;
     const int b_slabs = (p.bn + slab_cols - 1) / slab_cols;
@@ -712,7 +751,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     } else if (warp == 1) {
         // ---- MMA issuer -----------------------------------------------------------------------------------------
         if (lane == 0) {
-            const bool f16 = p.elem_bytes == 2;
+            const bool f16 = ES == 2;
             const uint32_t idesc = umma::instr_desc(f16 ? 1u /* bf16 */ : 2u /* tf32 */, UM_BM, (uint32_t)p.bn, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
             // Descriptor templates: everything but the start address is fixed for the whole kernel, so the issuing thread
             // only adds an address per MMA (it is the one thread feeding the tensor core; its instruction count matters).
@@ -724,7 +763,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
             const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
             const bool single = p.passes == 1;
-            const int kstep_elems = 32 / p.elem_bytes;      // k-values per MMA step
+            const int kstep_elems = 32 / ES;      // k-values per MMA step
             int s = 0; uint32_t ph = 0;
             int lt = 0;                            // tiles done by this CTA
             bool ok = true;
@@ -758,9 +797,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 #pragma unroll
                         for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
                             if (k8 < ksteps) {
-                                umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                                umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
-                                umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                                if (ES == 2) {
+                                    umma::mma_f16(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);  // small terms first
+                                    umma::mma_f16(tmem_d, dah, dbl, idesc, 1u);
+                                    umma::mma_f16(tmem_d, dah, dbh, idesc, 1u);
+                                } else {
+                                    umma::mma_tf32(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                    umma::mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+                                    umma::mma_tf32(tmem_d, dah, dbh, idesc, 1u);
+                                }
                             }
                         }
                     }
@@ -795,7 +840,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
             if (GROUP == G_GROUPED) epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem);
-            else epilogue_tile<G_DENSE>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
+            else epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
     umma::tc_fence_before();
@@ -809,14 +854,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 // this one by the tensor pipe.  The even CTA issues the MMAs for both and commits to the barriers of both; each CTA
 // drains its own 128 accumulator rows.  Dense (non-grouped) products only.  With an MN-major B the last n-tile is
 // narrowed to the columns that exist (in units of two slabs), so a width like 400 costs 448 columns, not 512.
+template <int ES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(UM_THREADS, 1)
 umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
     // the same offset in both CTAs: the dynamic shared-memory window starts at the same address in every CTA of a launch
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const int bk = 128 / p.elem_bytes;
-    const int slab_cols = 128 / p.elem_bytes;
+    const int bk = 128 / ES;
+    const int slab_cols = 128 / ES;
     const int slab_bytes = bk * 128;
     const int a_slabs = UM_BM / slab_cols;
     const int half_n = p.bn / 2;                                          // B columns staged by each CTA (full-width tile)
@@ -914,7 +960,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     } else if (warp == 1) {
         // ---- MMA issuer: the leader only --------------------------------------------------------------------------------
         if (lane == 0 && rank == 0) {
-            const bool f16 = p.elem_bytes == 2;
+            const bool f16 = ES == 2;
             const uint32_t mn_sbo = f16 ? 1024u : 512u, mn_layout = f16 ? 2u : 1u;
             const uint64_t a_tmpl = p.a_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
             const uint64_t b_tmpl = p.b_mn ? umma::smem_desc_mn(0, slab_bytes, mn_sbo, mn_layout) : umma::smem_desc_k_sw128(0);
@@ -922,7 +968,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t b_step = (p.b_mn ? (f16 ? 2048u : 1024u) : 32u) >> 4;
             const uint32_t a_lo_off = UM_A_BYTES >> 4, b_hi_off = (n_parts * UM_A_BYTES) >> 4, b_lo_off = b_hi_off + (b_bytes >> 4);
             const bool single = p.passes == 1;
-            const int kstep_elems = 32 / p.elem_bytes;
+            const int kstep_elems = 32 / ES;
             int s = 0; uint32_t ph = 0;
             int lt = 0;
             bool ok = true;
@@ -956,9 +1002,15 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 #pragma unroll
                         for (int k8 = 0; k8 < 4; ++k8, dah += a_step, dbh += b_step, dal += a_step, dbl += b_step) {
                             if (k8 < ksteps) {
-                                umma::mma_tf32_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);     // small terms first
-                                umma::mma_tf32_pair(tmem_d, dah, dbl, idesc, 1u);
-                                umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, 1u);
+                                if (ES == 2) {
+                                    umma::mma_f16_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);  // small terms first
+                                    umma::mma_f16_pair(tmem_d, dah, dbl, idesc, 1u);
+                                    umma::mma_f16_pair(tmem_d, dah, dbh, idesc, 1u);
+                                } else {
+                                    umma::mma_tf32_pair(tmem_d, dal, dbh, idesc, (kb > 0 || k8 > 0) ? 1u : 0u);
+                                    umma::mma_tf32_pair(tmem_d, dah, dbl, idesc, 1u);
+                                    umma::mma_tf32_pair(tmem_d, dah, dbh, idesc, 1u);
+                                }
                             }
                         }
                     }
@@ -985,7 +1037,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
             if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
-            epilogue_tile<G_DENSE>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
+            epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
                           umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank);
         }
     }
@@ -1031,29 +1083,34 @@ __global__ void __launch_bounds__(256) tc_fixup_kernel(ScoreArgs a, int head, co
 static inline size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 
 struct TcLayout {        // carving of the tensor-core workspace
-    size_t mat;          // bytes of one (n_a + n_x, dim) matrix
-    size_t w;            // bytes of one (batch, n_neg) matrix (backward only)
-    size_t off_hi, off_lo, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, off_colpart, off_rowpart, off_losspart, total;
+    size_t mat;          // bytes of one (n_a + n_x, dim) split matrix
+    size_t w;            // bytes of one (batch, n_neg) split matrix (backward only)
+    size_t off_hi, off_lo, off_b2, off_sq, off_fixc, off_fixl, off_whi, off_wlo, off_rowsum, off_colsum, off_colpart, off_rowpart, off_losspart, total;
     long long loss_parts;    // fused mode: loss partials (one per epilogue warp and 128-row tile)
     int fwd_bn, fwd_pair;    // tiling of the forward product
     unsigned long long fix_cap;
-    int ldp, ldw;        // row pitches in floats: dim and n_neg rounded up to whole 128-byte slabs
+    int es;              // bytes per split element: 2 (bf16 split) or 4 (tf32 split in fp32 storage)
+    int ldp, ldw;        // row pitches in elements: dim and n_neg rounded up to whole 128-byte slabs
+    bool third;          // a third split term is kept (bf16 split, fused distance epilogue: rows rebuilt exactly)
 };
 // CTA pairs pay off once a product has more than one 128-row tile per batch; narrow outputs stay on the one-CTA kernel.
 static bool want_pair(int m_rows, int n_cols) { return m_rows > UM_BM && n_cols >= 64; }
 static int pick_bn(int n);
 
-// mode 0: forward, 1: backward, 2: fused forward + loss + backward
-static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, int mode) {
+// mode 0: forward, 1: backward, 2: fused forward + loss + backward; es: split element size; dist: TransE
+static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, int mode, int es, bool dist) {
     const bool backward = mode != 0;
     TcLayout L;
     const long long n_chunks = batch / chunk;
     const size_t rows = static_cast<size_t>(batch + n_chunks * n_neg);
     const size_t pairs = static_cast<size_t>(batch) * n_neg;
-    L.ldp = (dim + 31) / 32 * 32;
-    L.ldw = (n_neg + 31) / 32 * 32;
-    L.mat = al256(rows * L.ldp * 4);
-    L.w = backward ? al256(static_cast<size_t>(batch) * L.ldw * 4) : 0;
+    const int slab = 128 / es;
+    L.es = es;
+    L.ldp = (dim + slab - 1) / slab * slab;
+    L.ldw = (n_neg + slab - 1) / slab * slab;
+    L.mat = al256(rows * L.ldp * es);
+    L.w = backward ? al256(static_cast<size_t>(batch) * L.ldw * es) : 0;
+    L.third = es == 2 && mode == 2 && dist;
     L.fix_cap = backward ? 0 : (pairs / 64 > 4096 ? pairs / 64 : 4096);
     L.fwd_pair = want_pair(chunk, n_neg) ? 1 : 0;
     L.fwd_bn = L.fwd_pair ? pick_bn(n_neg) : (n_neg >= 128 ? 128 : pick_bn(n_neg));
@@ -1062,6 +1119,7 @@ static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, int mo
     size_t o = 0;
     L.off_hi = o; o += L.mat;
     L.off_lo = o; o += L.mat;
+    L.off_b2 = o; o += L.third ? L.mat : 0;
     L.off_sq = o; o += al256(rows * 4);
     L.off_fixc = o; o += 256;
     L.off_fixl = o; o += al256(L.fix_cap * 8);
@@ -1075,43 +1133,49 @@ static TcLayout tc_layout(long long batch, int chunk, int n_neg, int dim, int mo
     L.total = o;
     return L;
 }
-size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode) {
-    return tc_layout(batch, chunk, n_neg, dim, mode).total;
+// Upper bound over the scorers (the distance scorer's fused call keeps a third split term).
+size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode, int es) {
+    return tc_layout(batch, chunk, n_neg, dim, mode, es, true).total;
 }
 
-template <int MODEL, typename T, typename I>
-static int tc_pack_go(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
+template <int MODEL, typename T, typename I, int ES>
+static int tc_pack_go(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, void* hi, void* lo, void* b2, float* sq, cudaStream_t s) {
     const int nv = quads_per_lane(a.dim);
     const int wpb = 8;
     const unsigned blocks = (unsigned)((n_a + n_x + wpb - 1) / wpb);
     switch (nv) {
-        case 1: tc_pack_kernel<MODEL, T, I, 1><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
-        case 2: tc_pack_kernel<MODEL, T, I, 2><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
-        case 4: tc_pack_kernel<MODEL, T, I, 4><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
-        case 8: tc_pack_kernel<MODEL, T, I, 8><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, sq); break;
+        case 1: tc_pack_kernel<MODEL, T, I, 1, ES><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, b2, sq); break;
+        case 2: tc_pack_kernel<MODEL, T, I, 2, ES><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, b2, sq); break;
+        case 4: tc_pack_kernel<MODEL, T, I, 4, ES><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, b2, sq); break;
+        case 8: tc_pack_kernel<MODEL, T, I, 8, ES><<<blocks, wpb * 32, 0, s>>>(a, head, n_a, n_x, ldp, hi, lo, b2, sq); break;
         default: set_error("dim %d > 1024 is not supported", a.dim); return KGE_E_UNSUPPORTED;
     }
     KGE_LAUNCH_CHECK("tc_pack_kernel");
     return 0;
 }
-template <int MODEL>
-static int tc_pack_types(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
+template <int MODEL, int ES>
+static int tc_pack_types(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, void* hi, void* lo, void* b2, float* sq, cudaStream_t s) {
     if (a.dtype == KGE_F32)
-        return a.id_bits == 64 ? tc_pack_go<MODEL, float, int64_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s)
-                               : tc_pack_go<MODEL, float, int32_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
-    return a.id_bits == 64 ? tc_pack_go<MODEL, __nv_bfloat16, int64_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s)
-                           : tc_pack_go<MODEL, __nv_bfloat16, int32_t>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+        return a.id_bits == 64 ? tc_pack_go<MODEL, float, int64_t, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s)
+                               : tc_pack_go<MODEL, float, int32_t, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
+    return a.id_bits == 64 ? tc_pack_go<MODEL, __nv_bfloat16, int64_t, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s)
+                           : tc_pack_go<MODEL, __nv_bfloat16, int32_t, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
 }
-static int tc_pack(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, float* hi, float* lo, float* sq, cudaStream_t s) {
+template <int ES>
+static int tc_pack_es(const ScoreArgs& a, int head, long long n_a, long long n_x, int ldp, void* hi, void* lo, void* b2, float* sq, cudaStream_t s) {
     switch (a.model) {
-        case KGE_TRANSE: return tc_pack_types<KGE_TRANSE>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
-        case KGE_DISTMULT: return tc_pack_types<KGE_DISTMULT>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
-        case KGE_COMPLEX: return tc_pack_types<KGE_COMPLEX>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
-        case KGE_RESCAL: return tc_pack_types<KGE_RESCAL>(a, head, n_a, n_x, ldp, hi, lo, sq, s);
+        case KGE_TRANSE: return tc_pack_types<KGE_TRANSE, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
+        case KGE_DISTMULT: return tc_pack_types<KGE_DISTMULT, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
+        case KGE_COMPLEX: return tc_pack_types<KGE_COMPLEX, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
+        case KGE_RESCAL: return tc_pack_types<KGE_RESCAL, ES>(a, head, n_a, n_x, ldp, hi, lo, b2, sq, s);
         default: break;
     }
     set_error("model %d is not supported with chunk-shared negatives", a.model);
     return KGE_E_UNSUPPORTED;
+}
+static int tc_pack(const ScoreArgs& a, int head, long long n_a, long long n_x, const TcLayout& L, char* w, float* sq, cudaStream_t s) {
+    void* hi = w + L.off_hi; void* lo = w + L.off_lo; void* b2 = L.third ? w + L.off_b2 : nullptr;
+    return L.es == 2 ? tc_pack_es<2>(a, head, n_a, n_x, L.ldp, hi, lo, b2, sq, s) : tc_pack_es<4>(a, head, n_a, n_x, L.ldp, hi, lo, b2, sq, s);
 }
 
 template <typename T, typename I>
@@ -1162,8 +1226,10 @@ int gemm_profile_read(double* ms, long long* launches, double* flops) {
 
 static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, GemmTc& p,
                     long long batch, cudaStream_t s) {
-    if (p.elem_bytes == 0) p.elem_bytes = 4;
-    if (p.passes == 0) p.passes = 3;
+    if ((p.elem_bytes != 2 && p.elem_bytes != 4) || (p.passes != 1 && p.passes != 3) || (p.tile_tab && p.elem_bytes != 2) || (p.pair && p.passes != 3)) {
+        set_error("tile kernel: element size %d with %d passes is not built", p.elem_bytes, p.passes);
+        return KGE_E_UNSUPPORTED;
+    }
     p.err = device_error_word();
     if (!p.err) { set_error("no device error word"); return KGE_E_DEVICE; }
     int dev = 0, sms = 0;
@@ -1172,9 +1238,11 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
     // the shared-memory opt-in is a per-device attribute of the kernel: remembered per device ordinal
     static std::atomic<bool> attr_set[128];
     if (dev < 0 || dev >= 128 || !attr_set[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<G_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_gemm_kernel<G_GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<G_DENSE, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_gemm_kernel<G_DENSE, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_gemm_kernel<G_GROUPED, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(umma_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_MAX_SMEM);
         if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(tile kernels)");
         if (dev >= 0 && dev < 128) attr_set[dev].store(true, std::memory_order_release);
     }
@@ -1202,11 +1270,13 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
         cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
     }
     if (p.pair) {
-        umma_pair_kernel<<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        if (p.elem_bytes == 2) umma_pair_kernel<2><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        else umma_pair_kernel<4><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_pair_kernel");
     } else {
-        if (p.tile_tab) umma_gemm_kernel<G_GROUPED><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
-        else umma_gemm_kernel<G_DENSE><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        if (p.tile_tab) umma_gemm_kernel<G_GROUPED, 2><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        else if (p.elem_bytes == 2) umma_gemm_kernel<G_DENSE, 2><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        else umma_gemm_kernel<G_DENSE, 4><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_gemm_kernel");
     }
     if (prof) {
@@ -1223,34 +1293,36 @@ int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_byt
     if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 0);
+    const bool dist = a.model == KGE_TRANSE;
+    const int es = a.tc_es == 4 ? 4 : 2, bk = 128 / es;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 0, es, dist);
     if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
-    float* hi = reinterpret_cast<float*>(w + L.off_hi);
-    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    char* hi = w + L.off_hi;
+    char* lo = w + L.off_lo;
     float* sq = reinterpret_cast<float*>(w + L.off_sq);
     unsigned long long* fixc = reinterpret_cast<unsigned long long*>(w + L.off_fixc);
     unsigned long long* fixl = reinterpret_cast<unsigned long long*>(w + L.off_fixl);
-    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, sq, s);
+    int rc = tc_pack(a, head, n_a, n_x, L, w, sq, s);
     if (rc) return rc;
-    const bool dist = a.model == KGE_TRANSE;
     if (dist) {
         cudaError_t e = cudaMemsetAsync(fixc, 0, 8, s);
         if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(fix counter)");
     }
     // n_neg rows need 16-byte row pitch in the output only for vector stores; tensor maps need dim % 4 == 0 (checked)
     CUtensorMap mah, mal, mbh, mbl;
-    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4;
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * es;
     const bool pair = L.fwd_pair != 0;
     const int bn = L.fwd_bn;
     const int b_box = pair ? bn / 2 : bn;           // a CTA of a pair stages half of the tile's columns
-    if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mah, hi, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, lo, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * ld, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * ld, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, bk))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
     p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0; p.pair = pair;
+    p.elem_bytes = es; p.passes = 3;
     p.ep = dist ? EP_DIST : EP_STORE;
     p.out = a.negs; p.out_ld = a.n_neg; p.out_batch_rows = a.chunk;
     p.sq_a = sq; p.sq_b = sq + n_a; p.fix_count = fixc; p.fix_list = fixl; p.fix_cap = L.fix_cap;
@@ -1274,35 +1346,38 @@ static int tc_backward_products(const ScoreArgs& a, const TcLayout& L, char* w, 
                                 cudaStream_t s) {
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch;
-    float* hi = reinterpret_cast<float*>(w + L.off_hi);
-    float* lo = reinterpret_cast<float*>(w + L.off_lo);
-    float* whi = reinterpret_cast<float*>(w + L.off_whi);
-    float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
+    const int es = L.es, bk = 128 / es, slab = 128 / es;
+    char* hi = w + L.off_hi;
+    char* lo = w + L.off_lo;
+    char* whi = w + L.off_whi;
+    char* wlo = w + L.off_wlo;
     float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
     float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
     int rc = 0;
-    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4, lw = static_cast<uint64_t>(L.ldw) * 4;
-    // Pairs with an MN-major B: tiles are whole slabs per CTA (multiples of 64 columns), the last one narrowed by the kernel.
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * es, lw = static_cast<uint64_t>(L.ldw) * es;
+    // Pairs with an MN-major B: tiles are whole slabs per CTA (multiples of two slabs), the last one narrowed by the kernel.
     // The packed matrices have whole-slab pitches, so MN-major operands are read through 4-D slab maps (one copy per stage);
     // the one-CTA kernel keeps per-slab copies for B because its tile width need not be a whole number of slabs.
     const bool pair_ga = want_pair(a.chunk, a.dim), pair_gx = want_pair(a.n_neg, a.dim);
-    const int bn64 = a.dim >= 256 ? 256 : (a.dim + 63) / 64 * 64;
-    const float* xhi = hi + n_a * L.ldp;
-    const float* xlo = lo + n_a * L.ldp;
+    const int unit = 2 * slab;
+    const int bnp = a.dim >= 256 ? 256 : (a.dim + unit - 1) / unit * unit;
+    const char* xhi = hi + n_a * ld;
+    const char* xlo = lo + n_a * ld;
     CUtensorMap mah, mal, mbh, mbl;
     GemmTc p;
     // GA = W . X : A = W K-major (rows i, K = j), B = X MN-major (N = dim, K rows = j)
     memset(&p, 0, sizeof(p));
-    p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = pair_ga ? bn64 : pick_bn(a.dim); p.a_mn = 0; p.b_mn = 1; p.pair = pair_ga;
-    if ((rc = make_tensor_map_3d(&mah, whi, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mal, wlo, 4, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, UM_BK))) return rc;
+    p.m_rows = a.chunk; p.n_cols = a.dim; p.k_len = a.n_neg; p.bn = pair_ga ? bnp : pick_bn(a.dim); p.a_mn = 0; p.b_mn = 1; p.pair = pair_ga;
+    p.elem_bytes = es; p.passes = 3;
+    if ((rc = make_tensor_map_3d(&mah, whi, es, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, wlo, es, n_chunks, a.chunk, a.n_neg, lw, lw * a.chunk, UM_BM, bk))) return rc;
     if (pair_ga) {
         p.b_slabs4d = 1;
-        if ((rc = make_tensor_map_slabs(&mbh, xhi, 4, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, UM_BK, bn64 / 64))) return rc;
-        if ((rc = make_tensor_map_slabs(&mbl, xlo, 4, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, UM_BK, bn64 / 64))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbh, xhi, es, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, bk, bnp / unit))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbl, xlo, es, n_chunks, a.n_neg, L.ldp, ld, ld * a.n_neg, bk, bnp / unit))) return rc;
     } else {
-        if ((rc = make_tensor_map_3d(&mbh, xhi, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
-        if ((rc = make_tensor_map_3d(&mbl, xlo, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, UM_BK, 32, true))) return rc;
+        if ((rc = make_tensor_map_3d(&mbh, xhi, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bk, slab, es == 4))) return rc;
+        if ((rc = make_tensor_map_3d(&mbl, xlo, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, bk, slab, es == 4))) return rc;
     }
     p.ep = EP_STORE;
     p.out = ga; p.out_ld = a.dim; p.out_batch_rows = a.chunk;
@@ -1310,17 +1385,18 @@ static int tc_backward_products(const ScoreArgs& a, const TcLayout& L, char* w, 
     if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
     // GX = W^T . A : A-operand = W MN-major (M = j, K rows = i), B = anchors MN-major (N = dim, K rows = i)
     memset(&p, 0, sizeof(p));
-    p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = pair_gx ? bn64 : pick_bn(a.dim); p.a_mn = 1; p.b_mn = 1; p.pair = pair_gx;
+    p.m_rows = a.n_neg; p.n_cols = a.dim; p.k_len = a.chunk; p.bn = pair_gx ? bnp : pick_bn(a.dim); p.a_mn = 1; p.b_mn = 1; p.pair = pair_gx;
+    p.elem_bytes = es; p.passes = 3;
     p.a_slabs4d = 1;
-    if ((rc = make_tensor_map_slabs(&mah, whi, 4, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, UM_BK, UM_BM / 32))) return rc;
-    if ((rc = make_tensor_map_slabs(&mal, wlo, 4, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, UM_BK, UM_BM / 32))) return rc;
+    if ((rc = make_tensor_map_slabs(&mah, whi, es, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, bk, UM_BM / slab))) return rc;
+    if ((rc = make_tensor_map_slabs(&mal, wlo, es, n_chunks, a.chunk, L.ldw, lw, lw * a.chunk, bk, UM_BM / slab))) return rc;
     if (pair_gx) {
         p.b_slabs4d = 1;
-        if ((rc = make_tensor_map_slabs(&mbh, hi, 4, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, UM_BK, bn64 / 64))) return rc;
-        if ((rc = make_tensor_map_slabs(&mbl, lo, 4, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, UM_BK, bn64 / 64))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbh, hi, es, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, bk, bnp / unit))) return rc;
+        if ((rc = make_tensor_map_slabs(&mbl, lo, es, n_chunks, a.chunk, L.ldp, ld, ld * a.chunk, bk, bnp / unit))) return rc;
     } else {
-        if ((rc = make_tensor_map_3d(&mbh, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
-        if ((rc = make_tensor_map_3d(&mbl, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BK, 32, true))) return rc;
+        if ((rc = make_tensor_map_3d(&mbh, hi, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, bk, slab, es == 4))) return rc;
+        if ((rc = make_tensor_map_3d(&mbl, lo, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, bk, slab, es == 4))) return rc;
     }
     p.ep = dist ? EP_RANK1 : EP_STORE;
     p.out = a.g_neg; p.out_ld = a.dim; p.out_batch_rows = a.n_neg;
@@ -1338,29 +1414,31 @@ int launch_pair_backward_tc(const ScoreArgs& a, int head, float* ga, const float
     if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 1);
+    const bool dist = a.model == KGE_TRANSE;
+    const int es = a.tc_es == 4 ? 4 : 2;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 1, es, dist);
     if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
-    float* hi = reinterpret_cast<float*>(w + L.off_hi);
-    float* lo = reinterpret_cast<float*>(w + L.off_lo);
-    float* whi = reinterpret_cast<float*>(w + L.off_whi);
-    float* wlo = reinterpret_cast<float*>(w + L.off_wlo);
+    void* whi = w + L.off_whi;
+    void* wlo = w + L.off_wlo;
     float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
     float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
     float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
-    const bool dist = a.model == KGE_TRANSE;
-    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, nullptr, s);
+    int rc = tc_pack(a, head, n_a, n_x, L, w, nullptr, s);
     if (rc) return rc;
     if (dist) {
         const int bpc = (a.chunk + TW_ROWS - 1) / TW_ROWS;
-        tc_pack_w_sums_kernel<<<dim3(bpc, (unsigned)n_chunks), 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
+        const dim3 grid(bpc, (unsigned)n_chunks);
+        if (es == 2) tc_pack_w_sums_kernel<2><<<grid, 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
+        else tc_pack_w_sums_kernel<4><<<grid, 256, 0, s>>>(a.dneg, a.negs, a.chunk, a.n_neg, L.ldw, whi, wlo, rowsum, colpart);
         KGE_LAUNCH_CHECK("tc_pack_w_sums_kernel");
         tc_colsum_kernel<<<dim3((a.n_neg + 255) / 256, (unsigned)n_chunks), 256, 0, s>>>(colpart, bpc, a.n_neg, colsum);
         KGE_LAUNCH_CHECK("tc_colsum_kernel");
     } else {
         const int wpb = 8;
         const unsigned blocks = (unsigned)((a.batch + wpb - 1) / wpb);
-        tc_pack_w_kernel<<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
+        if (es == 2) tc_pack_w_kernel<2><<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
+        else tc_pack_w_kernel<4><<<blocks, wpb * 32, 0, s>>>(a.dneg, a.batch, a.n_neg, L.ldw, whi, wlo);
         KGE_LAUNCH_CHECK("tc_pack_w_kernel");
     }
     return tc_backward_products(a, L, w, dist, ga, ga_scale, s);
@@ -1406,37 +1484,40 @@ int launch_pair_loss_backward_tc(const ScoreArgs& a, int head, float neg_w, floa
     if (a.dim % 4 != 0) { set_error("the tensor-core path needs dim %% 4 == 0 (16-byte rows), got %d", a.dim); return KGE_E_UNSUPPORTED; }
     const long long n_chunks = a.batch / a.chunk;
     const long long n_a = a.batch, n_x = n_chunks * a.n_neg;
-    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 2);
+    const bool dist = a.model == KGE_TRANSE;
+    const int es = a.tc_es == 4 ? 4 : 2, bk = 128 / es;
+    const TcLayout L = tc_layout(a.batch, a.chunk, a.n_neg, a.dim, 2, es, dist);
     if (ws_bytes < L.total) { set_error("tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
     char* w = static_cast<char*>(ws);
-    float* hi = reinterpret_cast<float*>(w + L.off_hi);
-    float* lo = reinterpret_cast<float*>(w + L.off_lo);
+    char* hi = w + L.off_hi;
+    char* lo = w + L.off_lo;
     float* sq = reinterpret_cast<float*>(w + L.off_sq);
     float* rowsum = reinterpret_cast<float*>(w + L.off_rowsum);
     float* colsum = reinterpret_cast<float*>(w + L.off_colsum);
     float* colpart = reinterpret_cast<float*>(w + L.off_colpart);
     float* rowpart = reinterpret_cast<float*>(w + L.off_rowpart);
     float* losspart = reinterpret_cast<float*>(w + L.off_losspart);
-    const bool dist = a.model == KGE_TRANSE;
-    int rc = tc_pack(a, head, n_a, n_x, L.ldp, hi, lo, sq, s);
+    int rc = tc_pack(a, head, n_a, n_x, L, w, sq, s);
     if (rc) return rc;
     CUtensorMap mah, mal, mbh, mbl;
-    const uint64_t ld = static_cast<uint64_t>(L.ldp) * 4;
+    const uint64_t ld = static_cast<uint64_t>(L.ldp) * es;
     const bool pair = L.fwd_pair != 0;
     const int bn = L.fwd_bn;
     const int b_box = pair ? bn / 2 : bn;
-    if ((rc = make_tensor_map_3d(&mah, hi, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mal, lo, 4, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * L.ldp, 4, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, UM_BK))) return rc;
+    if ((rc = make_tensor_map_3d(&mah, hi, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, lo, es, n_chunks, a.chunk, a.dim, ld, ld * a.chunk, UM_BM, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, hi + n_a * ld, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, bk))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, lo + n_a * ld, es, n_chunks, a.n_neg, a.dim, ld, ld * a.n_neg, b_box, bk))) return rc;
     GemmTc p;
     memset(&p, 0, sizeof(p));
     p.m_rows = a.chunk; p.n_cols = a.n_neg; p.k_len = a.dim; p.bn = bn; p.a_mn = 0; p.b_mn = 0; p.pair = pair;
+    p.elem_bytes = es; p.passes = 3;
     p.ep = EP_LOSS;
     p.sq_a = sq; p.sq_b = sq + n_a; p.loss_dist = dist ? 1 : 0; p.neg_w = neg_w;
-    p.w_hi = reinterpret_cast<float*>(w + L.off_whi); p.w_lo = reinterpret_cast<float*>(w + L.off_wlo); p.ldw = L.ldw;
+    p.w_hi = w + L.off_whi; p.w_lo = w + L.off_wlo; p.ldw = L.ldw;
     p.rowpart = rowpart; p.colpart = colpart; p.loss_part = losspart;
-    p.ex_a_hi = hi; p.ex_a_lo = lo; p.ex_x_hi = hi + n_a * L.ldp; p.ex_x_lo = lo + n_a * L.ldp; p.ex_ld = L.ldp;
+    p.ex_a_hi = hi; p.ex_a_lo = lo; p.ex_x_hi = hi + n_a * ld; p.ex_x_lo = lo + n_a * ld; p.ex_ld = L.ldp;
+    if (L.third) { p.ex_a_b2 = w + L.off_b2; p.ex_x_b2 = w + L.off_b2 + n_a * ld; }
     if ((rc = run_gemm(mah, mal, mbh, mbl, p, n_chunks, s))) return rc;
     const long long tiles_n = (a.n_neg + bn - 1) / bn;
     const long long tiles = tiles_n * ((a.chunk + (pair ? 2 : 1) * UM_BM - 1) / ((pair ? 2 : 1) * UM_BM)) * n_chunks;

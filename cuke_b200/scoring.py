@@ -387,7 +387,7 @@ class Scorer:
     def supports_fused_step(self, n_neg: int) -> bool:
         """True where loss_backward applies: tensor precision and either chunk-shared negatives with TransE / DistMult /
         ComplEx, or TransR over bf16 tables with per-triple negatives."""
-        if self.precision != PRECISIONS["tensor"]:
+        if self.precision == PRECISIONS["fp32"]:
             return False
         if self.model == "TransR":
             return (self.ent.dtype == torch.bfloat16 and self.dim % 8 == 0 and self.dim <= 256 and self.neg_mode != "chunk_shared")

@@ -72,9 +72,13 @@ enum kge_dtype { KGE_F32 = 0, KGE_BF16 = 1 };   /* storage type of the tables; a
 
 enum kge_precision {
     KGE_PREC_FP32 = 0,    /* fp32 CUDA-core arithmetic throughout (default) */
-    KGE_PREC_TENSOR = 1   /* contractions on the tensor cores where a kernel exists: fp32 tables as 3-term split tf32
-                             ("3xTF32", product error ~2^-20, same 1e-4 tolerance), bf16 tables as bf16 MMA with fp32
-                             accumulation; everything else as KGE_PREC_FP32 */
+    KGE_PREC_TENSOR = 1,  /* contractions on the tensor cores where a kernel exists.  fp32 operands are split in two bf16
+                             terms, v ~ hi + lo (16 mantissa bits), and a product is three bf16 MMAs (lo.hi + hi.lo + hi.hi)
+                             accumulated in fp32: relative product error ~2^-16, inside the 1e-4 tolerance, at the full
+                             tensor rate and 4 operand bytes per element; bf16 tables as one bf16 MMA; everything else as
+                             KGE_PREC_FP32 */
+    KGE_PREC_TENSOR_TF32 = 2  /* as KGE_PREC_TENSOR with fp32 operands split in two tf32 terms ("3xTF32": product error
+                             ~2^-20, half the tensor rate, 8 operand bytes per element) */
 };
 
 enum kge_neg_mode {

@@ -12,6 +12,7 @@ from tests.kge_testlib import (BF16_TOL, FP32_TOL, MODELS, bf16_round, gpu_grads
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TENSOR_PRECISIONS = ["tensor", "tensor_tf32"]      # fp32 operands as two bf16 terms (default) or two tf32 terms
 CHUNK_MODELS = ["TransE", "DistMult", "ComplEx", "RESCAL"]
 BWD_MODELS = ["TransE", "TransH", "TransR", "TransF", "DistMult", "RESCAL", "ComplEx"]
 
@@ -89,15 +90,17 @@ def test_score_forward_chunk_shared(model, d, chunk, nchunks, nn, head):
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (64, 128, 2, 256, 0), (400, 256, 2, 384, 0),
                                                      (200, 130, 2, 150, 1), (36, 7, 3, 9, 0), (512, 1024, 1, 1024, 0),
                                                      (100, 384, 2, 200, 0), (64, 520, 1, 1000, 1)])
-def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
-    """3xTF32 tcgen05 path of the chunk-shared dot-product scorers: same 1e-4 tolerance as the fp32 CUDA-core path."""
+@pytest.mark.parametrize("prec", TENSOR_PRECISIONS)
+def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head, prec):
+    """tcgen05 path of the chunk-shared dot-product scorers (fp32 operands split in two bf16 or two tf32 terms, three MMAs
+    per product): same 1e-4 tolerance as the fp32 CUDA-core path."""
     from cuke_b200 import scoring
     if model == "RESCAL":
         head = 0
         d = min(d, 200)
     p = make_problem(model, seed=7 * d + chunk, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
     nnh = nn if head else 0
-    sc = gpu_scorer(p, nnh, precision="tensor")
+    sc = gpu_scorer(p, nnh, precision=prec)
     h, r, t, neg = gpu_ids(p)
     pos, negs, _ = sc.forward(h, r, t, neg)
     assert scoring.device_flags() == 0, "a bounded wait inside the tensor-core kernel ran out"
@@ -109,8 +112,9 @@ def test_score_forward_tensor_cores(model, d, chunk, nchunks, nn, head):
     assert torch.equal(negs, negs2)
 
 
+@pytest.mark.parametrize("prec", TENSOR_PRECISIONS)
 @pytest.mark.parametrize("frac,overflow", [(0.004, False), (0.05, False), (0.5, True)])
-def test_transe_tensor_cores_cancellation(frac, overflow):
+def test_transe_tensor_cores_cancellation(frac, overflow, prec):
     """TransE on the tensor cores uses |a|^2+|x|^2-2a.x; negatives that (nearly) coincide with the anchor cancel there
     and must come out exact through the fix-up list - or, when the list overflows, through the exact kernel."""
     from cuke_b200 import scoring
@@ -132,7 +136,7 @@ def test_transe_tensor_cores_cancellation(frac, overflow):
         E[3000:4000] = anchor0[None, :] * (1.0 + 1e-3 * g.standard_normal((1000, d))).astype(np.float32)
         p["h"][:] = p["h"][0]; p["r"][:] = p["r"][0]
         p["neg"][:] = g.integers(3000, 4000, p["neg"].shape)
-    sc = gpu_scorer(p, 0, precision="tensor")
+    sc = gpu_scorer(p, 0, precision=prec)
     pos, negs, _ = sc.forward(*gpu_ids(p))
     assert scoring.device_flags() == 0
     rpos, rneg = oracle.scores("TransE", E, R, None, p["h"], p["r"], p["t"], p["neg"], "chunk_shared", 0, chunk)
@@ -147,13 +151,14 @@ def test_transe_tensor_cores_cancellation(frac, overflow):
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
                                                      (36, 7, 4, 12, 0), (512, 512, 1, 1024, 0), (100, 384, 2, 200, 0),
                                                      (72, 520, 1, 1000, 1), (40, 260, 2, 129, 0), (36, 7, 3, 9, 0)])
-def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head):
+@pytest.mark.parametrize("prec", TENSOR_PRECISIONS)
+def test_backward_tensor_cores(model, d, chunk, nchunks, nn, head, prec):
     from cuke_b200 import scoring
     if model == "RESCAL":
         head = 0
         d = min(d, 200)
     p = make_problem(model, seed=11 * d + chunk, ne=600, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
-    _check_grads(p, nn if head else 0, chunk, precision="tensor")
+    _check_grads(p, nn if head else 0, chunk, precision=prec)
     assert scoring.device_flags() == 0
 
 
@@ -165,13 +170,14 @@ def _softplus(x):
 @pytest.mark.parametrize("d,chunk,nchunks,nn,head", [(32, 128, 1, 128, 0), (400, 256, 2, 384, 0), (200, 130, 2, 152, 1),
                                                      (36, 7, 4, 12, 0), (100, 384, 2, 200, 0), (72, 520, 1, 1000, 1),
                                                      (40, 260, 2, 129, 0), (36, 7, 3, 9, 0)])
-def test_fused_loss_backward(model, d, chunk, nchunks, nn, head):
+@pytest.mark.parametrize("prec", TENSOR_PRECISIONS)
+def test_fused_loss_backward(model, d, chunk, nchunks, nn, head, prec):
     """kge_score_loss_backward = forward -> logistic loss -> backward without the score matrix: the loss against the
     oracle's scores (float64 softplus), positives and gradient rows against the unfused calls, all at the fp32 tolerance."""
     from cuke_b200 import scoring
     p = make_problem(model, seed=13 * d + chunk, ne=600, d=d, B=chunk * nchunks, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
     nnh = nn if head else 0
-    sc = gpu_scorer(p, nnh, precision="tensor")
+    sc = gpu_scorer(p, nnh, precision=prec)
     assert sc.supports_fused_step(nn)
     h, r, t, neg = gpu_ids(p)
     pos, loss, sg = sc.loss_backward(h, r, t, neg)
@@ -190,7 +196,8 @@ def test_fused_loss_backward(model, d, chunk, nchunks, nn, head):
     assert torch.equal(loss, loss2) and torch.equal(sg.ent_slots, sg2.ent_slots) and torch.equal(sg.rel_slots, sg2.rel_slots)
 
 
-def test_fused_loss_backward_cancellation():
+@pytest.mark.parametrize("prec", TENSOR_PRECISIONS)
+def test_fused_loss_backward_cancellation(prec):
     """TransE negatives that (nearly) coincide with their anchor: the fused epilogue recomputes those distances from the
     rows themselves, so loss and gradients still match the unfused exact path."""
     from cuke_b200 import scoring
@@ -205,7 +212,7 @@ def test_fused_loss_backward_cancellation():
             row = 3000 + c * 24 + k
             E[row] = anchor * (1.0 + (1e-3 * g.standard_normal(d)).astype(np.float32) * (k % 2))
             p["neg"][c, k] = row
-    sc = gpu_scorer(p, 0, precision="tensor")
+    sc = gpu_scorer(p, 0, precision=prec)
     sc_exact = gpu_scorer(p, 0)                      # CUDA-core fp32 path
     h, r, t, neg = gpu_ids(p)
     pos, loss, sg = sc.loss_backward(h, r, t, neg)
