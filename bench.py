@@ -57,6 +57,9 @@ def parse():
                     help="profiling aid: run forward+backward of the scorers 3 times on a reduced case (--chunks chunks, "
                          "entity table scaled down to fit a few GB) and exit; meant to be run under ncu -k <kernel>")
     ap.add_argument("--chunks", type=int, default=32)
+    ap.add_argument("--micro", type=int, default=0,
+                    help="micro-batches per step (0 = 1 on one GPU, 2 on several: the row exchanges of one micro-batch travel while "
+                         "the other computes)")
     ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor", "tensor_tf32"],
                     help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
@@ -244,8 +247,9 @@ def workload_config(cfg, models, n_gpus):
             "dim": cfg.dim, "n_ent": cfg.n_ent, "n_rel": cfg.n_rel, "parallelism": f"dp{n_gpus}+row-sharded-entities",
             "step": "inspector, staging (row exchange), forward + logistic loss + backward, segmented gradient reduction (owner-side sum), "
                     "sparse SGD update of the touched rows, for both scorers",
-            "pipelining": "the inspection of batch i+1 (N>1: and its id exchange) runs on a side stream during step i; "
-                          "the timed region ends after the last update",
+            "pipelining": "the inspection of batch i+1 (N>1: and its id exchange) runs on a side stream during step i; N>1: a step "
+                          "is cut into micro-batches (`micro_batches`) whose row exchanges travel while another micro-batch "
+                          "computes; the timed region ends after the last update",
             "l2": "inputs larger than L2 (6.4 GB table, 76 MB staged rows, 2 x 268 MB of split gradient weights per scorer; "
                   "the 268 MB score matrix is consumed inside the tile kernel); no flush"}
 
@@ -508,8 +512,9 @@ def main():
     # learning rate is set so that the few hundred steps of a benchmark run leave the table in its initial distribution;
     # the update's memory traffic and launches do not depend on its value)
     optimizer = None if args.no_optimizer else ("sgd", 1e-8)
+    micro = args.micro if args.micro > 0 else (2 if world > 1 else 1)
     stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group,
-                      precision=args.precision, optimizer=optimizer)
+                      precision=args.precision, optimizer=optimizer, micro=micro)
 
     nb = 4
     host = []
@@ -607,7 +612,7 @@ def main():
         if world == 1:
             parity = parity_single_gpu(cfg, models, stepper, ent_local, rel, devb, dev)
         else:
-            parity = sharded_selfcheck(rank, world, group, precision=args.precision)
+            parity = sharded_selfcheck(rank, world, group, precision=args.precision, n_chunks=2 * micro, micro=micro)
             if rank == 0:
                 parity["against"] = "the same step on one GPU with the whole table (GPU against GPU)"
     except Exception as e:          # reported, never hidden
@@ -738,7 +743,7 @@ def main():
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), arithmetic=(
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), micro_batches=micro, arithmetic=(
                     "fp32 storage and accumulation; contractions on the tensor cores over a two-term bf16 split of each fp32 "
                     "operand (three MMAs per product, error-compensated; see the parity block for the measured error)"
                     if args.precision == "tensor" else

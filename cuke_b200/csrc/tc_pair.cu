@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) tc_colsum_kernel(const float* colpart, in
 constexpr int UM_BM = 128, UM_BK = 32;                       // 32 fp32 = one 128-byte swizzle row
 constexpr int UM_A_BYTES = UM_BM * UM_BK * 4;                // 16 KiB per A tile (either major)
 constexpr int UM_SLAB_BYTES = UM_BK * 128;                   // one MN-major slab: 32 k-rows x 128 bytes
-constexpr int UM_EPI_BYTES = 8 * 32 * 32 * 4;                // epilogue staging: one 32x32 fp32 square per epilogue warp
+constexpr int UM_EPI_BYTES = 8 * 32 * 32 * 4 + 8 * 32 * 4;   // per epilogue warp: one 32x32 fp32 square, then one 32-float strip
 constexpr int UM_TAIL_BYTES = 256 + UM_EPI_BYTES;            // barriers and tensor-memory slot, then the staging squares
 constexpr int UM_MAX_SMEM = 227 * 1024;                     // opt-in shared memory per CTA on sm_100
 
@@ -322,112 +322,159 @@ constexpr int UM_EPI_WARPS = 8;
 // row of THIS CTA's 128 rows.  `drained` is the (shared::cluster) address of the barrier that hands the accumulator
 // back to the MMA thread; every warp arrives on it once its tensor-memory reads are done.
 //
-// tcgen05.ld hands each thread one ROW of the chunk (32 consecutive columns).  Written out like that, a warp's store
-// instruction would touch 32 different rows, and every per-column operand would be a separate load per element.  So the
-// chunk goes through a 32x32 XOR-swizzled shared-memory staging square (conflict-free both ways) and comes back with
-// lane = COLUMN: global loads and stores are then 128-byte row segments, per-column operands are one register per lane,
-// per-row operands one shuffle per row, and the fix-up test is a mask bit instead of a branch per element.
+// tcgen05.ld hands each thread one ROW of the chunk (32 consecutive columns), and the epilogues work in that layout:
+// a thread's 32 values are one contiguous 128-byte (fp32) or 64-byte (bf16) piece of its destination row, written with
+// 16-byte stores; everything per ROW (squared norm, scale, destination pointers) is a register of the owning thread
+// computed once per tile; a per-COLUMN operand (the squared norms of the distance forms) sits in a 32-float strip of the
+// warp, refilled per chunk and read as 128-bit broadcasts; the 32 elements of a thread are 32 independent dependency
+// chains, which is what keeps the special-function pipe busy with two warps per scheduler.  Only the column sums of the
+// fused distance form cross rows: they go through the warp's XOR-swizzled 32x32 square once per chunk.
 // GROUP selects which epilogues an instantiation of the one-CTA kernel carries: G_DENSE the dense chunk-shared products
 // (store, distance, rank-1, fused loss; epilogue_tile below), G_GROUPED the relation-grouped products (store, norm, dL/dv
 // rows, scatter; epilogue_grouped).  Two instantiations keep the register allocation of each set independent of the other.
 enum { G_DENSE = 0, G_GROUPED = 1 };
+
+// 32 fp32 values of one row -> out[0..lim): 16-byte stores when the row is 16-byte aligned and lim a multiple of 4
+__device__ __forceinline__ void store_row32(float* out, const float (&v)[32], int lim, bool vec) {
+    if (vec) {
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4)
+            if (4 * j4 < lim) *reinterpret_cast<float4*>(out + 4 * j4) = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < lim) out[j] = v[j];
+    }
+}
+// 32 values of one row as split elements: columns [0, wlim) of hi / lo, wlim a multiple of 16
+__device__ __forceinline__ void put_row32(float* hi, float* lo, const float (&v)[32], int wlim) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4)
+        if (4 * j4 < wlim) put_quad(hi + 4 * j4, lo + 4 * j4, nullptr, make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
+}
+__device__ __forceinline__ void put_row32(__nv_bfloat16* hi, __nv_bfloat16* lo, const float (&v)[32], int wlim) {
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+        if (8 * j8 < wlim) {
+            float4 h0, h1, t;
+            const uint2 a0 = bf16x4(make_float4(v[8 * j8], v[8 * j8 + 1], v[8 * j8 + 2], v[8 * j8 + 3]), h0);
+            const uint2 a1 = bf16x4(make_float4(v[8 * j8 + 4], v[8 * j8 + 5], v[8 * j8 + 6], v[8 * j8 + 7]), h1);
+            *reinterpret_cast<uint4*>(hi + 8 * j8) = make_uint4(a0.x, a0.y, a1.x, a1.y);
+            const uint2 l0 = bf16x4(make_float4(v[8 * j8] - h0.x, v[8 * j8 + 1] - h0.y, v[8 * j8 + 2] - h0.z, v[8 * j8 + 3] - h0.w), t);
+            const uint2 l1 = bf16x4(make_float4(v[8 * j8 + 4] - h1.x, v[8 * j8 + 5] - h1.y, v[8 * j8 + 6] - h1.z, v[8 * j8 + 7] - h1.w), t);
+            *reinterpret_cast<uint4*>(lo + 8 * j8) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+        }
+    }
+}
+// y[0..32) = hi + lo of 32 consecutive split elements (16-byte aligned; the pitch padding makes the whole read legal)
+__device__ __forceinline__ void get_row32(const float* hi, const float* lo, float (&y)[32]) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 h = __ldg(reinterpret_cast<const float4*>(hi) + j4), l = __ldg(reinterpret_cast<const float4*>(lo) + j4);
+        y[4 * j4] = h.x + l.x; y[4 * j4 + 1] = h.y + l.y; y[4 * j4 + 2] = h.z + l.z; y[4 * j4 + 3] = h.w + l.w;
+    }
+}
+__device__ __forceinline__ void get_row32(const __nv_bfloat16* hi, const __nv_bfloat16* lo, float (&y)[32]) {
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+        const uint4 h = __ldg(reinterpret_cast<const uint4*>(hi) + j8), l = __ldg(reinterpret_cast<const uint4*>(lo) + j8);
+        const uint32_t hw[4] = {h.x, h.y, h.z, h.w}, lw[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {      // a 32-bit word holds two bf16: the low half is the even element
+            y[8 * j8 + 2 * i] = __uint_as_float(hw[i] << 16) + __uint_as_float(lw[i] << 16);
+            y[8 * j8 + 2 * i + 1] = __uint_as_float(hw[i] & 0xFFFF0000u) + __uint_as_float(lw[i] & 0xFFFF0000u);
+        }
+    }
+}
+
 template <int GROUP, int ES>
 __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
                                               int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot) {
+    using S = typename Split<ES>::T;
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    const int row = q * 32 + lane;                 // row of the tile held by this thread after tcgen05.ld
     const int n_chunks32 = (bn_tile + 31) / 32;
-    const int m = m0 + row;
-    const bool row_ok = m < p.m_rows;
-    const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
-    float* stg = epi_smem + (warp - 2) * 1024;                  // this warp's 32x32 staging square
     const int mq = m0 + q * 32;                                  // first row of this warp's quarter
+    const int m = mq + lane;                                     // this thread's row of the batch
+    const bool row_ok = m < p.m_rows;
     const int rows_here = min(32, p.m_rows - mq);               // rows of the quarter that exist (may be <= 0)
-    const long long grow0 = static_cast<long long>(b) * p.m_rows + mq;        // row of A-side per-row vectors
-    // per-row operands live in the lane that owns the row and are broadcast by shuffle
+    const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
+    float* stg = epi_smem + (warp - 2) * 1024;                  // this warp's 32x32 square (column sums of W)
+    float* strip = epi_smem + UM_EPI_WARPS * 1024 + (warp - 2) * 32;      // this chunk's per-column operand
+    const long long grow0 = static_cast<long long>(b) * p.m_rows + mq;        // first row of the quarter in per-row vectors
+    const long long grow = grow0 + lane;
+    const float inf = __int_as_float(0x7f800000);
+    const bool dist_form = p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist);
+    // per-row operands of the owning thread.  Distance forms: rows past the end carry a squared norm of +inf, which turns
+    // each of their entries into an exact zero without a test per element.
     float row_op = 0.f;
-    if (row_ok) {
-        if (GROUP == G_DENSE && (p.ep == EP_DIST || (p.ep == EP_LOSS && p.loss_dist))) row_op = p.sq_a[grow0 + lane];
-        else if (GROUP == G_DENSE && p.ep == EP_RANK1) row_op = p.scale[grow0 + lane];
-    }
-    float loss_acc = 0.f, row_acc = 0.f;         // EP_LOSS: this thread's loss terms; this thread's (= row's) sum of W
+    if (dist_form) row_op = row_ok ? p.sq_a[grow] : inf;
+    else if (p.ep == EP_RANK1 && row_ok) row_op = p.scale[grow];
+    float* orow = (row_ok && p.ep != EP_LOSS) ? p.out + (static_cast<long long>(b) * p.out_batch_rows + m) * p.out_ld : nullptr;
+    const bool vec_out = (p.out_ld & 3) == 0;
+    S* wh = nullptr; S* wl = nullptr;
+    if (p.ep == EP_LOSS && row_ok) { wh = static_cast<S*>(p.w_hi) + grow * p.ldw; wl = static_cast<S*>(p.w_lo) + grow * p.ldw; }
+    const S* yh = nullptr; const S* yl = nullptr;
+    if (p.ep == EP_RANK1 && row_ok) { yh = static_cast<const S*>(p.y_hi) + grow * p.y_ld; yl = static_cast<const S*>(p.y_lo) + grow * p.y_ld; }
+    const float nw = p.neg_w;
+    float lsum = 0.f, row_acc = 0.f;             // EP_LOSS: this thread's loss terms (unscaled); this row's sum of W
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
         const int nbase = n0 + c * 32;
         const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
-        const bool col_ok = lane < lim;
-        const int col = nbase + lane;
         float y[32];
-        if (GROUP == G_DENSE && p.ep == EP_RANK1) {          // the y rows come from memory: requested before the accumulator is read
-            using S = typename Split<ES>::T;
-            const S* yh = static_cast<const S*>(p.y_hi) + grow0 * p.y_ld + col;
-            const S* yl = static_cast<const S*>(p.y_lo) + grow0 * p.y_ld + col;
+        if (p.ep == EP_RANK1) {                  // the y row comes from memory: requested before the accumulator is read
+            if (yh != nullptr && lim > 0) get_row32(yh + nbase, yl + nbase, y);
+            else {
 #pragma unroll
-            for (int r = 0; r < 32; ++r) {
-                const long long off = static_cast<long long>(r) * p.y_ld;
-                y[r] = (col_ok && r < rows_here) ? Split<ES>::get(yh + off, yl + off) : 0.f;
+                for (int j = 0; j < 32; ++j) y[j] = 0.f;
             }
         }
         float v[32];
         umma::tmem_ld32(t_row + c * 32, v);         // warp-collective
         if (rows_here <= 0 || lim <= 0) continue;    // warp-uniform
-#pragma unroll
-        for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
-        __syncwarp();
-        if (GROUP == G_DENSE && p.ep == EP_LOSS) {
-            using S = typename Split<ES>::T;
-            S* wh = static_cast<S*>(p.w_hi) + grow0 * p.ldw + col;
-            S* wl = static_cast<S*>(p.w_lo) + grow0 * p.ldw + col;
-            const bool pad_ok = col < p.ldw;         // pitch padding past the last column is written as zero
-            const float nw = p.neg_w;
-            float lsum = 0.f;                        // loss terms of this chunk, scaled by neg_w once at the end
+        if (dist_form) {
+            __syncwarp();                            // the previous chunk's reads of the strip are done
+            strip[lane] = lane < lim ? p.sq_b[static_cast<long long>(b) * p.n_cols + nbase + lane] : inf;
+            __syncwarp();
+        }
+        if (p.ep == EP_LOSS) {
+            // columns this chunk writes: its own, and - in the chunk that holds the last column - the zero padding of the pitch
+            const int wlim = nbase + lim >= p.n_cols ? static_cast<int>(min(32LL, p.ldw - nbase)) : lim;
             if (p.loss_dist) {
                 // S = -dd, dd = sqrt(d2) >= 0: softplus(S) = log1p(e), sigmoid(S) = e / (1 + e) with e = exp(-dd), and
-                // W = dS / S = -neg_w e / ((1 + e) dd).  The loop body has no branches, so rows overlap in the pipeline:
-                // columns past the end carry sq_b = +inf and entries whose d2 cancels are set to +inf too - both then
-                // contribute exact zeros - and the cancelling entries are redone from the rows themselves after the loop.
-                const float inf = __int_as_float(0x7f800000);
-                const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : inf;
-                float col_acc = 0.f;
+                // W = dS / S = -neg_w e / ((1 + e) dd).  No branches: columns past the end carry sq_b = +inf and entries
+                // whose d2 cancels are set to +inf too - both then contribute exact zeros - and the cancelling entries
+                // are redone from the rows themselves below.
                 uint32_t bad = 0;
-                // rows in batches of eight: all staging reads first, then eight independent chains, then the stores
-                // (a store between two reads would serialise the rows: the compiler cannot rule out aliasing)
-#pragma unroll 1
-                for (int r0 = 0; r0 < rows_here; r0 += 8) {
-                    float d2v[8], wv[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int r = r0 + i;
-                        const float x = stg[r * 32 + (lane ^ r)];
-                        const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
-                        const float d2 = fmaf(-2.f, x, nn);
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 sb4 = *reinterpret_cast<const float4*>(strip + 4 * j4);
+                    const float sbv[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int j = 4 * j4 + i;
+                        const float nn = row_op + sbv[i];
+                        float d2 = fmaf(-2.f, v[j], nn);
                         const bool flag = d2 < 0.015625f * nn;
-                        bad |= (flag ? 1u : 0u) << r;
-                        d2v[i] = (flag || r >= rows_here) ? inf : fmaxf(d2, 0.f);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float dd = sqrt_approx(d2v[i]);
+                        bad |= (flag ? 1u : 0u) << j;
+                        d2 = flag ? inf : fmaxf(d2, 0.f);
+                        const float dd = sqrt_approx(d2);
                         const float e = ex2_approx(dd * -1.44269504f);
-                        const float q = rcp_approx((1.f + e) * dd);          // dd = inf: q = 0 and e = 0; dd = 0: masked below
-                        wv[i] = dd > 0.f ? (-nw * e) * q : 0.f;
+                        const float qq = rcp_approx((1.f + e) * dd);         // dd = inf: qq = 0 and e = 0; dd = 0: masked below
+                        const float w = dd > 0.f ? (-nw * e) * qq : 0.f;
                         lsum += log1p_unit(e);
-                        col_acc += wv[i];
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int r = r0 + i;
-                        if (r < rows_here) {
-                            stg[r * 32 + (lane ^ r)] = wv[i];                     // kept for the row sums below
-                            if (pad_ok) Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, wv[i]);
-                        }
+                        row_acc += w;
+                        v[j] = w;
                     }
                 }
-                bad &= rows_here >= 32 ? 0xffffffffu : ((1u << rows_here) - 1u);
+                if (wh != nullptr) put_row32(wh + nbase, wl + nbase, v, wlim);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = v[j];
+                __syncwarp();
                 if (__any_sync(0xffffffffu, bad != 0)) {
                     for (int r = 0; r < rows_here; ++r) {
-                        unsigned todo = __ballot_sync(0xffffffffu, (bad >> r) & 1u);
+                        unsigned todo = __shfl_sync(0xffffffffu, bad, r);
                         while (todo) {
                             const int cl = __ffs(todo) - 1;
                             todo &= todo - 1;
@@ -444,98 +491,77 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                                 e2 = fmaf(df, df, e2);
                             }
                             e2 = warp_sum(e2);
-                            if (lane == cl) {
+                            if (lane == r) {           // the row's owner patches the one entry (after its own vector stores)
                                 const float dd = sqrtf(e2);
                                 const float e = __expf(-dd);
                                 const float w = dd > 0.f ? -nw * e / ((1.f + e) * dd) : 0.f;
                                 lsum += log1pf(e);
-                                col_acc += w;
-                                stg[r * 32 + (lane ^ r)] = w;
-                                Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, w);
+                                row_acc += w;
+                                stg[r * 32 + (cl ^ r)] = w;
+                                Split<ES>::put(wh + nbase + cl, wl + nbase + cl, w);
                             }
                         }
                     }
+                    __syncwarp();
                 }
-                if (col_ok) p.colpart[(static_cast<long long>(b) * ((p.m_rows + 31) / 32) + (mq >> 5)) * p.n_cols + col] = col_acc;
-                __syncwarp();
-                if (lane < rows_here) {              // back to thread = row: this chunk's part of the row sum of W
-                    float rs = 0.f;
+                float cs = 0.f;                       // lane = column: this quarter's part of the column sum of W
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) rs += stg[lane * 32 + (j ^ lane)];
-                    row_acc += rs;
-                }
+                for (int r = 0; r < 32; ++r) cs += stg[r * 32 + (lane ^ r)];
+                if (lane < lim) p.colpart[(static_cast<long long>(b) * ((p.m_rows + 31) / 32) + (mq >> 5)) * p.n_cols + nbase + lane] = cs;
             } else {
-#pragma unroll 1
-                for (int r0 = 0; r0 < rows_here; r0 += 8) {
-                    float sv[8], wv[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) { const int r = r0 + i; sv[i] = stg[r * 32 + (lane ^ r)]; }
+                for (int j = 0; j < 32; ++j) {
+                    // softplus(sc) and sigmoid(sc) from one exponential: e = exp(-|sc|) in (0, 1]
+                    const float sc = v[j];
+                    const float e = ex2_approx(fabsf(sc) * -1.44269504f);
+                    const float l1p = log1p_unit(e);
+                    const float inv = rcp_approx(1.f + e);
+                    const bool ok = row_ok && j < lim;
+                    v[j] = ok ? nw * (sc >= 0.f ? inv : e * inv) : 0.f;
+                    lsum += ok ? fmaxf(sc, 0.f) + l1p : 0.f;
+                }
+                if (wh != nullptr) put_row32(wh + nbase, wl + nbase, v, wlim);
+            }
+        } else if (p.ep == EP_DIST) {
+            uint32_t bad = 0;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        // softplus(sc) and sigmoid(sc) from one exponential: e = exp(-|sc|) in (0, 1]
-                        const float sc = sv[i];
-                        const float e = ex2_approx(fabsf(sc) * -1.44269504f);
-                        const float l1p = log1p_unit(e);
-                        const float inv = rcp_approx(1.f + e);
-                        const bool ok = col_ok && r0 + i < rows_here;
-                        wv[i] = ok ? nw * (sc >= 0.f ? inv : e * inv) : 0.f;
-                        lsum += ok ? fmaxf(sc, 0.f) + l1p : 0.f;
-                    }
+            for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 sb4 = *reinterpret_cast<const float4*>(strip + 4 * j4);
+                const float sbv[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int r = r0 + i;
-                        if (pad_ok && r < rows_here) Split<ES>::put(wh + static_cast<long long>(r) * p.ldw, wl + static_cast<long long>(r) * p.ldw, wv[i]);
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const int j = 4 * j4 + i;
+                    const float nn = row_op + sbv[i];
+                    const float d2 = fmaf(-2.f, v[j], nn);
+                    bad |= (d2 < 0.015625f * nn ? 1u : 0u) << j;       // cancellation: listed for exact recomputation
+                    v[j] = -sqrt_approx(fmaxf(d2, 0.f));
                 }
             }
-            loss_acc = fmaf(nw, lsum, loss_acc);
-        } else if (GROUP == G_DENSE && p.ep == EP_DIST) {
-            const float sb = col_ok ? p.sq_b[static_cast<long long>(b) * p.n_cols + col] : 0.f;
-            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
-            uint32_t bad = 0;
-#pragma unroll 8
-            for (int r = 0; r < rows_here; ++r, o += p.out_ld) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                const float nn = __shfl_sync(0xffffffffu, row_op, r) + sb;
-                const float d2 = fmaf(-2.f, x, nn);
-                bad |= (d2 < 0.015625f * nn ? 1u : 0u) << r;       // cancellation: listed for exact recomputation
-                if (col_ok) *o = -sqrt_approx(fmaxf(d2, 0.f));
-            }
-            if (!col_ok) bad = 0;
-            if (__any_sync(0xffffffffu, bad != 0)) {
+            if (orow != nullptr) {
+                store_row32(orow + nbase, v, lim, vec_out && (lim & 3) == 0);
                 while (bad) {
-                    const int r = __ffs(bad) - 1;
+                    const int j = __ffs(bad) - 1;
                     bad &= bad - 1;
                     const unsigned long long at = atomicAdd(p.fix_count, 1ULL);
-                    if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow0 + r) * p.n_cols + col;
+                    if (at < p.fix_cap) p.fix_list[at] = static_cast<unsigned long long>(grow) * p.n_cols + nbase + j;
                 }
             }
-        } else if (GROUP == G_DENSE && p.ep == EP_RANK1) {
-            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
+        } else if (p.ep == EP_RANK1) {
 #pragma unroll
-            for (int r = 0; r < 32; ++r) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                const float rs = __shfl_sync(0xffffffffu, row_op, r);
-                if (col_ok && r < rows_here) o[static_cast<long long>(r) * p.out_ld] = fmaf(rs, y[r], -x);
-            }
+            for (int j = 0; j < 32; ++j) v[j] = fmaf(row_op, y[j], -v[j]);
+            if (orow != nullptr) store_row32(orow + nbase, v, lim, vec_out && (lim & 3) == 0);
         } else {                             // EP_STORE
-            float* o = p.out + (static_cast<long long>(b) * p.out_batch_rows + mq) * p.out_ld + col;
-#pragma unroll 8
-            for (int r = 0; r < rows_here; ++r, o += p.out_ld) {
-                const float x = stg[r * 32 + (lane ^ r)];
-                if (col_ok) *o = x;
-            }
+            if (orow != nullptr) store_row32(orow + nbase, v, lim, vec_out && (lim & 3) == 0);
         }
-        __syncwarp();                            // the square is rewritten by the next chunk
     }
     // this warp is done reading the accumulator: hand it back to the MMA thread
     umma::tc_fence_before();
     __syncwarp();
     if (lane == 0) umma::mbar_arrive_cluster(drained);
-    if (GROUP == G_DENSE && p.ep == EP_LOSS) {
+    if (p.ep == EP_LOSS) {
         const long long total_rows = static_cast<long long>(p.batch) * p.m_rows;
-        if (row_ok && p.loss_dist) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow0 + lane] = row_acc;
-        const float l = warp_sum(loss_acc);
+        if (row_ok && p.loss_dist) p.rowpart[(static_cast<long long>(n0 / p.bn) * 2 + half) * total_rows + grow] = row_acc;
+        const float l = warp_sum(nw * lsum);
         if (lane == 0) p.loss_part[slot * UM_EPI_WARPS + (warp - 2)] = l;
     }
 }

@@ -175,6 +175,52 @@ def test_prefetched_plan_gives_identical_steps():
             assert torch.equal(x.rel_grad[m], y.rel_grad[m])
 
 
+@pytest.mark.parametrize("micro,precision", [(2, "tensor"), (3, "tensor"), (2, "fp32")])
+def test_micro_batched_step_equals_whole_step(micro, precision):
+    """A step cut into micro-batches (runs of whole chunks, each staged, scored and reduced on its own) gives the whole
+    batch's loss, positives and gradients, and with SGD the same tables afterwards - prefetched plans included."""
+    from cuke_b200.pipeline import KgeStep
+    ne, d, nr, nn, chunk, n_chunks = 3000, 64, 11, 96, 64, 5
+    B = chunk * n_chunks
+    models = ["TransE", "DistMult"]
+    p = make_problem("TransE", seed=8, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+    rel0 = {m: (p["g"].standard_normal((nr, d)) / 8).astype(np.float32) for m in models}
+    batches = []
+    for it in range(2):
+        pb = make_problem("TransE", seed=70 + it, ne=ne, nr=nr, d=d, B=B, nn=nn, neg_mode="chunk_shared", chunk=chunk, zipf=True)
+        batches.append(tuple(to_dev(pb[k]) for k in ("h", "r", "t", "neg")))
+
+    def run(k, optimizer):
+        E = to_dev(p["E"].copy())
+        rel = {m: to_dev(rel0[m].copy()) for m in models}
+        st = KgeStep(models, E, rel, ne, "chunk_shared", 0, chunk, precision=precision, optimizer=optimizer, micro=k)
+        outs = [st.step(*batches[i], prefetch=batches[i + 1] if i + 1 < len(batches) else None) for i in range(len(batches))]
+        torch.cuda.synchronize()
+        return E, rel, outs
+
+    _, _, whole = run(1, None)
+    _, _, cut = run(micro, None)
+    for x, y in zip(whole, cut):
+        assert y.parts is not None and len(y.parts) == micro
+        U = int(x.n_ent_rows.item())
+        for m in models:
+            assert abs(float(x.loss[m]) - float(y.loss[m])) <= 1e-5 * abs(float(x.loss[m]))
+            assert rel_err(y.pos[m].cpu().numpy(), x.pos[m].cpu().numpy()) < 1e-6
+            assert rel_err(y.rel_grad[m].cpu().numpy(), x.rel_grad[m].cpu().numpy()) < 1e-5
+            ref = np.zeros((ne, d), dtype=np.float64)
+            ref[x.ent_ids[:U].cpu().numpy()] = x.ent_grad[m][:U].double().cpu().numpy()
+            got = np.zeros((ne, d), dtype=np.float64)
+            for o in y.parts:
+                u = int(o.n_ent_rows.item())
+                got[o.ent_ids[:u].cpu().numpy()] += o.ent_grad[m][:u].double().cpu().numpy()
+            assert rel_err(got, ref) < 1e-5
+    Ea, ra, _ = run(1, ("sgd", 0.05))
+    Eb, rb, _ = run(micro, ("sgd", 0.05))
+    assert rel_err((Eb - to_dev(p["E"])).cpu().numpy(), (Ea - to_dev(p["E"])).cpu().numpy()) < 1e-4      # the updates themselves
+    for m in models:
+        assert rel_err((rb[m] - to_dev(rel0[m])).cpu().numpy(), (ra[m] - to_dev(rel0[m])).cpu().numpy()) < 1e-4
+
+
 @pytest.mark.parametrize("model", ["TransE", "TransH", "TransR", "TransF", "RESCAL", "DistMult", "ComplEx"])
 def test_compile_and_run_drop_in(model):
     """The reference's user code path: build the expression, print_cuda, compile_and_run(code, *args) with the
