@@ -60,6 +60,8 @@ def parse():
     ap.add_argument("--micro", type=int, default=0,
                     help="micro-batches per step (0 = 1 on one GPU, 2 on several: the row exchanges of one micro-batch travel while "
                          "the other computes)")
+    ap.add_argument("--no-peer-staging", action="store_true",
+                    help="N GPUs: stage rows by all-to-all (NCCL) instead of reading the owners' shards in place over NVLink")
     ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor", "tensor_tf32"],
                     help="fp32: CUDA-core arithmetic; tensor: 3xTF32 tcgen05 contractions where available (same tolerance)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work budget per scorer for cpu_baseline")
@@ -514,7 +516,8 @@ def main():
     optimizer = None if args.no_optimizer else ("sgd", 1e-8)
     micro = args.micro if args.micro > 0 else (2 if world > 1 else 1)
     stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group,
-                      precision=args.precision, optimizer=optimizer, micro=micro)
+                      precision=args.precision, optimizer=optimizer, micro=micro,
+                      peer_staging=world > 1 and not args.no_peer_staging)
 
     nb = 4
     host = []
@@ -537,15 +540,19 @@ def main():
         dist.all_reduce(tns, op=dist.ReduceOp.MAX, group=group)
         return float(tns.item())
 
+    host_ms = []        # per timed region: host time to queue its steps (no synchronisation inside), per step
+
     def timed(fn, steps, warmup):
         for i in range(warmup):
             fn(i)
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         e0.record()
         for i in range(steps):
             fn(warmup + i)
         e1.record()
+        host_ms.append((time.perf_counter() - t0) * 1e3 / steps)
         sync_all()
         return max_over_ranks(e0.elapsed_time(e1)) / steps
 
@@ -564,10 +571,17 @@ def main():
         sampler.settle()
     if world > 1:
         dist.barrier(group=group)
-    launches0 = _lib.lib().kge_launch_count()
     # N GPUs: the last scorer's gradient return of step i may overlap the inspector of step i+1 (wait=False); the last
     # timed step waits for its own return, so the timed region covers all the work of its K steps
     w_main = max(args.warmup, 3)
+    # settle: allocator pools, clocks and the NCCL channels reach their steady state before the W warm-up steps begin
+    # (a fixed number of steps: every rank must make the same calls)
+    for i_settle in range(64):
+        stepper.step(*devb[i_settle % nb], prefetch=None if args.no_prefetch else devb[(i_settle + 1) % nb])
+        if i_settle % 8 == 7:
+            torch.cuda.synchronize()
+    sync_all()
+    launches0 = _lib.lib().kge_launch_count()
     # the next batch's inspection (N GPUs: and its id exchange) is queued on a side stream while a step computes
     nxt = (lambda i: devb[(i + 1) % nb]) if not args.no_prefetch else (lambda i: None)
     ms_step = timed(lambda i: stepper.step(*devb[i % nb], wait=(i == w_main + args.steps - 1), prefetch=nxt(i)), args.steps, w_main)
@@ -577,7 +591,8 @@ def main():
     regions = [ms_step] + [timed(lambda i: stepper.step(*devb[i % nb], wait=(i == args.steps - 1), prefetch=nxt(i)), args.steps, 0)
                            for _ in range(4)]
     clocks = sampler.stop() if rank == 0 else None
-    spread = {"regions": len(regions), "steps_each": args.steps, "ms_per_step_median": statistics.median(regions),
+    spread = {"regions": len(regions), "steps_each": args.steps, "ms_per_step_regions": regions,
+              "host_queue_ms_per_step": host_ms[:len(regions)], "ms_per_step_median": statistics.median(regions),
               "ms_per_step_min": min(regions), "ms_per_step_max": max(regions),
               "note": "`value` and `ms_per_step` are the first region (W warm-up steps, then exactly K timed steps)"}
 
@@ -612,7 +627,8 @@ def main():
         if world == 1:
             parity = parity_single_gpu(cfg, models, stepper, ent_local, rel, devb, dev)
         else:
-            parity = sharded_selfcheck(rank, world, group, precision=args.precision, n_chunks=2 * micro, micro=micro)
+            parity = sharded_selfcheck(rank, world, group, precision=args.precision, n_chunks=2 * micro, micro=micro,
+                                       peer_staging=not args.no_peer_staging)
             if rank == 0:
                 parity["against"] = "the same step on one GPU with the whole table (GPU against GPU)"
     except Exception as e:          # reported, never hidden
@@ -743,7 +759,11 @@ def main():
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), micro_batches=micro, arithmetic=(
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), micro_batches=micro,
+                                                                                         staging=("one gather kernel over the owners' shards (CUDA IPC mappings, NVLink peer loads)"
+                                                                                                  if world > 1 and not args.no_peer_staging else
+                                                                                                  "all-to-all of ids and rows (NCCL)" if world > 1 else "local gather"),
+                                                                                         arithmetic=(
                     "fp32 storage and accumulation; contractions on the tensor cores over a two-term bf16 split of each fp32 "
                     "operand (three MMAs per product, error-compensated; see the parity block for the measured error)"
                     if args.precision == "tensor" else

@@ -76,6 +76,11 @@ int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss,
                                    const long long* rel_uniq, const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes,
                                    cudaStream_t s);
 int launch_validate_ids(const void* ids, int id_bits, long long n, long long limit, void* out, cudaStream_t s);
+int launch_gather_rows_peers(const void* const* shards, int world, long long rows_per_rank, long long n_rows_total, int dtype, int dim,
+                             const long long* ids, long long n, const long long* n_dev, void* out, cudaStream_t s);
+int ipc_export(const void* ptr, void* handle, unsigned long long* offset);
+int ipc_open(const void* handle, unsigned long long offset, void** out);
+int ipc_close(void* ptr, unsigned long long offset);
 int launch_wait_timeout_selftest(int polls, cudaStream_t s);
 
 // ---- validation -------------------------------------------------------------------------------------------
@@ -299,6 +304,42 @@ int kge_gather_rows(const void* table, int32_t dtype, int32_t dim, const int64_t
     KGE_REQUIRE_PTR(table, "table"); KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
     return launch_gather_rows(table, dtype, dim, (const long long*)ids, n, (const long long*)n_dev, first_row, out,
                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_gather_rows_peers(const void* const* shards, int32_t world, int64_t rows_per_rank, int64_t n_rows, int32_t dtype, int32_t dim,
+                          const int64_t* ids, int64_t n, const int64_t* n_dev, void* out, kge_stream_t stream) {
+    const char* fn = "kge_gather_rows_peers";
+    if (n <= 0) return 0;
+    if (dim <= 0 || world <= 0 || rows_per_rank <= 0 || n_rows <= 0 || n_rows > rows_per_rank * world) {
+        set_error("%s: need dim, world, rows_per_rank > 0 and 0 < n_rows <= rows_per_rank * world", fn);
+        return KGE_E_SHAPE;
+    }
+    if (dtype != KGE_F32 && dtype != KGE_BF16) { set_error("%s: unknown dtype %d", fn, dtype); return KGE_E_UNSUPPORTED; }
+    if (shards == nullptr) { set_error("%s: shards is NULL", fn); return KGE_E_NULL; }
+    KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
+    return launch_gather_rows_peers(shards, world, rows_per_rank, n_rows, dtype, dim, (const long long*)ids, n, (const long long*)n_dev, out,
+                                    reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset) {
+    const char* fn = "kge_ipc_export";
+    if (!ptr || !handle64 || !offset) { set_error("%s: NULL argument", fn); return KGE_E_NULL; }
+    unsigned long long off = 0;
+    const int rc = ipc_export(ptr, handle64, &off);
+    *offset = off;
+    return rc;
+}
+
+int kge_ipc_open(const void* handle64, uint64_t offset, void** ptr_out) {
+    const char* fn = "kge_ipc_open";
+    if (!handle64 || !ptr_out) { set_error("%s: NULL argument", fn); return KGE_E_NULL; }
+    return ipc_open(handle64, offset, ptr_out);
+}
+
+int kge_ipc_close(void* ptr, uint64_t offset) {
+    const char* fn = "kge_ipc_close";
+    if (!ptr) { set_error("%s: NULL argument", fn); return KGE_E_NULL; }
+    return ipc_close(ptr, offset);
 }
 
 int kge_scatter_rows(const float* rows, int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev,

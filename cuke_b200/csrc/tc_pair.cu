@@ -315,6 +315,11 @@ __device__ __forceinline__ float log1p_unit(float e) {
 }
 
 constexpr int UM_THREADS = 320;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2..9: epilogue
+// The relation-grouped instantiation runs TWO sets of eight epilogue warps (warps 2..9 and 10..17), one per accumulator
+// buffer: its tiles are small (one k-pass of <= 256) and an epilogue is a chain of dependent latencies (tile record, per-row
+// operands, tensor-memory reads), so two tiles are drained at the same time.  Its epilogues need 90 registers, which
+// leaves room for 576 threads; the dense epilogues (168 registers) stay with one set.
+constexpr int UM_THREADS_GROUPED = 64 + 2 * 256;
 constexpr int UM_EPI_WARPS = 8;
 
 // Epilogue of one 128-row x bn_tile accumulator, run by the eight epilogue warps of a CTA.  A warp may only read the
@@ -573,15 +578,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 // shared-memory strip of the warp and is read as 128-bit broadcasts.  (The dense epilogues go through a transposing
 // staging square instead, because their per-column operands and row-contiguous destinations favour lane = column.)
 __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
-                                                 int bn_tile, int buf, uint32_t drained, float* epi_smem) {
+                                                 int bn_tile, int buf, int par, uint32_t drained, float* epi_smem) {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ((warp - 2) & 7) >> 2;
     const int row = q * 32 + lane;
     const int n_chunks32 = (bn_tile + 31) / 32;
     const int m = m0 + row;
     const bool row_ok = m < p.m_rows;
     const uint32_t t_row = tmem_d + (static_cast<uint32_t>(q * 32) << 16);
-    float* rs = epi_smem + 1024 + (warp - 2) * 256;            // this warp's copy of R[z] (n_cols <= 256), zero padded
+    float* rs = epi_smem + 1024 + (warp - 2) * 256;            // this warp's copy of R[z] (n_cols <= 256), zero padded; 16 warps
     if (p.ep == EP_NORM || p.ep == EP_GV) {
         for (int c = lane; c < 256; c += 32) {
             float rv = 0.f;
@@ -658,13 +663,15 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
     __syncwarp();
     if (lane == 0) umma::mbar_arrive_cluster(drained);
     if (p.ep == EP_NORM) {
-        float* ssq_part = epi_smem;                            // [2 accumulators][2 halves][128 rows]
-        ssq_part[(buf * 2 + half) * UM_BM + row] = ssq;
-        asm volatile("bar.sync 1, 256;" ::: "memory");         // the eight epilogue warps
+        // [2 accumulators = warp sets][2 tile parities][2 halves][128 rows]: a set's next tile writes the other parity, so
+        // its faster warps cannot overwrite sums that the slower ones have not read yet
+        float* ssq_part = epi_smem + (buf * 2 + par) * 2 * UM_BM;
+        ssq_part[half * UM_BM + row] = ssq;
+        asm volatile("bar.sync %0, 256;" :: "r"(1 + buf) : "memory");         // the eight epilogue warps of this buffer's set
         if (half == 0) {
             long long dst = p.row_dst[m];                      // >= 0: negative score index (+ kTailSide), <= -2: positive -2-i, -1: padding
             if (dst >= kTailSide) dst -= kTailSide;
-            const float sc = -sqrt_approx(ssq_part[(buf * 2) * UM_BM + row] + ssq_part[(buf * 2 + 1) * UM_BM + row]);
+            const float sc = -sqrt_approx(ssq_part[row] + ssq_part[UM_BM + row]);
             if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
         }
     }
@@ -674,7 +681,7 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
 // working at the same time share A rows in L2).  Two accumulators in tensor memory alternate, so the epilogue of tile i
 // (tcgen05.ld, scorer epilogue, global stores) overlaps the TMA/MMA main loop of tile i+1.
 template <int GROUP, int ES>
-__global__ void __launch_bounds__(UM_THREADS, 1)
+__global__ void __launch_bounds__(GROUP == G_GROUPED ? UM_THREADS_GROUPED : UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo, GemmTc p) {
     extern __shared__ uint8_t smem_raw[];
@@ -843,8 +850,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         }
     } else {
         // ---- epilogue ---------------------------------------------------------------------------------------------
+        // grouped instantiation: the set of this warp (warps 2..9: 0, 10..17: 1) drains the tiles of its own buffer
+        const int set = (warp - 2) >> 3;
         int lt = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+            if (GROUP == G_GROUPED && (lt & 1) != set) continue;
             const int tq = tile / tiles_n;
             int n0 = (tile - tq * tiles_n) * p.bn;
             int b = tq / tiles_m;
@@ -860,12 +870,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             if (GROUP == G_GROUPED && p.ep == EP_NORM) {
                 // the eight epilogue warps meet at a named barrier inside this epilogue: they give up together or not at all
                 if (!ok && lane == 0) *epi_fail = 1u;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync %0, 256;" :: "r"(1 + buf) : "memory");
                 ok = *epi_fail == 0u;
             }
             if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
             umma::tc_fence_after();
-            if (GROUP == G_GROUPED) epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem);
+            if (GROUP == G_GROUPED) epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, (lt >> 1) & 1, umma::smem_u32(&acc_empty[buf]), epi_smem);
             else epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
@@ -1300,7 +1310,7 @@ static int run_gemm(const CUtensorMap& ah, const CUtensorMap& al, const CUtensor
         else umma_pair_kernel<4><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_pair_kernel");
     } else {
-        if (p.tile_tab) umma_gemm_kernel<G_GROUPED, 2><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
+        if (p.tile_tab) umma_gemm_kernel<G_GROUPED, 2><<<ctas, UM_THREADS_GROUPED, smem, s>>>(ah, al, bh, bl, p);
         else if (p.elem_bytes == 2) umma_gemm_kernel<G_DENSE, 2><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         else umma_gemm_kernel<G_DENSE, 4><<<ctas, UM_THREADS, smem, s>>>(ah, al, bh, bl, p);
         KGE_LAUNCH_CHECK("umma_gemm_kernel");

@@ -1,0 +1,75 @@
+"""A row-partitioned table that every GPU of the node reads in place (CUDA IPC mappings, NVLink / NVSwitch peer loads).
+
+One process per GPU.  Rank g holds rows [g * rows_per_rank, (g + 1) * rows_per_rank) in its own HBM; `PeerTable` exports
+that shard once, maps the shards of the other ranks and keeps the `world` base addresses in a small device array, so
+`gather(ids, ...)` is one kernel (kge_gather_rows_peers) that copies any rows of the table - local or remote - into a
+compact local buffer.  It replaces, for the staging half of a step, the exchange of ids, the gather at each owner and
+the all-to-all of rows.
+
+Ordering: a rank's `gather` must run after the owners' last updates of the rows have completed and before their next
+ones begin.  `KgeStep` queues a barrier among the ranks behind the updates of a step (`publish`), and an owner's next
+update consumes gradients that were computed from the gathered rows, so it cannot start early.
+
+The reference is single-GPU (apps/kge/data/data_init.py:6-15) and has no counterpart.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import DTYPES, check
+
+
+class PeerTable:
+    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        if not ent_local.is_cuda or not ent_local.is_contiguous():
+            raise ValueError("expected a contiguous CUDA shard")
+        self.ent_local, self.n_ent, self.rank, self.world, self.group = ent_local, int(n_ent), int(rank), int(world), group
+        self.rows_per_rank = (self.n_ent + world - 1) // world
+        self.dim = ent_local.shape[1]
+        self.dtype = DTYPES[{torch.float32: "f32", torch.bfloat16: "bf16"}[ent_local.dtype]]
+        L = _lib.lib()
+        handle = (C.c_ubyte * 64)()
+        off = C.c_uint64(0)
+        check(L.kge_ipc_export(ent_local.data_ptr(), handle, C.byref(off)))
+        mine = (bytes(handle), int(off.value), int(ent_local.shape[0]))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._opened = []
+        ptrs = []
+        for g, (h, o, rows) in enumerate(everyone):
+            want = max(0, min(self.n_ent, (g + 1) * self.rows_per_rank) - g * self.rows_per_rank)
+            if rows != want:
+                raise ValueError(f"rank {g} holds {rows} rows, the partition gives it {want}")
+            if g == rank:
+                ptrs.append(ent_local.data_ptr())
+                continue
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            p = C.c_void_p()
+            check(L.kge_ipc_open(buf, o, C.byref(p)))
+            self._opened.append((p.value, o))
+            ptrs.append(p.value)
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=ent_local.device)
+        # every shard is complete (and mapped everywhere) before anybody reads
+        torch.cuda.synchronize(ent_local.device)
+        dist.barrier(group=group)
+
+    def gather(self, ids: torch.Tensor, n: int, n_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[i] = row ids[i] of the whole table for i < min(n, *n_dev), on the current stream."""
+        if out is None:
+            out = torch.empty((max(n, 1), self.dim), dtype=self.ent_local.dtype, device=self.ent_local.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        check(_lib.lib().kge_gather_rows_peers(self.ptrs.data_ptr(), self.world, self.rows_per_rank, self.n_ent, self.dtype, self.dim,
+                                               ids.data_ptr(), int(n), None if n_dev is None else n_dev.data_ptr(), out.data_ptr(), stream))
+        return out
+
+    def close(self) -> None:
+        """Unmaps the peers' shards (collective in effect: nobody may still be reading this rank's shard)."""
+        L = _lib.lib()
+        for p, o in self._opened:
+            L.kge_ipc_close(p, o)
+        self._opened = []

@@ -57,6 +57,7 @@ class StepPlan:
     done: Optional[torch.cuda.Event] = None    # prefetched plans: recorded on the side stream after their last kernel
     first: int = 0                             # first triple of this micro-batch within the step's batch
     sub: Optional[Tuple[torch.Tensor, ...]] = None   # this micro-batch's own (h, r, t, neg): views of `batch`
+    inspected: Optional[torch.cuda.Event] = None     # recorded after the inspections, before the count exchange
 
 
 class RowExchange:
@@ -66,8 +67,11 @@ class RowExchange:
     cuke_b200.scoring (the CUDA kernels); tests drive the same protocol on CPU ranks over gloo with a
     numpy stand-in, which is how the multi-rank bookkeeping is checked without GPUs."""
 
-    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None, ops=scoring, plan_group=None):
+    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None, ops=scoring, plan_group=None,
+                 peers=None):
         self.ent_local, self.n_ent, self.rank, self.world, self.group, self.ops = ent_local, int(n_ent), rank, world, group, ops
+        self.peers = peers            # cuke_b200.peer.PeerTable: stage rows by reading the owners' shards in place
+        self.insp = None              # inspection of the batch whose rows are staged (peer staging reads its uniq)
         self.plan_group = plan_group if plan_group is not None else group       # communicator of the id-only collectives
         self.rows_per_rank = (self.n_ent + world - 1) // world
         self.dim = ent_local.shape[1]
@@ -101,14 +105,21 @@ class RowExchange:
                                input_split_sizes=self.need, group=self.plan_group)
         self.owner_insp = self.ops.inspect(self.req_ids[:S], self.n_ent) if S else None
 
-    def adopt(self, need, serve, req_ids, owner_insp):
-        self.need, self.serve, self.req_ids, self.owner_insp = need, serve, req_ids, owner_insp
+    def adopt(self, need, serve, req_ids, owner_insp, insp=None):
+        self.need, self.serve, self.req_ids, self.owner_insp, self.insp = need, serve, req_ids, owner_insp, insp
 
     # -- row half: depends on the tables -------------------------------------------------------------------------------
     def stage_rows(self, staged: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Owners gather the requested rows, all-to-all of rows.  Returns the compact buffer (row u = row uniq[u])."""
+        """Owners gather the requested rows, all-to-all of rows - or, with peer access, one gather kernel that reads the
+        owners' shards in place.  Returns the compact buffer (row u = row uniq[u])."""
         import torch.distributed as dist
         dev = self.ent_local.device
+        if self.peers is not None:
+            # the number of distinct rows is known on the device only: room for one row per slot, the kernel stops at n_unique
+            cap = max(self.insp.n, 1)
+            if staged is None or staged.shape[0] < cap:
+                staged = torch.empty((cap, self.dim), dtype=self.ent_local.dtype, device=dev)
+            return self.peers.gather(self.insp.uniq, cap, self.insp.n_unique, staged)
         U, S = sum(self.need), sum(self.serve)
         if S:
             send_rows = self.ops.gather_rows(self.ent_local, self.req_ids[:S], first_row=self.rank * self.rows_per_rank)
@@ -183,12 +194,16 @@ class KgeStep:
     rows at their owner at the end of the step (each scorer's gradient as its own update).
     relation_partitioned: every rank's batches hold only relations that no other rank sees (see cuke_b200.partition):
     relation-side gradients stay local (no all-reduce), which is what makes TransR / RESCAL usable on several GPUs.
-    micro: number of micro-batches a step is cut into (runs of whole chunks; see the module text)."""
+    micro: number of micro-batches a step is cut into (runs of whole chunks; see the module text).
+    peer_staging: several GPUs of one node: the rows of a batch are staged by one kernel that reads the owners' shards in
+    place over NVLink (cuke_b200.peer.PeerTable) instead of an all-to-all; gradients still travel by all-to-all.  After
+    changing the local shard outside of step() (an optimizer of the caller's), call publish() before the next step."""
 
     def __init__(self, models: List[str], ent_local: torch.Tensor, rel: Dict[str, torch.Tensor], n_ent: int,
                  neg_mode: str, n_neg_head: int = 0, chunk: int = 0, rank: int = 0, world: int = 1, group=None,
                  precision: str = "fp32", fused: bool = True, rel2: Optional[Dict[str, torch.Tensor]] = None,
-                 optimizer: Optional[tuple] = None, relation_partitioned: bool = False, micro: int = 1):
+                 optimizer: Optional[tuple] = None, relation_partitioned: bool = False, micro: int = 1,
+                 peer_staging: bool = False):
         self.micro = max(1, int(micro))
         self.models, self.ent_local, self.rel, self.rel2 = list(models), ent_local, rel, rel2 or {}
         self.fused = fused                    # use the fused forward+loss+backward call where the scorer supports it
@@ -223,7 +238,12 @@ class KgeStep:
         if world > 1:
             import torch.distributed as dist
             self.plan_group = dist.new_group(backend="nccl") if group is not None and dist.get_backend(group) == "nccl" else group
-        self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group) if world > 1 else None
+        self.peers = None
+        if world > 1 and peer_staging:
+            from .peer import PeerTable
+            self.peers = PeerTable(ent_local, n_ent, rank, world, group)
+        self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group, peers=self.peers) if world > 1 else None
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev) if self.peers is not None else None
         # gradient rows travel home on a side stream while the next scorer computes; plans of the next batch on another
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.plan_stream = torch.cuda.Stream(device=dev)
@@ -240,6 +260,8 @@ class KgeStep:
         rinsp = scoring.inspect(r32, self.n_rel[self.models[0]])
         plan = StepPlan((h, r, t, neg), ids, insp, r32, rinsp)
         if self.exchange is not None:
+            plan.inspected = torch.cuda.Event()
+            plan.inspected.record()
             plan.counts_host = self.exchange.plan_counts(insp)
             plan.ready = torch.cuda.Event()
             plan.ready.record()
@@ -299,7 +321,7 @@ class KgeStep:
         """N GPUs: completes the queued plans (host read of their split sizes, then the id exchanges on the side stream).
         step() calls it after launching its own work, when the device has long passed the few kernels the read waits for."""
         plans = self._planned
-        if plans is None or self.exchange is None or all(p.need is not None for p in plans):
+        if plans is None or self.exchange is None or self.peers is not None or all(p.need is not None for p in plans):
             return
         with torch.cuda.stream(self.plan_stream):
             for plan in plans:
@@ -313,7 +335,12 @@ class KgeStep:
         plans, self._planned = self._planned, None
         main = torch.cuda.current_stream()
         if plans is None or not all(a is b for a, b in zip(plans[0].batch, (h, r, t, neg))):
-            plans = self._make_plans(h, r, t, neg, ids, finish=True)
+            plans = self._make_plans(h, r, t, neg, ids, finish=self.peers is None)
+        elif self.peers is not None:
+            # rows are staged by peer loads from the inspection alone; the id exchange (split sizes on the host, ids to their
+            # owners, owner-side inspection) serves the gradient return only and is completed there (_finish_late)
+            for plan in plans:
+                main.wait_event(plan.inspected)
         else:
             self._planned = plans
             self.finish_prefetch()
@@ -322,6 +349,19 @@ class KgeStep:
         for plan in plans:
             self._hold(plan, main)
         return plans
+
+    def _finish_late(self, plan: StepPlan, main) -> None:
+        """Peer staging: the id half of the exchange, queued on the plan stream when the first gradient return of the
+        micro-batch is about to be queued.  The host read of the split sizes waits for an event that the device passed
+        during the previous step (prefetched plans) or a few kernels ago."""
+        if plan.need is not None:
+            return
+        with torch.cuda.stream(self.plan_stream):
+            self.plan_stream.wait_event(plan.inspected)
+            self._finish_plan(plan)
+            plan.done = torch.cuda.Event()
+            plan.done.record(self.plan_stream)
+        self._hold(plan, main)
 
     def _hold(self, plan: StepPlan, main) -> None:
         """The plan's tensors are read on streams other than the one they were allocated on."""
@@ -355,6 +395,19 @@ class KgeStep:
             self.comm_stream.wait_event(ready)
             dense.record_stream(self.comm_stream)
             dist.all_reduce(dense, group=self.group)
+
+    def publish(self) -> None:
+        """Peer staging: a barrier among the ranks on the side stream, behind the updates queued there so far.  A rank's next
+        staging gather is queued behind it, so it reads every owner's rows as updated."""
+        if self.peers is None:
+            return
+        import torch.distributed as dist
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            dist.all_reduce(self._token, group=self.group)
 
     def _update(self, table, key, rows, ids=None, n_dev=None, first_row: int = 0) -> None:
         """Applies one gradient on the stream where it became ready (the side stream when it travelled)."""
@@ -394,7 +447,7 @@ class KgeStep:
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
                 for plan in plans:
-                    self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp)
+                    self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp, plan.insp)
                     rows = self.exchange.stage_rows()
                     rows.record_stream(main)
                     ev = torch.cuda.Event()
@@ -420,6 +473,8 @@ class KgeStep:
             out.rel_grad, out.rel2_grad = last.rel_grad, last.rel2_grad
             out.rel2_ids, out.n_rel2_groups = last.rel2_ids, last.n_rel2_groups
             out.n_staged = outs[0].n_staged
+        if do_update and self.peers is not None:
+            self.publish()
         if self.exchange is not None and backward:
             out.done = torch.cuda.Event()
             out.done.record(self.comm_stream)
@@ -459,10 +514,13 @@ class KgeStep:
                 # the entity rows start their way home before the relation-side reduction is queued
                 ready = torch.cuda.Event()
                 ready.record(main)
+                self._finish_late(plan, main)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ready)
+                    if plan.done is not None:
+                        self.comm_stream.wait_event(plan.done)
                     grad_rows.record_stream(self.comm_stream)
-                    self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp)
+                    self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp, plan.insp)
                     out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
             if do_update:
                 self._update(self.ent_local, "ent", out.ent_grad[m], out.ent_ids, out.n_ent_rows, first_row)
@@ -489,7 +547,8 @@ class KgeStep:
 
 
 def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d: int = 64, chunk: int = 256, n_neg: int = 160,
-                      n_chunks: int = 2, n_ent: int = 5003, n_rel: int = 13, micro: int = 1) -> dict:
+                      n_chunks: int = 2, n_ent: int = 5003, n_rel: int = 13, micro: int = 1,
+                      peer_staging: bool = False) -> dict:
     """Row-partitioned step against the same step on one GPU, on a small seeded problem (GPU against GPU; no CPU code).
 
     Every rank scores its own batch against its shard of the table; rank 0 then recomputes all ranks' batches with the
@@ -516,7 +575,8 @@ def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d
 
     rpr = (n_ent + world - 1) // world
     local = torch.from_numpy(E[rank * rpr: min(n_ent, (rank + 1) * rpr)]).to(dev).contiguous()
-    step = KgeStep(models, local, rel, n_ent, "chunk_shared", 0, chunk, rank, world, group, precision=precision, micro=micro)
+    step = KgeStep(models, local, rel, n_ent, "chunk_shared", 0, chunk, rank, world, group, precision=precision, micro=micro,
+                   peer_staging=peer_staging)
     out = step.step(*batch(rank))
     parts = out.parts or [out]
     ks = [int(o.n_ent_rows.item()) for o in parts]
@@ -550,9 +610,11 @@ def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d
                     got[ids] += rows.double()
             err = max(err, float((got - dense[m]).abs().max() / dense[m].abs().max()))
             rerr = max(rerr, float((gathered[0][m][1].double() - drel[m]).abs().max() / drel[m].abs().max()))
-        res = {"ok": bool(loss_equal and owned and err < 1e-5 and rerr < 1e-5), "world": world, "precision": precision, "micro": micro,
+        res = {"ok": bool(loss_equal and owned and err < 1e-5 and rerr < 1e-5), "world": world, "precision": precision, "micro": micro, "peer_staging": peer_staging,
                "loss_bit_equal" if micro == 1 else "loss_equal_1e-6": loss_equal, "rows_owned_only": owned, "max_entity_err": err, "max_relation_err": rerr,
                "case": f"TransE+DistMult, {B} triples/rank, {n_neg} shared negatives per {chunk}-chunk, dim {d}, {n_ent} rows"}
     if world > 1:
         dist.barrier(group=group)
+    if step.peers is not None:
+        step.peers.close()
     return res

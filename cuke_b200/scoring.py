@@ -16,8 +16,16 @@ from ._lib import (DTYPES, MATRIX_MODELS, MODELS, NEG_MODES, PRECISIONS, VECTOR_
                    check)
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream(device=None) -> int:
+    """Handle of the current CUDA stream of `device` (default: the current device).  The raw query is an order of
+    magnitude cheaper than building a torch.cuda.Stream object, and a step makes dozens of these calls."""
+    if _raw_stream is not None:
+        idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+        return _raw_stream(idx)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -52,7 +60,7 @@ _ws_cache = {}
 def workspace(nbytes: int, device, tag: str = "") -> torch.Tensor:
     """A reusable scratch buffer per (device, current stream, tag); grown on demand, never shrunk.  Keyed by stream
     so that calls issued on different streams never share scratch."""
-    key = (str(device), torch.cuda.current_stream(device).cuda_stream, tag)
+    key = (device.index if isinstance(device, torch.device) else str(device), _stream(device if isinstance(device, torch.device) else None), tag)
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)

@@ -293,6 +293,25 @@ KGE_API int kge_logistic_loss(const float* pos, int64_t n_pos, const float* neg,
 KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64_t n_max, int64_t rows_per_rank,
                      int32_t world, int64_t* counts, kge_stream_t stream);
 
+/* The row-partitioned table read in place by every GPU of a node (one process per GPU, NVLink / NVSwitch peer access).
+ * kge_ipc_export: handle64 (64 bytes) identifies the device allocation that holds ptr, *offset is ptr's distance from
+ *   its start; both travel to the other processes by any host channel.  The memory must come from cudaMalloc (the
+ *   default of torch's caching allocator), not from a memory pool or a virtual-memory mapping.
+ * kge_ipc_open: maps a peer's allocation into this process (peer access is enabled on first use) and returns the
+ *   address that corresponds to the exported ptr.  kge_ipc_close unmaps it (same offset).
+ * kge_gather_rows_peers: out[i][:] = row ids[i] of the partitioned table for i < min(n, *n_dev), where shards is a DEVICE
+ *   array of `world` pointers, shards[g] = first row of rank g's shard (rows [g * rows_per_rank, ...)), this rank's own
+ *   shard included; n_rows is the table's total row count.  One kernel: local rows come from HBM, remote rows through
+ *   NVLink with plain 16-byte loads, and every row lands in this GPU's memory.  An id outside [0, n_rows) sets
+ *   KGE_ERR_ID_RANGE and yields a zero row; nothing outside the table is read.  Ordering against the owners' updates of
+ *   their rows is the caller's (a barrier among the ranks after the updates of a step, before the gathers of the next).
+ * No counterpart in the reference (single GPU, apps/kge/data/data_init.py:6-15). */
+KGE_API int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset);
+KGE_API int kge_ipc_open(const void* handle64, uint64_t offset, void** ptr_out);
+KGE_API int kge_ipc_close(void* ptr, uint64_t offset);
+KGE_API int kge_gather_rows_peers(const void* const* shards, int32_t world, int64_t rows_per_rank, int64_t n_rows, int32_t dtype,
+                          int32_t dim, const int64_t* ids, int64_t n, const int64_t* n_dev, void* out, kge_stream_t stream);
+
 /* ---- general expressions ----------------------------------------------------------------------------------------
  * Evaluates, for every batch element i, a small register program over per-element VECTOR registers (dim floats) and
  * SCALAR registers: the target of the Python front-end for expressions of the reference's batched operators that are

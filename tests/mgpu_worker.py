@@ -2,7 +2,7 @@
 Every rank scores its own batch against a row-partitioned table; rank 0 then recomputes all ranks' batches on one
 GPU with the whole table and compares (cuke_b200.pipeline.sharded_selfcheck): losses per rank bit-equal, the summed
 entity / relation gradients to 1e-5.  Run on the tensor-core path (fused step; CTA-pair and one-CTA tile shapes) and
-once on the fp32 CUDA-core path, then with the sharded step cut into micro-batches."""
+once on the fp32 CUDA-core path, then with the sharded step cut into micro-batches and with the rows staged by peer loads instead of an all-to-all."""
 import os
 import sys
 
@@ -24,7 +24,9 @@ def main():
              dict(precision="tensor", d=40, chunk=64, n_neg=96, n_chunks=4),         # one-CTA tiles
              dict(precision="fp32", d=64, chunk=64, n_neg=96, n_chunks=4),
              dict(precision="tensor", d=64, chunk=256, n_neg=160, n_chunks=4, micro=2),   # two micro-batches per step
-             dict(precision="tensor", d=40, chunk=64, n_neg=96, n_chunks=5, micro=3)]     # uneven micro-batches
+             dict(precision="tensor", d=40, chunk=64, n_neg=96, n_chunks=5, micro=3),     # uneven micro-batches
+             dict(precision="tensor", d=64, chunk=256, n_neg=160, n_chunks=2, peer_staging=True),   # rows read in place over NVLink
+             dict(precision="fp32", d=36, chunk=64, n_neg=96, n_chunks=4, micro=2, peer_staging=True)]
     ok = True
     for c in cases:
         res = sharded_selfcheck(rank, world, dist.group.WORLD, **c)
