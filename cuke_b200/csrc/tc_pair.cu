@@ -339,9 +339,25 @@ constexpr int UM_EPI_WARPS = 8;
 // rows, scatter; epilogue_grouped).  Two instantiations keep the register allocation of each set independent of the other.
 enum { G_DENSE = 0, G_GROUPED = 1 };
 
-// 32 fp32 values of one row -> out[0..lim): 16-byte stores when the row is 16-byte aligned and lim a multiple of 4
+// One 32-byte global store (sm_100: 256-bit vector accesses).  A thread-per-row epilogue issues one store request per
+// lane - the lanes of a warp write 32 different rows - and the L1 / L2 path takes requests, not bytes: a request that
+// fills a whole 32-byte sector moves twice the data of a 16-byte one at the same cost.  p must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4, uint32_t a5,
+                                             uint32_t a6, uint32_t a7) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :: "l"(p), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7) : "memory");
+}
+// 32 fp32 values of one row -> out[0..lim): vector stores when the row is 16-byte aligned and lim a multiple of 4
+// (32-byte stores where the address allows, else 16-byte ones)
 __device__ __forceinline__ void store_row32(float* out, const float (&v)[32], int lim, bool vec) {
-    if (vec) {
+    if (vec && (reinterpret_cast<uintptr_t>(out) & 31) == 0 && (lim & 7) == 0) {
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8)
+            if (8 * j8 < lim)
+                st_global_v8(out + 8 * j8, __float_as_uint(v[8 * j8]), __float_as_uint(v[8 * j8 + 1]), __float_as_uint(v[8 * j8 + 2]),
+                             __float_as_uint(v[8 * j8 + 3]), __float_as_uint(v[8 * j8 + 4]), __float_as_uint(v[8 * j8 + 5]),
+                             __float_as_uint(v[8 * j8 + 6]), __float_as_uint(v[8 * j8 + 7]));
+    } else if (vec) {
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4)
             if (4 * j4 < lim) *reinterpret_cast<float4*>(out + 4 * j4) = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
@@ -357,17 +373,22 @@ __device__ __forceinline__ void put_row32(float* hi, float* lo, const float (&v)
     for (int j4 = 0; j4 < 8; ++j4)
         if (4 * j4 < wlim) put_quad(hi + 4 * j4, lo + 4 * j4, nullptr, make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]));
 }
+// (wlim is a multiple of 16 and the row pieces start on 32-byte boundaries: 16 elements = one 32-byte store per part)
 __device__ __forceinline__ void put_row32(__nv_bfloat16* hi, __nv_bfloat16* lo, const float (&v)[32], int wlim) {
 #pragma unroll
-    for (int j8 = 0; j8 < 4; ++j8) {
-        if (8 * j8 < wlim) {
-            float4 h0, h1, t;
-            const uint2 a0 = bf16x4(make_float4(v[8 * j8], v[8 * j8 + 1], v[8 * j8 + 2], v[8 * j8 + 3]), h0);
-            const uint2 a1 = bf16x4(make_float4(v[8 * j8 + 4], v[8 * j8 + 5], v[8 * j8 + 6], v[8 * j8 + 7]), h1);
-            *reinterpret_cast<uint4*>(hi + 8 * j8) = make_uint4(a0.x, a0.y, a1.x, a1.y);
-            const uint2 l0 = bf16x4(make_float4(v[8 * j8] - h0.x, v[8 * j8 + 1] - h0.y, v[8 * j8 + 2] - h0.z, v[8 * j8 + 3] - h0.w), t);
-            const uint2 l1 = bf16x4(make_float4(v[8 * j8 + 4] - h1.x, v[8 * j8 + 5] - h1.y, v[8 * j8 + 6] - h1.z, v[8 * j8 + 7] - h1.w), t);
-            *reinterpret_cast<uint4*>(lo + 8 * j8) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+    for (int j16 = 0; j16 < 2; ++j16) {
+        if (16 * j16 < wlim) {
+            uint32_t hw[8], lw[8];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int j = 16 * j16 + 4 * q4;
+                float4 h, t;
+                const uint2 a = bf16x4(make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), h);
+                const uint2 l = bf16x4(make_float4(v[j] - h.x, v[j + 1] - h.y, v[j + 2] - h.z, v[j + 3] - h.w), t);
+                hw[2 * q4] = a.x; hw[2 * q4 + 1] = a.y; lw[2 * q4] = l.x; lw[2 * q4 + 1] = l.y;
+            }
+            st_global_v8(hi + 16 * j16, hw[0], hw[1], hw[2], hw[3], hw[4], hw[5], hw[6], hw[7]);
+            st_global_v8(lo + 16 * j16, lw[0], lw[1], lw[2], lw[3], lw[4], lw[5], lw[6], lw[7]);
         }
     }
 }
@@ -392,9 +413,14 @@ __device__ __forceinline__ void get_row32(const __nv_bfloat16* hi, const __nv_bf
     }
 }
 
+// `acc_full` / `aph`: barrier and phase that announce the finished accumulator.  The epilogue waits on it itself, after it
+// has requested everything that does not depend on the accumulator (per-row operands, the first chunk's per-column
+// operands): the accumulator buffer is then held only for the tensor-memory reads and the arithmetic, not for the
+// latency of those loads.  Returns false if the wait ran out (nothing was read or written for this tile).
 template <int GROUP, int ES>
-__device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
-                                              int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot) {
+__device__ __forceinline__ bool epilogue_tile(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
+                                              int bn_tile, int buf, uint32_t drained, float* epi_smem, long long slot,
+                                              uint64_t* acc_full, uint32_t aph) {
     using S = typename Split<ES>::T;
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -423,10 +449,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
     if (p.ep == EP_RANK1 && row_ok) { yh = static_cast<const S*>(p.y_hi) + grow * p.y_ld; yl = static_cast<const S*>(p.y_lo) + grow * p.y_ld; }
     const float nw = p.neg_w;
     float lsum = 0.f, row_acc = 0.f;             // EP_LOSS: this thread's loss terms (unscaled); this row's sum of W
+    // distance forms: this lane's per-column operand of chunk c (+inf past the last column), requested one chunk ahead
+    auto col_operand = [&](int c) -> float {
+        const int nb = n0 + c * 32;
+        const int lm = min(32, min(bn_tile - c * 32, p.n_cols - nb));
+        return (c < n_chunks32 && lane < lm) ? p.sq_b[static_cast<long long>(b) * p.n_cols + nb + lane] : inf;
+    };
+    float sb_cur = dist_form ? col_operand(half) : 0.f;
+    bool acc_ready = false;
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
         const int nbase = n0 + c * 32;
         const int lim = min(32, min(bn_tile - c * 32, p.n_cols - nbase));                 // valid columns of this chunk
+        const float sb_next = dist_form ? col_operand(c + 2) : 0.f;
         float y[32];
         if (p.ep == EP_RANK1) {                  // the y row comes from memory: requested before the accumulator is read
             if (yh != nullptr && lim > 0) get_row32(yh + nbase, yl + nbase, y);
@@ -435,12 +470,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
                 for (int j = 0; j < 32; ++j) y[j] = 0.f;
             }
         }
+        if (!acc_ready) {
+            if (!umma::mbar_wait(acc_full, aph)) return false;          // warp-uniform
+            umma::tc_fence_after();
+            acc_ready = true;
+        }
         float v[32];
         umma::tmem_ld32(t_row + c * 32, v);         // warp-collective
+        const float sb_mine = sb_cur;
+        sb_cur = sb_next;
         if (rows_here <= 0 || lim <= 0) continue;    // warp-uniform
         if (dist_form) {
             __syncwarp();                            // the previous chunk's reads of the strip are done
-            strip[lane] = lane < lim ? p.sq_b[static_cast<long long>(b) * p.n_cols + nbase + lane] : inf;
+            strip[lane] = sb_mine;
             __syncwarp();
         }
         if (p.ep == EP_LOSS) {
@@ -559,6 +601,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
             if (orow != nullptr) store_row32(orow + nbase, v, lim, vec_out && (lim & 3) == 0);
         }
     }
+    if (!acc_ready && !umma::mbar_wait(acc_full, aph)) return false;      // a warp without chunks still takes part in the hand-over
     // this warp is done reading the accumulator: hand it back to the MMA thread
     umma::tc_fence_before();
     __syncwarp();
@@ -569,6 +612,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
         const float l = warp_sum(nw * lsum);
         if (lane == 0) p.loss_part[slot * UM_EPI_WARPS + (warp - 2)] = l;
     }
+    return true;
 }
 
 // Epilogues of the relation-grouped products (norm, dL/dv rows, scatter, plain store), in the layout tcgen05.ld delivers:
@@ -577,8 +621,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmTc& p, uint32_t tmem_d, 
 // 64-byte (bf16) piece of its destination row, written with 16-byte stores; the per-COLUMN vector R[z] sits in a
 // shared-memory strip of the warp and is read as 128-bit broadcasts.  (The dense epilogues go through a transposing
 // staging square instead, because their per-column operands and row-contiguous destinations favour lane = column.)
-__device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
-                                                 int bn_tile, int buf, int par, uint32_t drained, float* epi_smem) {
+__device__ __forceinline__ bool epilogue_grouped(const GemmTc& p, uint32_t tmem_d, int warp, int lane, int m0, int n0, int b,
+                                                 int bn_tile, int buf, int par, uint32_t drained, float* epi_smem,
+                                                 uint64_t* acc_full, uint32_t aph, volatile uint32_t* epi_fail) {
     const int q = warp & 3;
     const int half = ((warp - 2) & 7) >> 2;
     const int row = q * 32 + lane;
@@ -615,6 +660,16 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
         }
     }
     float ssq = 0.f;
+    // The accumulator is waited for only now, after the per-tile operands above have been requested (see epilogue_tile).
+    bool ok = umma::mbar_wait(acc_full, aph);                                                   // warp-uniform result
+    if (p.ep == EP_NORM) {
+        // the eight epilogue warps of a set meet at a named barrier inside this epilogue: they give up together or not at all
+        if (!ok && lane == 0) *epi_fail = 1u;
+        asm volatile("bar.sync %0, 256;" :: "r"(1 + buf) : "memory");
+        ok = *epi_fail == 0u;
+    }
+    if (!ok) return false;
+    umma::tc_fence_after();
 #pragma unroll 1
     for (int c = half; c < n_chunks32; c += 2) {
         float v[32];
@@ -651,10 +706,8 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
         } else {                                               // EP_SCATTER (signed) and EP_STORE
             if (orow != nullptr) {
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4)
-                    if (4 * j4 < lim)
-                        *reinterpret_cast<float4*>(orow + nbase + 4 * j4) =
-                            make_float4(sign * v[4 * j4 + 0], sign * v[4 * j4 + 1], sign * v[4 * j4 + 2], sign * v[4 * j4 + 3]);
+                for (int j = 0; j < 32; ++j) v[j] *= sign;
+                store_row32(orow + nbase, v, lim, true);       // n_cols % 8 == 0 on this path: rows are 32-byte aligned
             }
         }
     }
@@ -675,6 +728,7 @@ __device__ __forceinline__ void epilogue_grouped(const GemmTc& p, uint32_t tmem_
             if (dst >= 0) p.neg_out[dst] = sc; else if (dst <= -2) p.pos_out[-2 - dst] = sc;
         }
     }
+    return true;
 }
 
 // Persistent: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; the n-tile index runs fastest so that CTAs
@@ -866,17 +920,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-            bool ok = umma::mbar_wait(&acc_full[buf], aph);                                           // warp-uniform result
-            if (GROUP == G_GROUPED && p.ep == EP_NORM) {
-                // the eight epilogue warps meet at a named barrier inside this epilogue: they give up together or not at all
-                if (!ok && lane == 0) *epi_fail = 1u;
-                asm volatile("bar.sync %0, 256;" :: "r"(1 + buf) : "memory");
-                ok = *epi_fail == 0u;
-            }
+            bool ok;                                   // false: the wait for the accumulator ran out (warp-uniform)
+            if (GROUP == G_GROUPED) ok = epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, (lt >> 1) & 1,
+                                                          umma::smem_u32(&acc_empty[buf]), epi_smem, &acc_full[buf], aph, epi_fail);
+            else ok = epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf,
+                                                 umma::smem_u32(&acc_empty[buf]), epi_smem, tile, &acc_full[buf], aph);
             if (!ok) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
-            umma::tc_fence_after();
-            if (GROUP == G_GROUPED) epilogue_grouped(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, (lt >> 1) & 1, umma::smem_u32(&acc_empty[buf]), epi_smem);
-            else epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, p.bn, buf, umma::smem_u32(&acc_empty[buf]), epi_smem, tile);
         }
     }
     umma::tc_fence_before();
@@ -1071,10 +1120,12 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             const int bnt = p.b_mn ? min(p.bn, (p.n_cols - n0 + unit - 1) / unit * unit) : p.bn;
             const int buf = lt & 1;
             const uint32_t aph = static_cast<uint32_t>(lt >> 1) & 1;
-            if (!umma::mbar_wait(&acc_full[buf], aph)) { if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT); break; }
-            umma::tc_fence_after();
-            epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
-                          umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank);
+            if (!epilogue_tile<G_DENSE, ES>(p, tmem_base + buf * acc_cols, warp, lane, m0, n0, b, bnt, buf,
+                                            umma::map_to_cta(umma::smem_u32(&acc_empty[buf]), 0), epi_smem, 2LL * tile + rank,
+                                            &acc_full[buf], aph)) {
+                if (lane == 0) atomicOr(p.err, KGE_ERR_WAIT_TIMEOUT);
+                break;
+            }
         }
     }
     umma::tc_fence_before();
