@@ -57,9 +57,9 @@ def parse():
                     help="profiling aid: run forward+backward of the scorers 3 times on a reduced case (--chunks chunks, "
                          "entity table scaled down to fit a few GB) and exit; meant to be run under ncu -k <kernel>")
     ap.add_argument("--chunks", type=int, default=32)
-    ap.add_argument("--micro", type=int, default=0,
-                    help="micro-batches per step (0 = 1 on one GPU, 2 on several: the row exchanges of one micro-batch travel while "
-                         "the other computes)")
+    ap.add_argument("--micro", type=int, default=1,
+                    help="micro-batches per step (runs of whole chunks; with k > 1 the row exchanges of one micro-batch travel while "
+                         "another computes - measured slower than 1 at c5, where half-size contractions lose more than the overlap gains)")
     ap.add_argument("--no-peer-staging", action="store_true",
                     help="N GPUs: stage rows by all-to-all (NCCL) instead of reading the owners' shards in place over NVLink")
     ap.add_argument("--precision", default="tensor", choices=["fp32", "tensor", "tensor_tf32"],
@@ -514,7 +514,7 @@ def main():
     # learning rate is set so that the few hundred steps of a benchmark run leave the table in its initial distribution;
     # the update's memory traffic and launches do not depend on its value)
     optimizer = None if args.no_optimizer else ("sgd", 1e-8)
-    micro = args.micro if args.micro > 0 else (2 if world > 1 else 1)
+    micro = max(1, args.micro)
     stepper = KgeStep(models, ent_local, rel, cfg.n_ent, cfg.neg_mode, cfg.n_neg_head, cfg.chunk, rank, world, group,
                       precision=args.precision, optimizer=optimizer, micro=micro,
                       peer_staging=world > 1 and not args.no_peer_staging)
@@ -760,7 +760,8 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), micro_batches=micro,
-                                                                                         staging=("one gather kernel over the owners' shards (CUDA IPC mappings, NVLink peer loads)"
+                                                                                         staging=("rows: one gather kernel over the owners' shards; gradients: one owner-side sum over the ranks' buffers "
+                                                                                                  "(CUDA IPC mappings, NVLink peer loads); NCCL only for ids, counts and barriers"
                                                                                                   if world > 1 and not args.no_peer_staging else
                                                                                                   "all-to-all of ids and rows (NCCL)" if world > 1 else "local gather"),
                                                                                          arithmetic=(

@@ -78,6 +78,8 @@ int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss,
 int launch_validate_ids(const void* ids, int id_bits, long long n, long long limit, void* out, cudaStream_t s);
 int launch_gather_rows_peers(const void* const* shards, int world, long long rows_per_rank, long long n_rows_total, int dtype, int dim,
                              const long long* ids, long long n, const long long* n_dev, void* out, cudaStream_t s);
+int launch_pull_reduce(const float* const* bases, const long long* src_off, const long long* src_start, int world, int dim,
+                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, cudaStream_t s);
 int ipc_export(const void* ptr, void* handle, unsigned long long* offset);
 int ipc_open(const void* handle, unsigned long long offset, void** out);
 int ipc_close(void* ptr, unsigned long long offset);
@@ -319,6 +321,17 @@ int kge_gather_rows_peers(const void* const* shards, int32_t world, int64_t rows
     KGE_REQUIRE_PTR(ids, "ids"); KGE_REQUIRE_PTR(out, "out");
     return launch_gather_rows_peers(shards, world, rows_per_rank, n_rows, dtype, dim, (const long long*)ids, n, (const long long*)n_dev, out,
                                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kge_pull_reduce(const float* const* bases, const int64_t* src_off, const int64_t* src_start, int32_t world, int32_t dim,
+                    const int32_t* perm, const int32_t* seg, const int64_t* n_unique, int64_t n_max, float* out, kge_stream_t stream) {
+    const char* fn = "kge_pull_reduce";
+    if (n_max <= 0) return 0;
+    if (dim <= 0 || world <= 0) { set_error("%s: dim and world must be positive", fn); return KGE_E_SHAPE; }
+    if (!bases || !src_off || !src_start || !perm || !seg || !n_unique) { set_error("%s: NULL argument", fn); return KGE_E_NULL; }
+    KGE_REQUIRE_ROWS(out, "out", dim);
+    return launch_pull_reduce(bases, (const long long*)src_off, (const long long*)src_start, world, dim, perm, seg,
+                              (const long long*)n_unique, n_max, out, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset) {

@@ -77,6 +77,57 @@ int launch_gather_rows_peers(const void* const* shards, int world, long long row
     return 0;
 }
 
+// Owner-side sum of the gradient rows that the ranks hold for this rank's rows, read in place from their buffers.
+// The ids requested by the ranks were concatenated in rank order (position pos of rank r: src_start[r] <= pos <
+// src_start[r + 1]) and inspected: distinct id u owns the sorted positions [seg[u], seg[u + 1]) of perm.  Rank r keeps its
+// gradient rows in the order of ITS sorted distinct ids, of which this owner's are the range starting at src_off[r]; so the
+// row for position pos lives at bases[r] + (src_off[r] + pos - src_start[r]) * dim.  One warp per distinct id; at most one
+// row per rank and id, added in rank order (perm is a stable sort): a fixed order, no atomics.
+__global__ void __launch_bounds__(256) pull_reduce_kernel(const float* const* bases, const long long* src_off, const long long* src_start,
+                                                          int world, int dim, const int* perm, const int* seg, const long long* n_unique,
+                                                          long long n_max, float* out) {
+    const int lane = threadIdx.x & 31;
+    const long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (u >= min(n_max, *n_unique)) return;
+    const int p0 = seg[u], p1 = seg[u + 1];
+    float* dst = out + u * dim;
+    const bool vec = (dim & 3) == 0;
+    for (int k0 = 0; k0 < dim; k0 += 128) {                 // 128 floats per pass: one float4 per lane
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int k = k0 + 4 * lane;
+        for (int p = p0; p < p1; ++p) {
+            const long long pos = perm[p];
+            int r = 0;
+            while (r + 1 < world && pos >= src_start[r + 1]) ++r;
+            const float* row = bases[r] + (src_off[r] + pos - src_start[r]) * dim;
+            if (vec) {
+                if (k < dim) { const float4 x = *reinterpret_cast<const float4*>(row + k); acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w; }
+            } else {
+                if (k < dim) acc.x += row[k];
+                if (k + 1 < dim) acc.y += row[k + 1];
+                if (k + 2 < dim) acc.z += row[k + 2];
+                if (k + 3 < dim) acc.w += row[k + 3];
+            }
+        }
+        if (vec) { if (k < dim) *reinterpret_cast<float4*>(dst + k) = acc; }
+        else {
+            if (k < dim) dst[k] = acc.x;
+            if (k + 1 < dim) dst[k + 1] = acc.y;
+            if (k + 2 < dim) dst[k + 2] = acc.z;
+            if (k + 3 < dim) dst[k + 3] = acc.w;
+        }
+    }
+}
+
+int launch_pull_reduce(const float* const* bases, const long long* src_off, const long long* src_start, int world, int dim,
+                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, cudaStream_t s) {
+    if (n_max <= 0) return 0;
+    const int wpb = 8;
+    pull_reduce_kernel<<<(unsigned)((n_max + wpb - 1) / wpb), wpb * 32, 0, s>>>(bases, src_off, src_start, world, dim, perm, seg, n_unique, n_max, out);
+    KGE_LAUNCH_CHECK("pull_reduce_kernel");
+    return 0;
+}
+
 // handle: 64 bytes (cudaIpcMemHandle_t) of the allocation that holds ptr; *offset: ptr's distance from its start.
 int ipc_export(const void* ptr, void* handle, unsigned long long* offset) {
     MemRangeFn range = mem_range_fn();

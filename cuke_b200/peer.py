@@ -23,40 +23,80 @@ from . import _lib
 from ._lib import DTYPES, check
 
 
-class PeerTable:
-    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None):
+# A device allocation can be opened once per process: tensors that share one allocation of the caching allocator share
+# the mapping.  handle bytes -> [mapped base address, users]
+_open_allocations = {}
+
+
+def _open(handle: bytes) -> int:
+    ent = _open_allocations.get(handle)
+    if ent is None:
+        buf = (C.c_ubyte * 64).from_buffer_copy(handle)
+        p = C.c_void_p()
+        check(_lib.lib().kge_ipc_open(buf, 0, C.byref(p)))
+        ent = _open_allocations[handle] = [p.value, 0]
+    ent[1] += 1
+    return ent[0]
+
+
+def _close(handle: bytes) -> None:
+    ent = _open_allocations.get(handle)
+    if ent is None:
+        return
+    ent[1] -= 1
+    if ent[1] <= 0:
+        _lib.lib().kge_ipc_close(ent[0], 0)
+        del _open_allocations[handle]
+
+
+class PeerMap:
+    """One tensor per rank, each mapped into every process: `ptrs` is a device array of the `world` base addresses (this
+    rank's own tensor included).  Collective: every rank of `group` constructs it at the same point of its program."""
+
+    def __init__(self, local: torch.Tensor, rank: int, world: int, group=None):
         import torch.distributed as dist
-        if not ent_local.is_cuda or not ent_local.is_contiguous():
-            raise ValueError("expected a contiguous CUDA shard")
-        self.ent_local, self.n_ent, self.rank, self.world, self.group = ent_local, int(n_ent), int(rank), int(world), group
-        self.rows_per_rank = (self.n_ent + world - 1) // world
-        self.dim = ent_local.shape[1]
-        self.dtype = DTYPES[{torch.float32: "f32", torch.bfloat16: "bf16"}[ent_local.dtype]]
+        if not local.is_cuda or not local.is_contiguous():
+            raise ValueError("expected a contiguous CUDA tensor")
+        self.local, self.rank, self.world, self.group = local, int(rank), int(world), group
         L = _lib.lib()
         handle = (C.c_ubyte * 64)()
         off = C.c_uint64(0)
-        check(L.kge_ipc_export(ent_local.data_ptr(), handle, C.byref(off)))
-        mine = (bytes(handle), int(off.value), int(ent_local.shape[0]))
+        check(L.kge_ipc_export(local.data_ptr(), handle, C.byref(off)))
+        mine = (bytes(handle), int(off.value), int(local.shape[0]))
         everyone = [None] * world
         dist.all_gather_object(everyone, mine, group=group)
+        self.rows = [rows for _, _, rows in everyone]
         self._opened = []
         ptrs = []
-        for g, (h, o, rows) in enumerate(everyone):
+        for g, (h, o, _) in enumerate(everyone):
+            if g == rank:
+                ptrs.append(local.data_ptr())
+                continue
+            self._opened.append(h)
+            ptrs.append(_open(h) + o)
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=local.device)
+        # every tensor is complete (and mapped everywhere) before anybody reads
+        torch.cuda.synchronize(local.device)
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Unmaps the peers' tensors (nobody may still be reading this rank's)."""
+        for h in self._opened:
+            _close(h)
+        self._opened = []
+
+
+class PeerTable(PeerMap):
+    def __init__(self, ent_local: torch.Tensor, n_ent: int, rank: int, world: int, group=None):
+        super().__init__(ent_local, rank, world, group)
+        self.ent_local, self.n_ent = ent_local, int(n_ent)
+        self.rows_per_rank = (self.n_ent + world - 1) // world
+        self.dim = ent_local.shape[1]
+        self.dtype = DTYPES[{torch.float32: "f32", torch.bfloat16: "bf16"}[ent_local.dtype]]
+        for g, rows in enumerate(self.rows):
             want = max(0, min(self.n_ent, (g + 1) * self.rows_per_rank) - g * self.rows_per_rank)
             if rows != want:
                 raise ValueError(f"rank {g} holds {rows} rows, the partition gives it {want}")
-            if g == rank:
-                ptrs.append(ent_local.data_ptr())
-                continue
-            buf = (C.c_ubyte * 64).from_buffer_copy(h)
-            p = C.c_void_p()
-            check(L.kge_ipc_open(buf, o, C.byref(p)))
-            self._opened.append((p.value, o))
-            ptrs.append(p.value)
-        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=ent_local.device)
-        # every shard is complete (and mapped everywhere) before anybody reads
-        torch.cuda.synchronize(ent_local.device)
-        dist.barrier(group=group)
 
     def gather(self, ids: torch.Tensor, n: int, n_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """out[i] = row ids[i] of the whole table for i < min(n, *n_dev), on the current stream."""
@@ -66,10 +106,3 @@ class PeerTable:
         check(_lib.lib().kge_gather_rows_peers(self.ptrs.data_ptr(), self.world, self.rows_per_rank, self.n_ent, self.dtype, self.dim,
                                                ids.data_ptr(), int(n), None if n_dev is None else n_dev.data_ptr(), out.data_ptr(), stream))
         return out
-
-    def close(self) -> None:
-        """Unmaps the peers' shards (collective in effect: nobody may still be reading this rank's shard)."""
-        L = _lib.lib()
-        for p, o in self._opened:
-            L.kge_ipc_close(p, o)
-        self._opened = []

@@ -58,6 +58,9 @@ class StepPlan:
     first: int = 0                             # first triple of this micro-batch within the step's batch
     sub: Optional[Tuple[torch.Tensor, ...]] = None   # this micro-batch's own (h, r, t, neg): views of `batch`
     inspected: Optional[torch.cuda.Event] = None     # recorded after the inspections, before the count exchange
+    wanted: Optional[torch.Tensor] = None      # N GPUs, device (world, 2) int64: per requesting rank, how many of my rows it needs
+                                               # and where they start in its own sorted distinct ids
+    src_start: Optional[torch.Tensor] = None   # device (world + 1,): positions of each rank's ids within req_ids
 
 
 class RowExchange:
@@ -72,6 +75,7 @@ class RowExchange:
         self.ent_local, self.n_ent, self.rank, self.world, self.group, self.ops = ent_local, int(n_ent), rank, world, group, ops
         self.peers = peers            # cuke_b200.peer.PeerTable: stage rows by reading the owners' shards in place
         self.insp = None              # inspection of the batch whose rows are staged (peer staging reads its uniq)
+        self.wanted = self.src_start = None
         self.plan_group = plan_group if plan_group is not None else group       # communicator of the id-only collectives
         self.rows_per_rank = (self.n_ent + world - 1) // world
         self.dim = ent_local.shape[1]
@@ -85,8 +89,12 @@ class RowExchange:
         current stream has passed this point."""
         import torch.distributed as dist
         counts = self.ops.owner_counts(insp, self.rows_per_rank, self.world)       # ids I need from each owner
-        wanted = torch.empty_like(counts)                                           # ids each rank needs from me
-        dist.all_to_all_single(wanted, counts, group=self.plan_group)
+        # each owner also learns where its range starts in my sorted distinct ids (it reads my gradient rows there)
+        mine = torch.stack((counts, torch.cumsum(counts, 0) - counts), dim=1).contiguous()
+        wanted2 = torch.empty_like(mine)                                            # per rank: ids it needs from me, its offset
+        dist.all_to_all_single(wanted2, mine, group=self.plan_group)
+        self.wanted = wanted2
+        wanted = wanted2[:, 0]
         both = torch.stack((counts, wanted))
         if both.is_cuda:
             host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
@@ -104,9 +112,28 @@ class RowExchange:
         dist.all_to_all_single(self.req_ids[:S], insp.uniq[:U], output_split_sizes=self.serve,
                                input_split_sizes=self.need, group=self.plan_group)
         self.owner_insp = self.ops.inspect(self.req_ids[:S], self.n_ent) if S else None
+        if self.wanted is not None:
+            self.src_start = torch.cat((torch.zeros(1, dtype=torch.int64, device=self.wanted.device), torch.cumsum(self.wanted[:, 0], 0)))
 
-    def adopt(self, need, serve, req_ids, owner_insp, insp=None):
+    def adopt(self, need, serve, req_ids, owner_insp, insp=None, wanted=None, src_start=None):
         self.need, self.serve, self.req_ids, self.owner_insp, self.insp = need, serve, req_ids, owner_insp, insp
+        self.wanted, self.src_start = wanted, src_start
+
+    def return_grads_pull(self, grad_map):
+        """The owner-side sum of return_grads with the ranks' gradient rows read in place (grad_map: cuke_b200.peer.PeerMap
+        of the buffers that hold every rank's rows, in the order of its own sorted distinct ids).  The caller has put a
+        barrier among the ranks between the writes of those buffers and this call."""
+        S = sum(self.serve)
+        dev = self.ent_local.device
+        out = torch.empty((max(S, 1), self.dim), dtype=torch.float32, device=dev)
+        if S == 0:
+            return self.req_ids[:0], torch.zeros(1, dtype=torch.int64, device=dev), out[:0]
+        oinsp = self.owner_insp
+        src_off = self.wanted[:, 1].contiguous()
+        scoring.check(scoring._lib.lib().kge_pull_reduce(grad_map.ptrs.data_ptr(), src_off.data_ptr(), self.src_start.data_ptr(), self.world,
+                                                         self.dim, oinsp.perm.data_ptr(), oinsp.seg.data_ptr(), oinsp.n_unique.data_ptr(), S,
+                                                         out.data_ptr(), scoring._stream()))
+        return oinsp.uniq, oinsp.n_unique, out
 
     # -- row half: depends on the tables -------------------------------------------------------------------------------
     def stage_rows(self, staged: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -244,6 +271,7 @@ class KgeStep:
             self.peers = PeerTable(ent_local, n_ent, rank, world, group)
         self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group, peers=self.peers) if world > 1 else None
         self._token = torch.zeros(1, dtype=torch.float32, device=dev) if self.peers is not None else None
+        self._grad_maps = {}
         # gradient rows travel home on a side stream while the next scorer computes; plans of the next batch on another
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.plan_stream = torch.cuda.Stream(device=dev)
@@ -263,6 +291,7 @@ class KgeStep:
             plan.inspected = torch.cuda.Event()
             plan.inspected.record()
             plan.counts_host = self.exchange.plan_counts(insp)
+            plan.wanted = self.exchange.wanted
             plan.ready = torch.cuda.Event()
             plan.ready.record()
             if finish:
@@ -275,9 +304,10 @@ class KgeStep:
         if self.exchange is None or plan.need is not None:
             return
         plan.ready.synchronize()
+        self.exchange.wanted = plan.wanted
         self.exchange.plan_ids(plan.insp, plan.counts_host)
         plan.need, plan.serve = self.exchange.need, self.exchange.serve
-        plan.req_ids, plan.owner_insp = self.exchange.req_ids, self.exchange.owner_insp
+        plan.req_ids, plan.owner_insp, plan.src_start = self.exchange.req_ids, self.exchange.owner_insp, self.exchange.src_start
 
     def _split(self, h, r, t, neg, ids=None):
         """The micro-batches of a batch: runs of whole rows of `neg` (chunks, or triples with per-triple negatives)."""
@@ -365,7 +395,7 @@ class KgeStep:
 
     def _hold(self, plan: StepPlan, main) -> None:
         """The plan's tensors are read on streams other than the one they were allocated on."""
-        held = [plan.ids, plan.r32, plan.req_ids]
+        held = [plan.ids, plan.r32, plan.req_ids, plan.wanted, plan.src_start]
         for ins in (plan.insp, plan.rinsp, plan.owner_insp):
             if ins is not None:
                 held += [ins.uniq, ins.inverse, ins.perm, ins.seg, ins.n_unique]
@@ -395,6 +425,16 @@ class KgeStep:
             self.comm_stream.wait_event(ready)
             dense.record_stream(self.comm_stream)
             dist.all_reduce(dense, group=self.group)
+
+    def close(self) -> None:
+        """Peer access: unmaps the other ranks' shards and gradient buffers.  Call it on every rank, after a barrier, once no
+        rank will step again."""
+        torch.cuda.synchronize()
+        for gm in self._grad_maps.values():
+            gm.close()
+        self._grad_maps = {}
+        if self.peers is not None:
+            self.peers.close()
 
     def publish(self) -> None:
         """Peer staging: a barrier among the ranks on the side stream, behind the updates queued there so far.  A rank's next
@@ -462,7 +502,7 @@ class KgeStep:
         for j, plan in enumerate(plans):
             if arrived[j] is not None:
                 main.wait_event(arrived[j])
-            self._run_part(plan, staged[j], outs[j], first_row, backward, do_update, j == len(plans) - 1, rel_acc, main)
+            self._run_part(plan, staged[j], outs[j], first_row, backward, do_update, j == len(plans) - 1, rel_acc, main, j)
         out = outs[0]
         if len(outs) > 1:
             out = StepOutput(parts=outs)
@@ -473,8 +513,8 @@ class KgeStep:
             out.rel_grad, out.rel2_grad = last.rel_grad, last.rel2_grad
             out.rel2_ids, out.n_rel2_groups = last.rel2_ids, last.n_rel2_groups
             out.n_staged = outs[0].n_staged
-        if do_update and self.peers is not None:
-            self.publish()
+        if backward and self.peers is not None:
+            self.publish()         # behind the updates; also: every owner has read this step's gradient buffers
         if self.exchange is not None and backward:
             out.done = torch.cuda.Event()
             out.done.record(self.comm_stream)
@@ -483,8 +523,23 @@ class KgeStep:
         self.finish_prefetch()
         return out
 
+    def _grad_map(self, model: str, part: int, rows: int):
+        """Peer access: the buffer that holds this rank's entity-gradient rows of (scorer, micro-batch), mapped into every
+        process.  Made on first use - a collective, reached by every rank at the same point of its first step."""
+        key = (model, part)
+        gm = self._grad_maps.get(key)
+        if gm is None or gm.local.shape[0] < rows:
+            from .peer import PeerMap
+            if gm is not None:
+                torch.cuda.synchronize()
+                gm.close()
+            buf = torch.empty((rows, self.dim), dtype=torch.float32, device=self.ent_local.device)
+            gm = PeerMap(buf, self.rank, self.world, self.group)
+            self._grad_maps[key] = gm
+        return gm
+
     def _run_part(self, plan: StepPlan, staged: torch.Tensor, out: StepOutput, first_row: int, backward: bool, do_update: bool,
-                  last: bool, rel_acc: Dict[tuple, torch.Tensor], main) -> None:
+                  last: bool, rel_acc: Dict[tuple, torch.Tensor], main, part: int = 0) -> None:
         """Scorers, reductions, gradient return and entity updates of one micro-batch; the relation-side gradients are
         accumulated in rel_acc and all-reduced / applied with the last micro-batch."""
         h, r, t, neg = plan.sub
@@ -507,9 +562,25 @@ class KgeStep:
                 if not backward:
                     continue
                 sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg, rinsp)
-            grad_rows = scoring.segment_reduce(sg.ent_slots, insp, zero_tail=False)     # aligned with insp.uniq
+            gmap = self._grad_map(m, part, insp.n) if self.peers is not None else None
+            grad_rows = scoring.segment_reduce(sg.ent_slots, insp, out=None if gmap is None else gmap.local,
+                                               zero_tail=False)                           # aligned with insp.uniq
             if self.exchange is None:
                 out.ent_ids, out.n_ent_rows, out.ent_grad[m] = insp.uniq, insp.n_unique, grad_rows
+            elif gmap is not None:
+                # peer access: every owner reads the rows it owns out of the ranks' buffers and sums them in one kernel
+                # (no all-to-all, no receive buffer); the barrier says that every rank's rows of this scorer are complete
+                import torch.distributed as dist
+                ready = torch.cuda.Event()
+                ready.record(main)
+                self._finish_late(plan, main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ready)
+                    if plan.done is not None:
+                        self.comm_stream.wait_event(plan.done)
+                    dist.all_reduce(self._token, group=self.group)
+                    self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp, plan.insp, plan.wanted, plan.src_start)
+                    out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads_pull(gmap)
             else:
                 # the entity rows start their way home before the relation-side reduction is queued
                 ready = torch.cuda.Event()
@@ -615,6 +686,5 @@ def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d
                "case": f"TransE+DistMult, {B} triples/rank, {n_neg} shared negatives per {chunk}-chunk, dim {d}, {n_ent} rows"}
     if world > 1:
         dist.barrier(group=group)
-    if step.peers is not None:
-        step.peers.close()
+    step.close()
     return res

@@ -306,6 +306,17 @@ KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64
  *   KGE_ERR_ID_RANGE and yields a zero row; nothing outside the table is read.  Ordering against the owners' updates of
  *   their rows is the caller's (a barrier among the ranks after the updates of a step, before the gathers of the next).
  * No counterpart in the reference (single GPU, apps/kge/data/data_init.py:6-15). */
+/* kge_pull_reduce: the owner-side sum of gradient rows, read in place from the ranks' buffers (the counterpart of
+ *   kge_gather_rows_peers for the way back).  The ids the ranks requested from this owner were concatenated in rank order
+ *   (rank r: positions [src_start[r], src_start[r+1])) and inspected (perm, seg, n_unique as from kge_inspect).  bases is a
+ *   DEVICE array of `world` pointers to the ranks' gradient-row buffers, rows in the order of each rank's own sorted
+ *   distinct ids, of which this owner's start at row src_off[r].  out[u][:] = sum over the ranks that touched distinct id
+ *   u, in rank order (fixed order, no atomics), for u < min(n_max, *n_unique).  src_off, src_start (world + 1) int64 device.
+ *   The caller orders it after every rank's rows are complete (a barrier among the ranks) and keeps the buffers
+ *   unchanged until every owner has read them. */
+KGE_API int kge_pull_reduce(const float* const* bases, const int64_t* src_off, const int64_t* src_start, int32_t world, int32_t dim,
+                    const int32_t* perm, const int32_t* seg, const int64_t* n_unique, int64_t n_max, float* out,
+                    kge_stream_t stream);
 KGE_API int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset);
 KGE_API int kge_ipc_open(const void* handle64, uint64_t offset, void** ptr_out);
 KGE_API int kge_ipc_close(void* ptr, uint64_t offset);
