@@ -51,12 +51,17 @@ __global__ void __launch_bounds__(256) gather_rows_peers_kernel(const void* cons
     const int owner = (int)(id / rows_per_rank);
     const V* src = static_cast<const V*>(shards[owner]) + (id - owner * rows_per_rank) * row_units;
     V* dst = out + i * row_units;
-    long long k = lane;
-    for (; k + 96 < row_units; k += 128) {
-        const V a = src[k], b = src[k + 32], c = src[k + 64], d = src[k + 96];
-        dst[k] = a; dst[k + 32] = b; dst[k + 64] = c; dst[k + 96] = d;
+    for (long long k = lane; k < row_units; k += 128) {
+        const bool pb = k + 32 < row_units, pc = k + 64 < row_units, pd = k + 96 < row_units;
+        V a = src[k], b{}, c{}, d{};
+        if (pb) b = src[k + 32];
+        if (pc) c = src[k + 64];
+        if (pd) d = src[k + 96];
+        dst[k] = a;
+        if (pb) dst[k + 32] = b;
+        if (pc) dst[k + 64] = c;
+        if (pd) dst[k + 96] = d;
     }
-    for (; k < row_units; k += 32) dst[k] = src[k];
 }
 
 int launch_gather_rows_peers(const void* const* shards, int world, long long rows_per_rank, long long n_rows_total, int dtype, int dim,
