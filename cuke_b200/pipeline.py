@@ -688,3 +688,64 @@ def sharded_selfcheck(rank: int, world: int, group, precision: str = "tensor", d
         dist.barrier(group=group)
     step.close()
     return res
+
+
+def sharded_traincheck(rank: int, world: int, group, precision: str = "tensor", d: int = 64, chunk: int = 128, n_neg: int = 96,
+                       n_chunks: int = 2, n_ent: int = 3001, n_rel: int = 11, steps: int = 4, lr: float = 0.02,
+                       peer_staging: bool = True, micro: int = 1) -> dict:
+    """Several training steps (sparse SGD inside the step) on a row-partitioned table against the same steps on one GPU over
+    the ranks' batches joined: after the last step every rank's shard must equal the single-GPU table's rows to 1e-5 of the
+    largest update, and so must the replicated relation tables.  A stale read of a peer's rows, an update that overtakes a
+    peer's gather or a gradient buffer overwritten before its owner has read it would all show up here.  Collective.
+    Returns {"ok", "max_entity_err", "max_relation_err", ...} on rank 0 and {"ok": None} elsewhere."""
+    import numpy as np
+    import torch.distributed as dist
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = np.random.Generator(np.random.PCG64(91))
+    E = (g.standard_normal((n_ent, d)) / np.sqrt(d)).astype(np.float32)
+    models = ["TransE", "DistMult"]
+    R = {m: (g.standard_normal((n_rel, d)) / np.sqrt(d)).astype(np.float32) for m in models}
+    w = np.arange(1, n_ent + 1, dtype=np.float64) ** -1.1
+    B = chunk * n_chunks
+
+    def batch(step, rk):
+        gi = np.random.Generator(np.random.PCG64(5000 + 97 * step + rk))
+        ids = lambda size: torch.from_numpy(gi.choice(n_ent, size=size, p=w / w.sum()).astype(np.int64)).to(dev)
+        return ids(B), torch.from_numpy(gi.integers(0, n_rel, B)).to(dev), ids(B), ids((n_chunks, n_neg))
+
+    rpr = (n_ent + world - 1) // world
+    lo, hi = rank * rpr, min(n_ent, (rank + 1) * rpr)
+    local = torch.from_numpy(E[lo:hi]).to(dev).contiguous()
+    rel = {m: torch.from_numpy(R[m]).to(dev) for m in models}
+    st = KgeStep(models, local, rel, n_ent, "chunk_shared", 0, chunk, rank, world, group, precision=precision,
+                 optimizer=("sgd", lr), peer_staging=peer_staging, micro=micro)
+    mine = [batch(s, rank) for s in range(steps)]
+    for s in range(steps):
+        st.step(*mine[s], prefetch=mine[s + 1] if s + 1 < steps else None)
+    torch.cuda.synchronize()
+    shards = [None] * world
+    got = (local.cpu(), {m: rel[m].cpu() for m in models})
+    if world > 1:
+        dist.all_gather_object(shards, got, group=group)
+    else:
+        shards = [got]
+    res = {"ok": None}
+    if rank == 0:
+        full_E = torch.from_numpy(E).to(dev)
+        full_rel = {m: torch.from_numpy(R[m]).to(dev) for m in models}
+        ref = KgeStep(models, full_E, full_rel, n_ent, "chunk_shared", 0, chunk, precision=precision, optimizer=("sgd", lr))
+        for s in range(steps):
+            parts = [batch(s, rk) for rk in range(world)]
+            ref.step(*(torch.cat([p[i] for p in parts]) for i in range(4)))
+        torch.cuda.synchronize()
+        moved = float((full_E.cpu() - torch.from_numpy(E)).abs().max())
+        err = max(float((shards[rk][0] - full_E[rk * rpr: min(n_ent, (rk + 1) * rpr)].cpu()).abs().max()) for rk in range(world)) / moved
+        rmoved = max(float((full_rel[m].cpu() - torch.from_numpy(R[m])).abs().max()) for m in models)
+        rerr = max(float((shards[rk][1][m] - full_rel[m].cpu()).abs().max()) for rk in range(world) for m in models) / rmoved
+        res = {"ok": bool(err < 1e-4 and rerr < 1e-4 and moved > 0), "world": world, "steps": steps, "peer_staging": peer_staging, "micro": micro,
+               "max_entity_err": err, "max_relation_err": rerr, "largest_entity_update": moved,
+               "case": f"TransE+DistMult, SGD lr {lr}, {steps} steps of {B} triples/rank, dim {d}, {n_ent} rows"}
+    if world > 1:
+        dist.barrier(group=group)
+    st.close()
+    return res

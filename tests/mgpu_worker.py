@@ -12,7 +12,7 @@ sys.path.insert(0, ROOT)
 import torch
 import torch.distributed as dist
 
-from cuke_b200.pipeline import sharded_selfcheck
+from cuke_b200.pipeline import sharded_selfcheck, sharded_traincheck
 
 
 def main():
@@ -32,6 +32,12 @@ def main():
         res = sharded_selfcheck(rank, world, dist.group.WORLD, **c)
         if rank == 0:
             print("selfcheck", c, res, flush=True)
+            ok = ok and res["ok"]
+    # several steps with the optimizer inside the step: the order of peer reads, updates and barriers across steps
+    for c in (dict(peer_staging=True), dict(peer_staging=False), dict(peer_staging=True, micro=2, n_chunks=4)):
+        res = sharded_traincheck(rank, world, dist.group.WORLD, **c)
+        if rank == 0:
+            print("traincheck", c, res, flush=True)
             ok = ok and res["ok"]
     if rank == 0:
         assert ok, "sharded step differs from the single-GPU step"
