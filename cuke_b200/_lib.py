@@ -77,7 +77,7 @@ SIGNATURES = {
     "kge_probe_fma": (C.c_int, [_vp, _i32, _i32, C.POINTER(C.c_double), _vp]),
     "kge_segment_reduce_workspace_bytes": (_sz, [_i64, _i32]),
     "kge_segment_reduce": (C.c_int, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _sz, _vp]),
-    "kge_pull_reduce": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "kge_pull_reduce": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _f32, _vp]),
     "kge_ipc_export": (C.c_int, [_vp, _vp, C.POINTER(C.c_uint64)]),
     "kge_ipc_open": (C.c_int, [_vp, C.c_uint64, C.POINTER(C.c_void_p)]),
     "kge_ipc_close": (C.c_int, [_vp, C.c_uint64]),

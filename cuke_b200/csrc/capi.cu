@@ -79,7 +79,8 @@ int launch_validate_ids(const void* ids, int id_bits, long long n, long long lim
 int launch_gather_rows_peers(const void* const* shards, int world, long long rows_per_rank, long long n_rows_total, int dtype, int dim,
                              const long long* ids, long long n, const long long* n_dev, void* out, cudaStream_t s);
 int launch_pull_reduce(const float* const* bases, const long long* src_off, const long long* src_start, int world, int dim,
-                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, cudaStream_t s);
+                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, float* sgd_table,
+                       const long long* ids, long long first_row, float lr, cudaStream_t s);
 int ipc_export(const void* ptr, void* handle, unsigned long long* offset);
 int ipc_open(const void* handle, unsigned long long offset, void** out);
 int ipc_close(void* ptr, unsigned long long offset);
@@ -324,14 +325,20 @@ int kge_gather_rows_peers(const void* const* shards, int32_t world, int64_t rows
 }
 
 int kge_pull_reduce(const float* const* bases, const int64_t* src_off, const int64_t* src_start, int32_t world, int32_t dim,
-                    const int32_t* perm, const int32_t* seg, const int64_t* n_unique, int64_t n_max, float* out, kge_stream_t stream) {
+                    const int32_t* perm, const int32_t* seg, const int64_t* n_unique, int64_t n_max, float* out, float* sgd_table,
+                    const int64_t* ids, int64_t first_row, float lr, kge_stream_t stream) {
     const char* fn = "kge_pull_reduce";
     if (n_max <= 0) return 0;
     if (dim <= 0 || world <= 0) { set_error("%s: dim and world must be positive", fn); return KGE_E_SHAPE; }
     if (!bases || !src_off || !src_start || !perm || !seg || !n_unique) { set_error("%s: NULL argument", fn); return KGE_E_NULL; }
     KGE_REQUIRE_ROWS(out, "out", dim);
+    if (sgd_table) {
+        KGE_REQUIRE_ROWS(sgd_table, "sgd_table", dim);
+        if (!ids) { set_error("%s: sgd_table without ids", fn); return KGE_E_NULL; }
+    }
     return launch_pull_reduce(bases, (const long long*)src_off, (const long long*)src_start, world, dim, perm, seg,
-                              (const long long*)n_unique, n_max, out, reinterpret_cast<cudaStream_t>(stream));
+                              (const long long*)n_unique, n_max, out, sgd_table, (const long long*)ids, first_row, lr,
+                              reinterpret_cast<cudaStream_t>(stream));
 }
 
 int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset) {

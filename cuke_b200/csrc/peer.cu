@@ -87,15 +87,18 @@ int launch_gather_rows_peers(const void* const* shards, int world, long long row
 // src_start[r + 1]) and inspected: distinct id u owns the sorted positions [seg[u], seg[u + 1]) of perm.  Rank r keeps its
 // gradient rows in the order of ITS sorted distinct ids, of which this owner's are the range starting at src_off[r]; so the
 // row for position pos lives at bases[r] + (src_off[r] + pos - src_start[r]) * dim.  One warp per distinct id; at most one
-// row per rank and id, added in rank order (perm is a stable sort): a fixed order, no atomics.
+// row per rank and id, added in rank order (perm is a stable sort): a fixed order, no atomics.  With sgd_table set the
+// plain SGD step of the owner follows in the same pass: sgd_table[ids[u] - first_row] -= lr * sum (fp32 table).
 __global__ void __launch_bounds__(256) pull_reduce_kernel(const float* const* bases, const long long* src_off, const long long* src_start,
                                                           int world, int dim, const int* perm, const int* seg, const long long* n_unique,
-                                                          long long n_max, float* out) {
+                                                          long long n_max, float* out, float* sgd_table, const long long* ids,
+                                                          long long first_row, float lr) {
     const int lane = threadIdx.x & 31;
     const long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (u >= min(n_max, *n_unique)) return;
     const int p0 = seg[u], p1 = seg[u + 1];
     float* dst = out + u * dim;
+    float* trow = sgd_table ? sgd_table + (ids[u] - first_row) * dim : nullptr;
     const bool vec = (dim & 3) == 0;
     for (int k0 = 0; k0 < dim; k0 += 128) {                 // 128 floats per pass: one float4 per lane
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -114,21 +117,30 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const float* const* ba
                 if (k + 3 < dim) acc.w += row[k + 3];
             }
         }
-        if (vec) { if (k < dim) *reinterpret_cast<float4*>(dst + k) = acc; }
-        else {
-            if (k < dim) dst[k] = acc.x;
-            if (k + 1 < dim) dst[k + 1] = acc.y;
-            if (k + 2 < dim) dst[k + 2] = acc.z;
-            if (k + 3 < dim) dst[k + 3] = acc.w;
+        if (vec) {
+            if (k < dim) {
+                *reinterpret_cast<float4*>(dst + k) = acc;
+                if (trow) {
+                    float4 w = *reinterpret_cast<float4*>(trow + k);
+                    w.x -= lr * acc.x; w.y -= lr * acc.y; w.z -= lr * acc.z; w.w -= lr * acc.w;
+                    *reinterpret_cast<float4*>(trow + k) = w;
+                }
+            }
+        } else {
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int e = 0; e < 4; ++e)
+                if (k + e < dim) { dst[k + e] = a4[e]; if (trow) trow[k + e] -= lr * a4[e]; }
         }
     }
 }
 
 int launch_pull_reduce(const float* const* bases, const long long* src_off, const long long* src_start, int world, int dim,
-                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, cudaStream_t s) {
+                       const int* perm, const int* seg, const long long* n_unique, long long n_max, float* out, float* sgd_table,
+                       const long long* ids, long long first_row, float lr, cudaStream_t s) {
     if (n_max <= 0) return 0;
     const int wpb = 8;
-    pull_reduce_kernel<<<(unsigned)((n_max + wpb - 1) / wpb), wpb * 32, 0, s>>>(bases, src_off, src_start, world, dim, perm, seg, n_unique, n_max, out);
+    pull_reduce_kernel<<<(unsigned)((n_max + wpb - 1) / wpb), wpb * 32, 0, s>>>(bases, src_off, src_start, world, dim, perm, seg, n_unique, n_max, out,
+                                                                                sgd_table, ids, first_row, lr);
     KGE_LAUNCH_CHECK("pull_reduce_kernel");
     return 0;
 }

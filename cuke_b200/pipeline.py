@@ -119,10 +119,11 @@ class RowExchange:
         self.need, self.serve, self.req_ids, self.owner_insp, self.insp = need, serve, req_ids, owner_insp, insp
         self.wanted, self.src_start = wanted, src_start
 
-    def return_grads_pull(self, grad_map):
+    def return_grads_pull(self, grad_map, sgd_lr: Optional[float] = None):
         """The owner-side sum of return_grads with the ranks' gradient rows read in place (grad_map: cuke_b200.peer.PeerMap
         of the buffers that hold every rank's rows, in the order of its own sorted distinct ids).  The caller has put a
-        barrier among the ranks between the writes of those buffers and this call."""
+        barrier among the ranks between the writes of those buffers and this call.  sgd_lr: apply the owner's plain SGD step
+        to the local shard (fp32) in the same kernel."""
         S = sum(self.serve)
         dev = self.ent_local.device
         out = torch.empty((max(S, 1), self.dim), dtype=torch.float32, device=dev)
@@ -132,7 +133,9 @@ class RowExchange:
         src_off = self.wanted[:, 1].contiguous()
         scoring.check(scoring._lib.lib().kge_pull_reduce(grad_map.ptrs.data_ptr(), src_off.data_ptr(), self.src_start.data_ptr(), self.world,
                                                          self.dim, oinsp.perm.data_ptr(), oinsp.seg.data_ptr(), oinsp.n_unique.data_ptr(), S,
-                                                         out.data_ptr(), scoring._stream()))
+                                                         out.data_ptr(), None if sgd_lr is None else self.ent_local.data_ptr(),
+                                                         oinsp.uniq.data_ptr(), self.rank * self.rows_per_rank,
+                                                         0.0 if sgd_lr is None else float(sgd_lr), scoring._stream()))
         return oinsp.uniq, oinsp.n_unique, out
 
     # -- row half: depends on the tables -------------------------------------------------------------------------------
@@ -272,6 +275,7 @@ class KgeStep:
         self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group, peers=self.peers) if world > 1 else None
         self._token = torch.zeros(1, dtype=torch.float32, device=dev) if self.peers is not None else None
         self._grad_maps = {}
+        self._fenced = False
         # gradient rows travel home on a side stream while the next scorer computes; plans of the next batch on another
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.plan_stream = torch.cuda.Stream(device=dev)
@@ -425,6 +429,7 @@ class KgeStep:
             self.comm_stream.wait_event(ready)
             dense.record_stream(self.comm_stream)
             dist.all_reduce(dense, group=self.group)
+        self._fenced = True
 
     def close(self) -> None:
         """Peer access: unmaps the other ranks' shards and gradient buffers.  Call it on every rank, after a barrier, once no
@@ -433,6 +438,7 @@ class KgeStep:
         for gm in self._grad_maps.values():
             gm.close()
         self._grad_maps = {}
+        self._fenced = False
         if self.peers is not None:
             self.peers.close()
 
@@ -513,8 +519,11 @@ class KgeStep:
             out.rel_grad, out.rel2_grad = last.rel_grad, last.rel2_grad
             out.rel2_ids, out.n_rel2_groups = last.rel2_ids, last.n_rel2_groups
             out.n_staged = outs[0].n_staged
-        if backward and self.peers is not None:
-            self.publish()         # behind the updates; also: every owner has read this step's gradient buffers
+        if backward and self.peers is not None and not self._fenced:
+            # behind the updates; also: every owner has read this step's gradient buffers.  (When the last thing queued on
+            # the side stream after the last shard access was the relation-gradient all-reduce, that collective already is
+            # this barrier: no rank enters it before its own reads and updates are done.)
+            self.publish()
         if self.exchange is not None and backward:
             out.done = torch.cuda.Event()
             out.done.record(self.comm_stream)
@@ -563,6 +572,8 @@ class KgeStep:
                     continue
                 sg = sc.backward(sh, r32, st, sneg, pos, negs, dpos, dneg, rinsp)
             gmap = self._grad_map(m, part, insp.n) if self.peers is not None else None
+            ent_updated = False
+            self._fenced = False          # this scorer's reads of peer buffers and shard updates follow
             grad_rows = scoring.segment_reduce(sg.ent_slots, insp, out=None if gmap is None else gmap.local,
                                                zero_tail=False)                           # aligned with insp.uniq
             if self.exchange is None:
@@ -580,7 +591,10 @@ class KgeStep:
                         self.comm_stream.wait_event(plan.done)
                     dist.all_reduce(self._token, group=self.group)
                     self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp, plan.insp, plan.wanted, plan.src_start)
-                    out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads_pull(gmap)
+                    fused_sgd = do_update and self.optimizer[0] == "sgd" and self.ent_local.dtype == torch.float32
+                    out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads_pull(
+                        gmap, self.optimizer[1] if fused_sgd else None)
+                    ent_updated = fused_sgd
             else:
                 # the entity rows start their way home before the relation-side reduction is queued
                 ready = torch.cuda.Event()
@@ -593,7 +607,7 @@ class KgeStep:
                     grad_rows.record_stream(self.comm_stream)
                     self.exchange.adopt(plan.need, plan.serve, plan.req_ids, plan.owner_insp, plan.insp)
                     out.ent_ids, out.n_ent_rows, out.ent_grad[m] = self.exchange.return_grads(grad_rows)
-            if do_update:
+            if do_update and not ent_updated:
                 self._update(self.ent_local, "ent", out.ent_grad[m], out.ent_ids, out.n_ent_rows, first_row)
             for slots, table, key, dest in ((sg.rel_slots, self.rel.get(m), ("rel", m), out.rel_grad),
                                             (sg.rel2_slots, self.rel2.get(m), ("rel2", m), out.rel2_grad)):

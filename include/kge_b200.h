@@ -312,11 +312,13 @@ KGE_API int kge_owner_counts(const int64_t* uniq, const int64_t* n_unique, int64
  *   DEVICE array of `world` pointers to the ranks' gradient-row buffers, rows in the order of each rank's own sorted
  *   distinct ids, of which this owner's start at row src_off[r].  out[u][:] = sum over the ranks that touched distinct id
  *   u, in rank order (fixed order, no atomics), for u < min(n_max, *n_unique).  src_off, src_start (world + 1) int64 device.
+ *   With sgd_table (fp32, this owner's shard) the owner's plain SGD step is applied in the same pass:
+ *   sgd_table[ids[u] - first_row][:] -= lr * out[u][:], ids = the sorted distinct ids of the inspection; NULL: no update.
  *   The caller orders it after every rank's rows are complete (a barrier among the ranks) and keeps the buffers
  *   unchanged until every owner has read them. */
 KGE_API int kge_pull_reduce(const float* const* bases, const int64_t* src_off, const int64_t* src_start, int32_t world, int32_t dim,
                     const int32_t* perm, const int32_t* seg, const int64_t* n_unique, int64_t n_max, float* out,
-                    kge_stream_t stream);
+                    float* sgd_table, const int64_t* ids, int64_t first_row, float lr, kge_stream_t stream);
 KGE_API int kge_ipc_export(const void* ptr, void* handle64, uint64_t* offset);
 KGE_API int kge_ipc_open(const void* handle64, uint64_t offset, void** ptr_out);
 KGE_API int kge_ipc_close(void* ptr, uint64_t offset);
