@@ -65,6 +65,12 @@ size_t transr_backward_workspace_bytes(const kge_problem* p);
 int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const float* pos, const float* negs, const float* dpos,
                            const float* dneg, const kge_grads* g, void* ws, cudaStream_t s);
 size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode, int es);
+size_t tc_rescal_workspace_bytes(long long batch, int dim, long long n_rel, int backward);
+int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, float* anchors, void* ws, size_t ws_bytes, cudaStream_t s);
+int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                              const long long* n_groups, long long n_rel, const float* ga, float* g_head, float* dproj,
+                              void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
 void gemm_profile_enable(int on);
 int gemm_profile_read(double* ms, long long* launches, double* flops);
@@ -184,6 +190,14 @@ static bool tc_forward(const kge_problem* p) {
 static bool tc_transr(const kge_problem* p) {
     return tensor_precision(p) && p->model == KGE_TRANSR && p->dtype == KGE_BF16 && p->dim % 8 == 0 && p->dim <= 256 &&
            p->neg_mode != KGE_NEG_CHUNK_SHARED;
+}
+// RESCAL projections on the tensor cores: fp32 tables split into bf16 pairs, one n-tile per row (dim <= 256)
+static bool tc_rescal(const kge_problem* p) {
+    return p->precision == KGE_PREC_TENSOR && p->model == KGE_RESCAL && p->dtype == KGE_F32 && p->dim % 8 == 0 && p->dim <= 256 &&
+           p->n_rel > 0;
+}
+static size_t tc_rescal_bytes(const kge_problem* p, int backward) {
+    return tc_rescal(p) ? tc_rescal_workspace_bytes(p->batch, p->dim, p->n_rel, backward) : 0;
 }
 static bool tc_backward(const kge_problem* p) { return tc_forward(p); }
 static size_t tc_bytes(const kge_problem* p, int backward) {
@@ -407,9 +421,18 @@ static size_t score_scratch_bytes(const kge_problem* p, int32_t backward) {
     if (backward && tc_transr(p))
         return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 1) + 256;
     if (backward && p->model == KGE_TRANSR) return transr_backward_workspace_bytes(p) + 256;
-    if (backward) return 3 * rb + tc_bytes(p, 1) + 256;
+    if (backward) return 3 * rb + tc_bytes(p, 1) + tc_rescal_bytes(p, 1) + 256;
     if (tc_transr(p)) return tc_transr_workspace_bytes(p->batch, p->neg_mode == KGE_NEG_NONE ? 0 : p->n_neg, p->dim, p->n_rel, 0) + 256;
-    return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + 256;
+    return (p->model == KGE_RESCAL ? rb : 0) + tc_bytes(p, 0) + tc_rescal_bytes(p, 0) + 256;
+}
+
+// RESCAL anchors by the tensor-core route where it applies (its scratch at `tcw`), else by the CUDA-core kernels
+static int rescal_anchors(const kge_problem* p, const kge_tensors* t, const ScoreArgs& a, float* anchors, char* tcw, int backward,
+                          cudaStream_t s) {
+    if (tc_rescal(p) && t->rel_perm && t->rel_seg && t->rel_uniq && t->n_rel_groups)
+        return launch_rescal_anchors_tc(a, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq, (const long long*)t->n_rel_groups,
+                                        p->n_rel, anchors, tcw, tc_rescal_bytes(p, backward), s);
+    return launch_rescal_anchors(p, t, anchors, s);
 }
 
 int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_score, float* neg_score, void* workspace,
@@ -441,7 +464,7 @@ int kge_score_forward(const kge_problem* p, const kge_tensors* t, float* pos_sco
     if (p->model == KGE_TRANSR) return launch_transr_forward(p, t, pos_score, neg_score, s);
     if (p->model == KGE_RESCAL) {
         float* anchors = static_cast<float*>(workspace);
-        rc = launch_rescal_anchors(p, t, anchors, s);
+        rc = rescal_anchors(p, t, a, anchors, static_cast<char*>(workspace) + rows_bytes(p) + tc_bytes(p, 0), 0, s);
         if (rc) return rc;
         a.anchors = anchors;
     }
@@ -504,8 +527,9 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     a.negs = const_cast<float*>(neg_score);
     a.dpos = dpos; a.dneg = dneg;
     a.g_head = g->g_head; a.g_tail = g->g_tail; a.g_neg = g->g_neg; a.g_rel = g->g_rel; a.g_rel2 = g->g_rel2;
+    char* rescal_tcw = static_cast<char*>(workspace) + 3 * rb + tc_bytes(p, 1);
     if (p->model == KGE_RESCAL) {
-        rc = launch_rescal_anchors(p, t, ws0, s);
+        rc = rescal_anchors(p, t, a, ws0, rescal_tcw, 1, s);
         if (rc) return rc;
         a.anchors = ws0; a.g_rel = ws2; a.g_rel2 = nullptr;
     }
@@ -531,7 +555,13 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
         rc = launch_triple_backward(a, s);
     }
     if (rc) return rc;
-    if (p->model == KGE_RESCAL) rc = launch_rescal_backward(p, t, ws2, g->g_head, g->g_rel2, s);
+    if (p->model == KGE_RESCAL) {
+        if (tc_rescal(p) && t->rel_perm && t->rel_seg && t->rel_uniq && t->n_rel_groups)
+            rc = launch_rescal_backward_tc(a, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq, (const long long*)t->n_rel_groups,
+                                           p->n_rel, ws2, g->g_head, g->g_rel2, rescal_tcw, tc_rescal_bytes(p, 1), s);
+        else
+            rc = launch_rescal_backward(p, t, ws2, g->g_head, g->g_rel2, s);
+    }
     return rc;
 }
 

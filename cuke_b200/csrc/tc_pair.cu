@@ -1631,6 +1631,7 @@ struct TransRPlan {
     int4* tile_tab; long long* n_tiles;
     long long tile_cap;
     int4* tile_tab2; long long* n_tiles2; int tiles_m2;     // grouped-K tiles of the dP product (backward), or NULL
+    int z_is_group;             // the B matrices are packed per GROUP (RESCAL over fp32 tables): z = group index, not relation id
 };
 
 // One block: tiles per group, exclusive scan, tile table (first padded row, relation id, group, valid rows).
@@ -1655,7 +1656,7 @@ __global__ void __launch_bounds__(1024) transr_plan_kernel(TransRPlan pl) {
     for (int g = g0; g < g1; ++g) {
         const long long rows = (long long)(pl.rel_seg[g + 1] - pl.rel_seg[g]) * pl.per;
         const long long nt = (rows + UM_BM - 1) / UM_BM;
-        const int z = (int)pl.rel_uniq[g];
+        const int z = pl.z_is_group ? g : (int)pl.rel_uniq[g];
         for (long long t = 0; t < nt && t0 + t < pl.tile_cap; ++t)
             pl.tile_tab[t0 + t] = make_int4((int)((t0 + t) * UM_BM), z, g, (int)min((long long)UM_BM, rows - t * UM_BM));
         if (pl.tile_tab2)
@@ -1849,7 +1850,7 @@ static int transr_tc(const ScoreArgs& a_in, int mode, float neg_w, float* loss, 
     pl.tile_tab = reinterpret_cast<int4*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
     pl.tile_cap = L.tile_cap;
     pl.tile_tab2 = backward ? reinterpret_cast<int4*>(w + L.off_tab2) : nullptr;
-    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2;
+    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2; pl.z_is_group = 0;
     transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
     KGE_LAUNCH_CHECK("transr_plan_kernel");
     {
@@ -1938,6 +1939,192 @@ int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss,
                                    const long long* rel_uniq, const long long* n_groups, long long n_rel, void* ws, size_t ws_bytes,
                                    cudaStream_t s) {
     return transr_tc(a, 2, neg_w, loss, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
+}
+
+// ---- RESCAL projections on the tensor cores (fp32 tables, bf16 operand split) --------------------------------------------
+// anchors[i] = E[h_i] . P[r_i], g_head[i] = ga[i] . P[r_i]^T and dP[g] = sum over the group of E[h]^T (x) ga are the same
+// relation-grouped products as TransR's, over fp32 tables: rows and the matrices of the relations that occur in the batch
+// are split into bf16 pairs (v ~ hi + lo) by two pack kernels, and umma_gemm_kernel<G_GROUPED> runs them with three MMAs per
+// k-step.  A group of ~33 rows fills a quarter of a 128-row tile, but the tensor pipe has the room (the products are bound by
+// reading the matrices): what counts is that a matrix is read from HBM once, split once, and then read by TMA.
+struct RescalTcLayout { size_t off_xhi, off_xlo, off_phi, off_plo, off_dst, off_tab, off_nt, off_tab2, off_ghi, off_glo, total;
+                        long long rows_cap, tile_cap, gmax; int tiles_m2; };
+static RescalTcLayout rescal_tc_layout(long long batch, int dim, long long n_rel, bool backward) {
+    RescalTcLayout L;
+    L.gmax = n_rel < batch ? n_rel : batch;
+    L.rows_cap = batch + L.gmax * UM_BM;
+    L.tile_cap = L.rows_cap / UM_BM + 1;
+    L.tiles_m2 = (dim + UM_BM - 1) / UM_BM;
+    size_t o = 0;
+    L.off_xhi = o; o += al256((size_t)L.rows_cap * dim * 2);
+    L.off_xlo = o; o += al256((size_t)L.rows_cap * dim * 2);
+    L.off_phi = o; o += al256((size_t)L.gmax * dim * dim * 2);
+    L.off_plo = o; o += al256((size_t)L.gmax * dim * dim * 2);
+    L.off_dst = o; o += al256((size_t)L.rows_cap * 8);
+    L.off_tab = o; o += al256((size_t)L.tile_cap * 16);
+    L.off_nt = o; o += 256;
+    L.off_tab2 = o; o += backward ? al256((size_t)L.gmax * L.tiles_m2 * 16) : 0;
+    L.off_ghi = o; o += backward ? al256((size_t)L.rows_cap * dim * 2) : 0;
+    L.off_glo = o; o += backward ? al256((size_t)L.rows_cap * dim * 2) : 0;
+    L.total = o;
+    return L;
+}
+size_t tc_rescal_workspace_bytes(long long batch, int dim, long long n_rel, int backward) {
+    return rescal_tc_layout(batch, dim, n_rel, backward != 0).total;
+}
+
+// One CTA per tile (8 warps x 16 rows): the group's rows as bf16 pairs.  SRC 0: entity rows E[h] (fp32), 1: fp32 rows
+// `frows` in triple order.  row_dst (if given): -2 - triple for the valid rows (the scatter epilogue's "positive" slot:
+// output row = triple), -1 for padding.
+template <typename I, int SRC>
+__global__ void __launch_bounds__(256) rescal_pack_rows_kernel(ScoreArgs a, TransRPlan pl, const float* frows, __nv_bfloat16* hi,
+                                                               __nv_bfloat16* lo, long long* row_dst) {
+    const long long tile = blockIdx.x;
+    if (tile >= *pl.n_tiles) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int4 tt = pl.tile_tab[tile];
+    const int g = tt.z, valid = tt.w;
+    long long t0 = tile;
+    while (t0 > 0 && pl.tile_tab[t0 - 1].z == g) --t0;              // the group's first tile (a group has few tiles)
+    const long long first = (long long)tt.x - pl.tile_tab[t0].x;    // group-local index of this tile's first row
+    const int dim = a.dim;
+    for (int rr = warp; rr < UM_BM; rr += 8) {
+        const long long prow = (long long)tt.x + rr;
+        __nv_bfloat16* oh = hi + prow * dim;
+        __nv_bfloat16* ol = lo + prow * dim;
+        if (rr >= valid) {
+            for (int k = lane * 4; k < dim; k += 128) {
+                *reinterpret_cast<uint2*>(oh + k) = make_uint2(0u, 0u);
+                *reinterpret_cast<uint2*>(ol + k) = make_uint2(0u, 0u);
+            }
+            if (row_dst && lane == 0) row_dst[prow] = -1;
+            continue;
+        }
+        const int tri = pl.rel_perm[pl.rel_seg[g] + (int)(first + rr)];
+        const float* src = SRC == 0 ? reinterpret_cast<const float*>(a.ent) + load_id<I>(a.h, tri) * dim : frows + (long long)tri * dim;
+        for (int k = lane * 4; k < dim; k += 128)
+            put_quad(oh + k, ol + k, nullptr, __ldg(reinterpret_cast<const float4*>(src + k)));
+        if (row_dst && lane == 0) row_dst[prow] = -2 - (long long)tri;
+    }
+}
+
+// P[rel_uniq[g]] (dim x dim fp32) -> bf16 pairs at packed matrix g, for g < n_groups.  grid (blocks per matrix, gmax).
+__global__ void __launch_bounds__(256) rescal_pack_p_kernel(const float* proj, const long long* rel_uniq, const long long* n_groups,
+                                                            int dim, __nv_bfloat16* hi, __nv_bfloat16* lo) {
+    const long long g = blockIdx.y;
+    if (g >= *n_groups) return;
+    const long long quads = (long long)dim * dim / 4;
+    const float4* src = reinterpret_cast<const float4*>(proj + rel_uniq[g] * (long long)dim * dim);
+    __nv_bfloat16* oh = hi + g * (long long)dim * dim;
+    __nv_bfloat16* ol = lo + g * (long long)dim * dim;
+    for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (long long)gridDim.x * blockDim.x)
+        put_quad(oh + 4 * q, ol + 4 * q, nullptr, __ldg(src + q));
+}
+
+struct RescalTc {
+    RescalTcLayout L; TransRPlan pl; char* w;
+    __nv_bfloat16 *xhi, *xlo, *phi, *plo, *ghi, *glo; long long* dst;
+};
+
+// Plan (tile list), X rows and the batch's matrices as bf16 pairs.  a: fp32 tables, dim % 8 == 0, dim <= 256.
+static int rescal_tc_prepare(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, bool backward, void* ws, size_t ws_bytes, RescalTc& r,
+                             cudaStream_t s) {
+    r.L = rescal_tc_layout(a.batch, a.dim, n_rel, backward);
+    const RescalTcLayout& L = r.L;
+    if (ws_bytes < L.total) { set_error("RESCAL tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
+    char* w = r.w = static_cast<char*>(ws);
+    r.xhi = reinterpret_cast<__nv_bfloat16*>(w + L.off_xhi); r.xlo = reinterpret_cast<__nv_bfloat16*>(w + L.off_xlo);
+    r.phi = reinterpret_cast<__nv_bfloat16*>(w + L.off_phi); r.plo = reinterpret_cast<__nv_bfloat16*>(w + L.off_plo);
+    r.ghi = backward ? reinterpret_cast<__nv_bfloat16*>(w + L.off_ghi) : nullptr;
+    r.glo = backward ? reinterpret_cast<__nv_bfloat16*>(w + L.off_glo) : nullptr;
+    r.dst = reinterpret_cast<long long*>(w + L.off_dst);
+    TransRPlan& pl = r.pl;
+    pl.rel_perm = rel_perm; pl.rel_seg = rel_seg; pl.rel_uniq = rel_uniq; pl.n_groups = n_groups; pl.per = 1;
+    pl.tile_tab = reinterpret_cast<int4*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
+    pl.tile_cap = L.tile_cap;
+    pl.tile_tab2 = backward ? reinterpret_cast<int4*>(w + L.off_tab2) : nullptr;
+    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2; pl.z_is_group = 1;
+    transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
+    KGE_LAUNCH_CHECK("transr_plan_kernel");
+    const unsigned blocks = (unsigned)L.tile_cap;
+    if (a.id_bits == 64) rescal_pack_rows_kernel<int64_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, r.xlo, r.dst);
+    else rescal_pack_rows_kernel<int32_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, r.xlo, r.dst);
+    KGE_LAUNCH_CHECK("rescal_pack_rows_kernel");
+    const unsigned per_matrix = (unsigned)(((long long)a.dim * a.dim / 4 + 1023) / 1024);
+    rescal_pack_p_kernel<<<dim3(per_matrix, (unsigned)L.gmax), 256, 0, s>>>(reinterpret_cast<const float*>(a.rel2), rel_uniq, n_groups, a.dim,
+                                                                          r.phi, r.plo);
+    KGE_LAUNCH_CHECK("rescal_pack_p_kernel");
+    return 0;
+}
+
+static void rescal_tc_params(GemmTc& p, const ScoreArgs& a, const RescalTc& r) {
+    memset(&p, 0, sizeof(p));
+    p.m_rows = (int)r.L.rows_cap; p.n_cols = a.dim; p.k_len = a.dim; p.bn = (a.dim + 15) / 16 * 16;
+    p.elem_bytes = 2; p.passes = 3;
+    p.tile_tab = r.pl.tile_tab; p.n_tiles_dev = r.pl.n_tiles; p.tile_cap = r.L.tile_cap;
+    p.row_dst = r.dst; p.ep = EP_SCATTER; p.sc_n_neg = 1;
+}
+
+// anchors (batch, dim) fp32 in triple order.  ws: tc_rescal_workspace_bytes(batch, dim, n_rel, 0).
+int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                             const long long* n_groups, long long n_rel, float* anchors, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (a.batch <= 0) return 0;
+    RescalTc r;
+    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, false, ws, ws_bytes, r, s);
+    if (rc) return rc;
+    const uint64_t lda = (uint64_t)a.dim * 2;
+    CUtensorMap mah, mal, mbh, mbl;
+    // Y = X . P[g]: A = packed rows (K-major), B = packed matrix of the group as stored (MN-major: out[j] = sum_i x[i] P[i][j])
+    if ((rc = make_tensor_map_3d(&mah, r.xhi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mal, r.xlo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, r.phi, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, r.plo, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
+    GemmTc p;
+    rescal_tc_params(p, a, r);
+    p.a_mn = 0; p.b_mn = 1;
+    p.pos_out = anchors; p.neg_out = anchors;
+    return run_gemm(mah, mal, mbh, mbl, p, 1, s);
+}
+
+// g_head[i] = ga[i] . P[r_i]^T (rows of g_head in triple order) and dproj[g] = sum over group g of E[h]^T (x) ga.
+// ws: tc_rescal_workspace_bytes(batch, dim, n_rel, 1).
+int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
+                              const long long* n_groups, long long n_rel, const float* ga, float* g_head, float* dproj,
+                              void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (a.batch <= 0) return 0;
+    RescalTc r;
+    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, true, ws, ws_bytes, r, s);
+    if (rc) return rc;
+    const unsigned blocks = (unsigned)r.L.tile_cap;
+    if (a.id_bits == 64) rescal_pack_rows_kernel<int64_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.glo, nullptr);
+    else rescal_pack_rows_kernel<int32_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.glo, nullptr);
+    KGE_LAUNCH_CHECK("rescal_pack_rows_kernel(ga)");
+    const uint64_t lda = (uint64_t)a.dim * 2;
+    const int bn = (a.dim + 15) / 16 * 16;
+    CUtensorMap mgh, mgl, mph, mpl;
+    // GH = GA . P[g]^T: A = packed gradient rows (K-major over j), B[n = i][k = j] = P[g][i][j] (K-major as stored)
+    if ((rc = make_tensor_map_3d(&mgh, r.ghi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mgl, r.glo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mph, r.phi, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mpl, r.plo, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
+    GemmTc p;
+    rescal_tc_params(p, a, r);
+    p.a_mn = 0; p.b_mn = 0;
+    p.pos_out = g_head; p.neg_out = g_head;
+    if ((rc = run_gemm(mgh, mgl, mph, mpl, p, 1, s))) return rc;
+    // dP[g] = X^T . GA over the group's (zero-padded) rows: both operands MN-major, K runs over the rows
+    CUtensorMap mxh, mxl, mvh, mvl;
+    if ((rc = make_tensor_map_3d(&mxh, r.xhi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mxl, r.xlo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mvh, r.ghi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mvl, r.glo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, 64, 64))) return rc;
+    GemmTc q;
+    memset(&q, 0, sizeof(q));
+    q.m_rows = a.dim; q.n_cols = a.dim; q.k_len = UM_BM; q.bn = bn; q.a_mn = 1; q.b_mn = 1; q.elem_bytes = 2; q.passes = 3;
+    q.tile_tab = r.pl.tile_tab2; q.n_tiles_dev = r.pl.n_tiles2; q.tile_cap = r.L.gmax * r.L.tiles_m2; q.group_k = 1;
+    q.ep = EP_STORE; q.out = dproj; q.out_ld = a.dim; q.out_batch_rows = a.dim;
+    return run_gemm(mxh, mxl, mvh, mvl, q, 1, s);
 }
 
 }  // namespace kge
