@@ -580,7 +580,7 @@ def main():
     w_main = max(args.warmup, 3)
     # settle: allocator pools, clocks and the NCCL channels reach their steady state before the W warm-up steps begin
     # (a fixed number of steps: every rank must make the same calls)
-    for i_settle in range(64):
+    for i_settle in range(64 if args.steps >= 10 else 0):      # (short runs are profiling runs: every launch costs there)
         stepper.step(*devb[i_settle % nb], prefetch=None if args.no_prefetch else devb[(i_settle + 1) % nb])
         if i_settle % 8 == 7:
             torch.cuda.synchronize()

@@ -67,10 +67,11 @@ int launch_transr_backward(const kge_problem* p, const kge_tensors* t, const flo
 size_t tc_pair_workspace_bytes(long long batch, int chunk, int n_neg, int dim, int mode, int es);
 size_t tc_rescal_workspace_bytes(long long batch, int dim, long long n_rel, int backward);
 int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
-                             const long long* n_groups, long long n_rel, float* anchors, void* ws, size_t ws_bytes, cudaStream_t s);
+                             const long long* n_groups, long long n_rel, float* anchors, int backward, void* ws, size_t ws_bytes,
+                             cudaStream_t s);
 int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                               const long long* n_groups, long long n_rel, const float* ga, float* g_head, float* dproj,
-                              void* ws, size_t ws_bytes, cudaStream_t s);
+                              bool prepared, void* ws, size_t ws_bytes, cudaStream_t s);
 int launch_pair_forward_tc(const ScoreArgs& a, int head, void* ws, size_t ws_bytes, cudaStream_t s);
 void gemm_profile_enable(int on);
 int gemm_profile_read(double* ms, long long* launches, double* flops);
@@ -431,7 +432,7 @@ static int rescal_anchors(const kge_problem* p, const kge_tensors* t, const Scor
                           cudaStream_t s) {
     if (tc_rescal(p) && t->rel_perm && t->rel_seg && t->rel_uniq && t->n_rel_groups)
         return launch_rescal_anchors_tc(a, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq, (const long long*)t->n_rel_groups,
-                                        p->n_rel, anchors, tcw, tc_rescal_bytes(p, backward), s);
+                                        p->n_rel, anchors, backward, tcw, tc_rescal_bytes(p, backward), s);
     return launch_rescal_anchors(p, t, anchors, s);
 }
 
@@ -558,7 +559,7 @@ int kge_score_backward(const kge_problem* p, const kge_tensors* t, const float* 
     if (p->model == KGE_RESCAL) {
         if (tc_rescal(p) && t->rel_perm && t->rel_seg && t->rel_uniq && t->n_rel_groups)
             rc = launch_rescal_backward_tc(a, t->rel_perm, t->rel_seg, (const long long*)t->rel_uniq, (const long long*)t->n_rel_groups,
-                                           p->n_rel, ws2, g->g_head, g->g_rel2, rescal_tcw, tc_rescal_bytes(p, 1), s);
+                                           p->n_rel, ws2, g->g_head, g->g_rel2, true, rescal_tcw, tc_rescal_bytes(p, 1), s);
         else
             rc = launch_rescal_backward(p, t, ws2, g->g_head, g->g_rel2, s);
     }

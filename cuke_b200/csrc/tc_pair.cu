@@ -2027,9 +2027,11 @@ struct RescalTc {
 };
 
 // Plan (tile list), X rows and the batch's matrices as bf16 pairs.  a: fp32 tables, dim % 8 == 0, dim <= 256.
+// launch == false: the workspace already holds all of that from an earlier call with the same arguments on this stream
+// (the anchors of a backward call): only the pointers are rebuilt.
 static int rescal_tc_prepare(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                              const long long* n_groups, long long n_rel, bool backward, void* ws, size_t ws_bytes, RescalTc& r,
-                             cudaStream_t s) {
+                             cudaStream_t s, bool launch = true) {
     r.L = rescal_tc_layout(a.batch, a.dim, n_rel, backward);
     const RescalTcLayout& L = r.L;
     if (ws_bytes < L.total) { set_error("RESCAL tensor-core workspace: need %zu bytes, got %zu", L.total, ws_bytes); return KGE_E_WORKSPACE; }
@@ -2045,6 +2047,7 @@ static int rescal_tc_prepare(const ScoreArgs& a, const int* rel_perm, const int*
     pl.tile_cap = L.tile_cap;
     pl.tile_tab2 = backward ? reinterpret_cast<int4*>(w + L.off_tab2) : nullptr;
     pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2; pl.z_is_group = 1;
+    if (!launch) return 0;
     transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
     KGE_LAUNCH_CHECK("transr_plan_kernel");
     const unsigned blocks = (unsigned)L.tile_cap;
@@ -2066,12 +2069,14 @@ static void rescal_tc_params(GemmTc& p, const ScoreArgs& a, const RescalTc& r) {
     p.row_dst = r.dst; p.ep = EP_SCATTER; p.sc_n_neg = 1;
 }
 
-// anchors (batch, dim) fp32 in triple order.  ws: tc_rescal_workspace_bytes(batch, dim, n_rel, 0).
+// anchors (batch, dim) fp32 in triple order.  ws: tc_rescal_workspace_bytes(batch, dim, n_rel, backward); with backward != 0 the
+// workspace is laid out (and the tile lists built) for a launch_rescal_backward_tc(..., prepared = true) that follows.
 int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
-                             const long long* n_groups, long long n_rel, float* anchors, void* ws, size_t ws_bytes, cudaStream_t s) {
+                             const long long* n_groups, long long n_rel, float* anchors, int backward, void* ws, size_t ws_bytes,
+                             cudaStream_t s) {
     if (a.batch <= 0) return 0;
     RescalTc r;
-    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, false, ws, ws_bytes, r, s);
+    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, backward != 0, ws, ws_bytes, r, s);
     if (rc) return rc;
     const uint64_t lda = (uint64_t)a.dim * 2;
     CUtensorMap mah, mal, mbh, mbl;
@@ -2088,13 +2093,13 @@ int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int*
 }
 
 // g_head[i] = ga[i] . P[r_i]^T (rows of g_head in triple order) and dproj[g] = sum over group g of E[h]^T (x) ga.
-// ws: tc_rescal_workspace_bytes(batch, dim, n_rel, 1).
+// ws: tc_rescal_workspace_bytes(batch, dim, n_rel, 1); prepared: see launch_rescal_anchors_tc.
 int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int* rel_seg, const long long* rel_uniq,
                               const long long* n_groups, long long n_rel, const float* ga, float* g_head, float* dproj,
-                              void* ws, size_t ws_bytes, cudaStream_t s) {
+                              bool prepared, void* ws, size_t ws_bytes, cudaStream_t s) {
     if (a.batch <= 0) return 0;
     RescalTc r;
-    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, true, ws, ws_bytes, r, s);
+    int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, true, ws, ws_bytes, r, s, !prepared);
     if (rc) return rc;
     const unsigned blocks = (unsigned)r.L.tile_cap;
     if (a.id_bits == 64) rescal_pack_rows_kernel<int64_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.glo, nullptr);
