@@ -194,8 +194,7 @@ static bool tc_transr(const kge_problem* p) {
 }
 // RESCAL projections on the tensor cores: fp32 tables split into bf16 pairs, one n-tile per row (dim <= 256)
 static bool tc_rescal(const kge_problem* p) {
-    return p->precision == KGE_PREC_TENSOR && p->model == KGE_RESCAL && p->dtype == KGE_F32 && p->dim % 8 == 0 && p->dim <= 256 &&
-           p->n_rel > 0;
+    return p->precision == KGE_PREC_TENSOR && p->model == KGE_RESCAL && p->dim % 8 == 0 && p->dim <= 256 && p->n_rel > 0;
 }
 static size_t tc_rescal_bytes(const kge_problem* p, int backward) {
     return tc_rescal(p) ? tc_rescal_workspace_bytes(p->batch, p->dim, p->n_rel, backward) : 0;

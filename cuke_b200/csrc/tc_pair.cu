@@ -1941,12 +1941,14 @@ int launch_transr_loss_backward_tc(const ScoreArgs& a, float neg_w, float* loss,
     return transr_tc(a, 2, neg_w, loss, dproj, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, ws, ws_bytes, s);
 }
 
-// ---- RESCAL projections on the tensor cores (fp32 tables, bf16 operand split) --------------------------------------------
+// ---- RESCAL projections on the tensor cores (fp32 tables: bf16 operand split; bf16 tables: one pass) ---------------------
 // anchors[i] = E[h_i] . P[r_i], g_head[i] = ga[i] . P[r_i]^T and dP[g] = sum over the group of E[h]^T (x) ga are the same
 // relation-grouped products as TransR's, over fp32 tables: rows and the matrices of the relations that occur in the batch
 // are split into bf16 pairs (v ~ hi + lo) by two pack kernels, and umma_gemm_kernel<G_GROUPED> runs them with three MMAs per
 // k-step.  A group of ~33 rows fills a quarter of a 128-row tile, but the tensor pipe has the room (the products are bound by
-// reading the matrices): what counts is that a matrix is read from HBM once, split once, and then read by TMA.
+// reading the matrices): what counts is that a matrix is read from HBM once, split once, and then read by TMA.  Over bf16
+// tables nothing is split: rows are copied, P[r] is read by TMA straight from the table, gradient rows are rounded to bf16
+// (the 2e-2 tolerance of bf16 tables), one MMA per k-step.
 struct RescalTcLayout { size_t off_xhi, off_xlo, off_phi, off_plo, off_dst, off_tab, off_nt, off_tab2, off_ghi, off_glo, total;
                         long long rows_cap, tile_cap, gmax; int tiles_m2; };
 static RescalTcLayout rescal_tc_layout(long long batch, int dim, long long n_rel, bool backward) {
@@ -1976,7 +1978,8 @@ size_t tc_rescal_workspace_bytes(long long batch, int dim, long long n_rel, int 
 // One CTA per tile (8 warps x 16 rows): the group's rows as bf16 pairs.  SRC 0: entity rows E[h] (fp32), 1: fp32 rows
 // `frows` in triple order.  row_dst (if given): -2 - triple for the valid rows (the scatter epilogue's "positive" slot:
 // output row = triple), -1 for padding.
-template <typename I, int SRC>
+// lo == NULL (bf16 tables): one bf16 term per element - entity rows are copied, fp32 rows rounded.
+template <typename T, typename I, int SRC>
 __global__ void __launch_bounds__(256) rescal_pack_rows_kernel(ScoreArgs a, TransRPlan pl, const float* frows, __nv_bfloat16* hi,
                                                                __nv_bfloat16* lo, long long* row_dst) {
     const long long tile = blockIdx.x;
@@ -1995,15 +1998,19 @@ __global__ void __launch_bounds__(256) rescal_pack_rows_kernel(ScoreArgs a, Tran
         if (rr >= valid) {
             for (int k = lane * 4; k < dim; k += 128) {
                 *reinterpret_cast<uint2*>(oh + k) = make_uint2(0u, 0u);
-                *reinterpret_cast<uint2*>(ol + k) = make_uint2(0u, 0u);
+                if (lo) *reinterpret_cast<uint2*>(ol + k) = make_uint2(0u, 0u);
             }
             if (row_dst && lane == 0) row_dst[prow] = -1;
             continue;
         }
         const int tri = pl.rel_perm[pl.rel_seg[g] + (int)(first + rr)];
-        const float* src = SRC == 0 ? reinterpret_cast<const float*>(a.ent) + load_id<I>(a.h, tri) * dim : frows + (long long)tri * dim;
-        for (int k = lane * 4; k < dim; k += 128)
-            put_quad(oh + k, ol + k, nullptr, __ldg(reinterpret_cast<const float4*>(src + k)));
+        for (int k = lane * 4; k < dim; k += 128) {
+            float4 v;
+            if (SRC == 0) v = ldg4(reinterpret_cast<const T*>(a.ent) + load_id<I>(a.h, tri) * dim + k);
+            else v = __ldg(reinterpret_cast<const float4*>(frows + (long long)tri * dim + k));
+            if (lo) put_quad(oh + k, ol + k, nullptr, v);
+            else { float4 back; *reinterpret_cast<uint2*>(oh + k) = bf16x4(v, back); }
+        }
         if (row_dst && lane == 0) row_dst[prow] = -2 - (long long)tri;
     }
 }
@@ -2024,6 +2031,9 @@ __global__ void __launch_bounds__(256) rescal_pack_p_kernel(const float* proj, c
 struct RescalTc {
     RescalTcLayout L; TransRPlan pl; char* w;
     __nv_bfloat16 *xhi, *xlo, *phi, *plo, *ghi, *glo; long long* dst;
+    bool single;               // bf16 tables: one term per operand, the matrices read straight from the table
+    long long p_batch;         // matrices behind phi / plo: the batch's groups (packed) or all relations (the table)
+    int passes;
 };
 
 // Plan (tile list), X rows and the batch's matrices as bf16 pairs.  a: fp32 tables, dim % 8 == 0, dim <= 256.
@@ -2041,19 +2051,33 @@ static int rescal_tc_prepare(const ScoreArgs& a, const int* rel_perm, const int*
     r.ghi = backward ? reinterpret_cast<__nv_bfloat16*>(w + L.off_ghi) : nullptr;
     r.glo = backward ? reinterpret_cast<__nv_bfloat16*>(w + L.off_glo) : nullptr;
     r.dst = reinterpret_cast<long long*>(w + L.off_dst);
+    r.single = a.dtype == KGE_BF16;
+    r.passes = r.single ? 1 : 3;
+    r.p_batch = r.single ? n_rel : L.gmax;
+    if (r.single) {            // every "lo" aliases its "hi": run_gemm reads one map per operand in a single pass
+        r.xlo = r.xhi; r.glo = r.ghi;
+        r.phi = r.plo = const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(a.rel2));
+    }
     TransRPlan& pl = r.pl;
     pl.rel_perm = rel_perm; pl.rel_seg = rel_seg; pl.rel_uniq = rel_uniq; pl.n_groups = n_groups; pl.per = 1;
     pl.tile_tab = reinterpret_cast<int4*>(w + L.off_tab); pl.n_tiles = reinterpret_cast<long long*>(w + L.off_nt);
     pl.tile_cap = L.tile_cap;
     pl.tile_tab2 = backward ? reinterpret_cast<int4*>(w + L.off_tab2) : nullptr;
-    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2; pl.z_is_group = 1;
+    pl.n_tiles2 = pl.n_tiles + 1; pl.tiles_m2 = L.tiles_m2; pl.z_is_group = r.single ? 0 : 1;
     if (!launch) return 0;
     transr_plan_kernel<<<1, 1024, 0, s>>>(pl);
     KGE_LAUNCH_CHECK("transr_plan_kernel");
     const unsigned blocks = (unsigned)L.tile_cap;
-    if (a.id_bits == 64) rescal_pack_rows_kernel<int64_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, r.xlo, r.dst);
-    else rescal_pack_rows_kernel<int32_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, r.xlo, r.dst);
+    __nv_bfloat16* xlo = r.single ? nullptr : r.xlo;
+    if (r.single) {
+        if (a.id_bits == 64) rescal_pack_rows_kernel<__nv_bfloat16, int64_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, xlo, r.dst);
+        else rescal_pack_rows_kernel<__nv_bfloat16, int32_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, xlo, r.dst);
+    } else {
+        if (a.id_bits == 64) rescal_pack_rows_kernel<float, int64_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, xlo, r.dst);
+        else rescal_pack_rows_kernel<float, int32_t, 0><<<blocks, 256, 0, s>>>(a, pl, nullptr, r.xhi, xlo, r.dst);
+    }
     KGE_LAUNCH_CHECK("rescal_pack_rows_kernel");
+    if (r.single) return 0;
     const unsigned per_matrix = (unsigned)(((long long)a.dim * a.dim / 4 + 1023) / 1024);
     rescal_pack_p_kernel<<<dim3(per_matrix, (unsigned)L.gmax), 256, 0, s>>>(reinterpret_cast<const float*>(a.rel2), rel_uniq, n_groups, a.dim,
                                                                           r.phi, r.plo);
@@ -2064,7 +2088,7 @@ static int rescal_tc_prepare(const ScoreArgs& a, const int* rel_perm, const int*
 static void rescal_tc_params(GemmTc& p, const ScoreArgs& a, const RescalTc& r) {
     memset(&p, 0, sizeof(p));
     p.m_rows = (int)r.L.rows_cap; p.n_cols = a.dim; p.k_len = a.dim; p.bn = (a.dim + 15) / 16 * 16;
-    p.elem_bytes = 2; p.passes = 3;
+    p.elem_bytes = 2; p.passes = r.passes;
     p.tile_tab = r.pl.tile_tab; p.n_tiles_dev = r.pl.n_tiles; p.tile_cap = r.L.tile_cap;
     p.row_dst = r.dst; p.ep = EP_SCATTER; p.sc_n_neg = 1;
 }
@@ -2083,8 +2107,8 @@ int launch_rescal_anchors_tc(const ScoreArgs& a, const int* rel_perm, const int*
     // Y = X . P[g]: A = packed rows (K-major), B = packed matrix of the group as stored (MN-major: out[j] = sum_i x[i] P[i][j])
     if ((rc = make_tensor_map_3d(&mah, r.xhi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
     if ((rc = make_tensor_map_3d(&mal, r.xlo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
-    if ((rc = make_tensor_map_3d(&mbh, r.phi, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
-    if ((rc = make_tensor_map_3d(&mbl, r.plo, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mbh, r.phi, 2, r.p_batch, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mbl, r.plo, 2, r.p_batch, a.dim, a.dim, lda, lda * a.dim, 64, 64))) return rc;
     GemmTc p;
     rescal_tc_params(p, a, r);
     p.a_mn = 0; p.b_mn = 1;
@@ -2102,8 +2126,9 @@ int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int
     int rc = rescal_tc_prepare(a, rel_perm, rel_seg, rel_uniq, n_groups, n_rel, true, ws, ws_bytes, r, s, !prepared);
     if (rc) return rc;
     const unsigned blocks = (unsigned)r.L.tile_cap;
-    if (a.id_bits == 64) rescal_pack_rows_kernel<int64_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.glo, nullptr);
-    else rescal_pack_rows_kernel<int32_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.glo, nullptr);
+    // (the source type of the SRC = 1 form is fp32 whatever the tables are)
+    if (a.id_bits == 64) rescal_pack_rows_kernel<float, int64_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.single ? nullptr : r.glo, nullptr);
+    else rescal_pack_rows_kernel<float, int32_t, 1><<<blocks, 256, 0, s>>>(a, r.pl, ga, r.ghi, r.single ? nullptr : r.glo, nullptr);
     KGE_LAUNCH_CHECK("rescal_pack_rows_kernel(ga)");
     const uint64_t lda = (uint64_t)a.dim * 2;
     const int bn = (a.dim + 15) / 16 * 16;
@@ -2111,8 +2136,8 @@ int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int
     // GH = GA . P[g]^T: A = packed gradient rows (K-major over j), B[n = i][k = j] = P[g][i][j] (K-major as stored)
     if ((rc = make_tensor_map_3d(&mgh, r.ghi, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
     if ((rc = make_tensor_map_3d(&mgl, r.glo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, UM_BM, 64))) return rc;
-    if ((rc = make_tensor_map_3d(&mph, r.phi, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
-    if ((rc = make_tensor_map_3d(&mpl, r.plo, 2, r.L.gmax, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mph, r.phi, 2, r.p_batch, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
+    if ((rc = make_tensor_map_3d(&mpl, r.plo, 2, r.p_batch, a.dim, a.dim, lda, lda * a.dim, bn, 64))) return rc;
     GemmTc p;
     rescal_tc_params(p, a, r);
     p.a_mn = 0; p.b_mn = 0;
@@ -2126,7 +2151,7 @@ int launch_rescal_backward_tc(const ScoreArgs& a, const int* rel_perm, const int
     if ((rc = make_tensor_map_3d(&mvl, r.glo, 2, 1, r.L.rows_cap, a.dim, lda, lda * r.L.rows_cap, 64, 64))) return rc;
     GemmTc q;
     memset(&q, 0, sizeof(q));
-    q.m_rows = a.dim; q.n_cols = a.dim; q.k_len = UM_BM; q.bn = bn; q.a_mn = 1; q.b_mn = 1; q.elem_bytes = 2; q.passes = 3;
+    q.m_rows = a.dim; q.n_cols = a.dim; q.k_len = UM_BM; q.bn = bn; q.a_mn = 1; q.b_mn = 1; q.elem_bytes = 2; q.passes = r.passes;
     q.tile_tab = r.pl.tile_tab2; q.n_tiles_dev = r.pl.n_tiles2; q.tile_cap = r.L.gmax * r.L.tiles_m2; q.group_k = 1;
     q.ep = EP_STORE; q.out = dproj; q.out_ld = a.dim; q.out_batch_rows = a.dim;
     return run_gemm(mxh, mxl, mvh, mvl, q, 1, s);
