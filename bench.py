@@ -8,15 +8,20 @@
 
 Workload (default c5): TransE and DistMult scored on the same batch, fp32, entity table 4,000,000 x 400 rows
 row-partitioned over the N GPUs, relations 1000 x 400 replicated, 65,536 triples per GPU per step, 1,024 shared
-negatives per 1,024-triple chunk, Zipf(1.1) entity ids.  A step = inspector, staging of distinct rows (NCCL
-all-to-all when N > 1), forward, logistic loss, backward, segmented gradient reduction (and the exchange back to
-the owners) for BOTH scorers.  Scored triples per step per GPU = 2 scorers x (65,536 + 64 x 1,024 x 1,024).
+negatives per 1,024-triple chunk, Zipf(1.1) entity ids.  A step = inspector, staging of distinct rows, forward,
+logistic loss, backward, segmented gradient reduction, the way back to the rows' owners and the sparse SGD update,
+for BOTH scorers.  When N > 1 rows and gradient rows move by kernels that read the other GPUs' memory over NVLink
+(`--no-peer-staging`: by NCCL all-to-all); `--micro k` cuts a step into k micro-batches; `--precision` selects the
+operand split of the tensor-core contractions (tensor = bf16 pairs, tensor_tf32 = tf32 pairs) or the fp32 CUDA-core
+path.  Scored triples per step per GPU = 2 scorers x (65,536 + 64 x 1,024 x 1,024).
 
 One JSON line is printed by rank 0.  `value` is measured with the step's ids already on the device; `e2e` includes
-the pinned-host -> device copy of the ids and the device -> host read of the losses every step.  `--impl reference`
+the pinned-host -> device copy of the ids and the device -> host read of the losses every step (consumed by the host
+one step late, the last one inside the timed region).  64 untimed settle steps precede the W warm-up steps of runs
+with K >= 10.  `--impl reference`
 times the reference's own CPU path (cuke's generated OpenMP C++, oracle/_ref) on a bounded sample.
 Beside the contract's keys the line carries
-  spread    the same K-step region repeated (median, min, max of ms per step);
+  spread    the same K-step region repeated (every region's ms per step, median, min, max, host time to queue a step);
   roofline  the dominant kernel timed live (useful TFLOP/s against the measured bf16 peak), the ncu DRAM traffic of
             its launches read from profiles/, and under "hbm" the compulsory bytes of the WHOLE step over the step time;
   parity    computed outside the timed regions: at N = 1 one whole chunk of the timed batch through the timed KgeStep
