@@ -246,6 +246,19 @@ def reference_arm(args, cfg, models):
     print(json.dumps(line), flush=True)
 
 
+def staging_note(stepper, world):
+    """How rows and gradient rows moved in this run (the peer path falls back to collectives on every rank alike if any
+    rank could not map a peer's memory; the reason is reported)."""
+    if world == 1:
+        return "local gather"
+    rows = "rows: one gather kernel over the owners' shards" if stepper.peers is not None else "rows: all-to-all of ids and rows (NCCL)"
+    grads = ("gradients: one owner-side sum over the ranks' buffers" if getattr(stepper, "_pull", False)
+             else "gradients: all-to-all + owner-side segmented sum (NCCL)")
+    how = " (CUDA IPC mappings, NVLink peer loads); NCCL for ids, counts and barriers" if stepper.peers is not None else ""
+    note = f"; peer access unavailable: {stepper.peer_note}" if getattr(stepper, "peer_note", None) else ""
+    return f"{rows}; {grads}{how}{note}"
+
+
 def workload_config(cfg, models, n_gpus):
     return {"workload": f"{cfg.name}: {'+'.join(models)} fwd+bwd fp32, entities {cfg.n_ent}x{cfg.dim} row-partitioned over "
                         f"{n_gpus} GPU(s), relations {cfg.n_rel}x{cfg.dim}, {cfg.batch} triples/GPU, {cfg.n_neg} shared negatives "
@@ -785,10 +798,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "triples/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": dict(workload_config(cfg, models, world), micro_batches=micro,
-                                                                                         staging=("rows: one gather kernel over the owners' shards; gradients: one owner-side sum over the ranks' buffers "
-                                                                                                  "(CUDA IPC mappings, NVLink peer loads); NCCL only for ids, counts and barriers"
-                                                                                                  if world > 1 and not args.no_peer_staging else
-                                                                                                  "all-to-all of ids and rows (NCCL)" if world > 1 else "local gather"),
+                                                                                         staging=staging_note(stepper, world),
                                                                                          arithmetic=(
                     "fp32 storage and accumulation; contractions on the tensor cores over a two-term bf16 split of each fp32 "
                     "operand (three MMAs per product, error-compensated; see the parity block for the measured error)"

@@ -49,6 +49,11 @@ def _close(handle: bytes) -> None:
         del _open_allocations[handle]
 
 
+class PeerUnavailable(RuntimeError):
+    """Raised on EVERY rank when any rank could not export its tensor or map a peer's (no peer access between two GPUs, memory
+    that did not come from cudaMalloc, ...): the callers fall back to collectives together."""
+
+
 class PeerMap:
     """One tensor per rank, each mapped into every process: `ptrs` is a device array of the `world` base addresses (this
     rank's own tensor included).  Collective: every rank of `group` constructs it at the same point of its program."""
@@ -61,23 +66,37 @@ class PeerMap:
         L = _lib.lib()
         handle = (C.c_ubyte * 64)()
         off = C.c_uint64(0)
-        check(L.kge_ipc_export(local.data_ptr(), handle, C.byref(off)))
-        mine = (bytes(handle), int(off.value), int(local.shape[0]))
+        problem = None
+        try:
+            check(L.kge_ipc_export(local.data_ptr(), handle, C.byref(off)))
+        except Exception as e:                      # still take part in the collectives below
+            problem = f"rank {rank}: {e}"
+        mine = (bytes(handle), int(off.value), int(local.shape[0]), problem)
         everyone = [None] * world
         dist.all_gather_object(everyone, mine, group=group)
-        self.rows = [rows for _, _, rows in everyone]
+        self.rows = [rows for _, _, rows, _ in everyone]
         self._opened = []
         ptrs = []
-        for g, (h, o, _) in enumerate(everyone):
-            if g == rank:
-                ptrs.append(local.data_ptr())
-                continue
-            self._opened.append(h)
-            ptrs.append(_open(h) + o)
-        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=local.device)
-        # every tensor is complete (and mapped everywhere) before anybody reads
+        problem = next((p for _, _, _, p in everyone if p), None)
+        if problem is None:
+            try:
+                for g, (h, o, _, _) in enumerate(everyone):
+                    if g == rank:
+                        ptrs.append(local.data_ptr())
+                        continue
+                    ptrs.append(_open(h) + o)
+                    self._opened.append(h)
+            except Exception as e:
+                problem = f"rank {rank}: {e}"
+        # every tensor is complete (and mapped everywhere) before anybody reads; the same collective tells every rank
+        # whether all of them succeeded
         torch.cuda.synchronize(local.device)
-        dist.barrier(group=group)
+        flag = torch.tensor([0 if problem is None else 1], dtype=torch.int32, device=local.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()) != 0:
+            self.close()
+            raise PeerUnavailable(problem or "another rank could not map a peer's memory")
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=local.device)
 
     def close(self) -> None:
         """Unmaps the peers' tensors (nobody may still be reading this rank's)."""

@@ -269,12 +269,17 @@ class KgeStep:
             import torch.distributed as dist
             self.plan_group = dist.new_group(backend="nccl") if group is not None and dist.get_backend(group) == "nccl" else group
         self.peers = None
+        self.peer_note = None          # why peer access is off although it was asked for
         if world > 1 and peer_staging:
-            from .peer import PeerTable
-            self.peers = PeerTable(ent_local, n_ent, rank, world, group)
+            from .peer import PeerTable, PeerUnavailable
+            try:
+                self.peers = PeerTable(ent_local, n_ent, rank, world, group)
+            except PeerUnavailable as e:           # raised on every rank alike: all of them take the all-to-all path
+                self.peer_note = str(e)
         self.exchange = RowExchange(ent_local, n_ent, rank, world, group, plan_group=self.plan_group, peers=self.peers) if world > 1 else None
         self._token = torch.zeros(1, dtype=torch.float32, device=dev) if self.peers is not None else None
         self._grad_maps = {}
+        self._pull = self.peers is not None
         self._fenced = False
         # gradient rows travel home on a side stream while the next scorer computes; plans of the next batch on another
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
@@ -536,14 +541,21 @@ class KgeStep:
         """Peer access: the buffer that holds this rank's entity-gradient rows of (scorer, micro-batch), mapped into every
         process.  Made on first use - a collective, reached by every rank at the same point of its first step."""
         key = (model, part)
+        if not self._pull:
+            return None
         gm = self._grad_maps.get(key)
         if gm is None or gm.local.shape[0] < rows:
-            from .peer import PeerMap
+            from .peer import PeerMap, PeerUnavailable
             if gm is not None:
                 torch.cuda.synchronize()
                 gm.close()
             buf = torch.empty((rows, self.dim), dtype=torch.float32, device=self.ent_local.device)
-            gm = PeerMap(buf, self.rank, self.world, self.group)
+            try:
+                gm = PeerMap(buf, self.rank, self.world, self.group)
+            except PeerUnavailable as e:           # every rank alike: gradients travel by all-to-all from now on
+                self._pull, self.peer_note = False, str(e)
+                self._grad_maps.pop(key, None)
+                return None
             self._grad_maps[key] = gm
         return gm
 

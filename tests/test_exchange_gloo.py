@@ -72,6 +72,23 @@ WORKER = textwrap.dedent('''
     k = int(on)
     assert oid[:k].tolist() == touched, "owner-side distinct ids"
     assert np.allclose(orows[:k].numpy(), dense[touched], rtol=1e-6), "owner-side gradient sums"
+    # The peer-memory form of the return (kge_pull_reduce): the owner reads every rank's gradient rows in place.  Its index
+    # arithmetic - where my rows start in rank r's buffer (sent along with the counts), where rank r's ids start in the
+    # concatenated request list - is restated here over all-gathered buffers: position pos of rank r in the request list
+    # is row src_off[r] + pos - src_start[r] of r's buffer.
+    S = sum(ex.serve)
+    if S:
+        src_off, src_start = ex.wanted[:, 1].tolist(), ex.src_start.tolist()
+        oi = ex.owner_insp
+        pulled = np.zeros((k, d))
+        for u in range(k):
+            for p in range(int(oi.seg[u]), int(oi.seg[u + 1]) if u + 1 < k else S):
+                pos = int(oi.perm[p])
+                r = max(rr for rr in range(world) if src_start[rr] <= pos)
+                assert pos < src_start[r + 1]
+                pulled[u] += np.array(all_g[r][src_off[r] + pos - src_start[r]])
+        assert np.allclose(pulled, orows[:k].numpy(), rtol=1e-6), "peer-pull index arithmetic"
+        assert ex.wanted[:, 0].tolist() == ex.serve
     dist.barrier()
     if rank == 0:
         print("EXCHANGE_OK", world)
@@ -79,7 +96,7 @@ WORKER = textwrap.dedent('''
 ''') % ROOT
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 4])
 def test_row_exchange_over_gloo(world, tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
