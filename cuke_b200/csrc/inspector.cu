@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(RS_THREADS) radix_scatter_kernel(const unsigne
             vals_out[pos] = val;
         }
         __syncthreads();
-        {   // thread `tid` owns digit `tid`: fold this round's counts into the running offset and clear them
+        {   // thread `tid` owns digit `tid`: fold this pass's counts into the running offset and clear them
             unsigned t = 0;
 #pragma unroll
             for (int q = 0; q < RS_THREADS / 32; ++q) { t += warp_cnt[q][tid]; warp_cnt[q][tid] = 0; }
